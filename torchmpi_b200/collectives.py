@@ -1,0 +1,356 @@
+"""Tensor collectives: broadcast, reduce, allreduce, sendreceive, allgather (+ reduce_scatter).
+
+Front end of every collective: argument checks, the collective span (flat or
+hierarchical composition), the choice of backend, sync or async.  It takes the
+place of lib/collectives.cpp and lib/collectives_cuda.cpp of the reference.
+Tensors must be contiguous; their shape is ignored (docs/collectives.md:14-23).
+The reduction is always a sum, optionally times ``scale`` (fused into the GPU
+kernels); ``scale=1`` reproduces the reference, which never divides
+(torchmpi/nn.lua:49-56).
+
+Backends:
+  ``p2p``   own data plane - CUDA peer-memory kernels on GPU tensors, the shared
+            memory heap on CPU tensors of ranks on one host
+  ``nccl``  NCCL through torch.distributed (GPU tensors; the comparison baseline)
+  ``gloo``  gloo through torch.distributed (CPU tensors; GPU tensors are staged)
+  ``mpi``   the "stock library" entry of the reference: gloo on CPU, NCCL on GPU
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+from . import _lib, config, runtime
+from ._lib import lib, check, dtype_code
+from .handles import Handle
+from .runtime import S
+
+ALGOS = {"auto": 0, "oneshot": 1, "twoshot": 2, "nvls": 3, "ring": 4}
+
+
+def _check_tensor(t: torch.Tensor, name: str = "tensor") -> None:
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{name} must be a tensor")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+    dtype_code(t.dtype)
+
+
+def _me(members: Sequence[int]) -> int:
+    try:
+        return tuple(members).index(S.rank)
+    except ValueError:
+        raise RuntimeError(f"rank {S.rank} is not in communicator {tuple(members)}") from None
+
+
+def _resolve_backend(t: torch.Tensor, backend: Optional[str], members: Sequence[int], op: str) -> str:
+    if backend is None:
+        from . import selector
+        backend = selector.select(t, op)
+    if backend == "mpi":
+        backend = "nccl" if t.is_cuda else "gloo"
+    if backend == "p2p":
+        if t.is_cuda:
+            if S.cuda_heap is None or not S.cuda_heap.covers(members):
+                backend = "nccl"
+        elif not (S.shm_ready and all(m in S.shm_ranks for m in members)):
+            backend = "gloo"
+    if backend == "nccl" and not t.is_cuda:
+        raise ValueError("the nccl backend needs CUDA tensors")
+    if backend not in ("p2p", "nccl", "gloo"):
+        raise ValueError(f"unknown backend '{backend}'")
+    return backend
+
+
+def _scale_inplace(t: torch.Tensor, scale: float) -> None:
+    if scale != 1.0:
+        if t.dtype.is_floating_point:
+            t.mul_(scale)
+        else:
+            t.copy_((t.double() * scale).to(t.dtype))
+
+
+# ---------------------------------------------------------------- flat primitives
+def _flat_allreduce(inp, out, members, backend, scale, algo, async_op) -> Optional[Handle]:
+    members = tuple(members)
+    n = inp.numel()
+    if len(members) == 1 or n == 0:
+        if out is not inp:
+            out.copy_(inp)
+        _scale_inplace(out, scale)
+        return Handle() if async_op else None
+    backend = _resolve_backend(inp, backend, members, "allreduce")
+    me = _me(members)
+    if backend == "p2p" and inp.is_cuda:
+        return S.cuda_heap.allreduce(inp, out, members, scale=scale, algo=algo, async_op=async_op)
+    if backend == "p2p":
+        arr = _lib.int_array(members)
+        args = (inp.data_ptr(), out.data_ptr(), n, dtype_code(inp.dtype), float(scale), arr, len(members), me, algo)
+        if async_op:
+            return Handle(ids=[lib.tmpi_shm_allreduce_async(*args)], keep=(inp, out, arr))
+        check(lib.tmpi_shm_allreduce(*args))
+        return None
+    group = runtime.group_for(members)
+    if backend == "gloo" and inp.is_cuda:
+        host = inp.detach().cpu()
+        work = dist.all_reduce(host, group=group, async_op=True)
+
+        def fin():
+            _scale_inplace(host, scale)
+            out.copy_(host)
+        h = Handle(works=[work], finalizers=[fin], keep=(host,))
+    else:
+        if out is not inp:
+            out.copy_(inp)
+        work = dist.all_reduce(out, group=group, async_op=True)
+        h = Handle(works=[work], finalizers=[lambda: _scale_inplace(out, scale)], keep=(out,))
+    if async_op:
+        return h
+    h.wait()
+    return None
+
+
+def _flat_broadcast(t, root, members, backend, async_op) -> Optional[Handle]:
+    members = tuple(members)
+    if len(members) == 1 or t.numel() == 0:
+        return Handle() if async_op else None
+    if not 0 <= root < len(members):
+        raise ValueError(f"root {root} outside communicator of size {len(members)}")
+    backend = _resolve_backend(t, backend, members, "broadcast")
+    me = _me(members)
+    if backend == "p2p" and t.is_cuda:
+        return S.cuda_heap.broadcast(t, root, members, async_op=async_op)
+    if backend == "p2p":
+        arr = _lib.int_array(members)
+        args = (t.data_ptr(), t.numel(), dtype_code(t.dtype), root, arr, len(members), me)
+        if async_op:
+            return Handle(ids=[lib.tmpi_shm_broadcast_async(*args)], keep=(t, arr))
+        check(lib.tmpi_shm_broadcast(*args))
+        return None
+    group = runtime.group_for(members)
+    if backend == "gloo" and t.is_cuda:
+        host = t.detach().cpu()
+        work = dist.broadcast(host, src=members[root], group=group, async_op=True)
+        h = Handle(works=[work], finalizers=[lambda: t.copy_(host)], keep=(host,))
+    else:
+        h = Handle(works=[dist.broadcast(t, src=members[root], group=group, async_op=True)], keep=(t,))
+    if async_op:
+        return h
+    h.wait()
+    return None
+
+
+def _flat_reduce(inp, out, root, members, backend, async_op) -> Optional[Handle]:
+    members = tuple(members)
+    if len(members) == 1 or inp.numel() == 0:
+        if out is not inp:
+            out.copy_(inp)
+        return Handle() if async_op else None
+    if not 0 <= root < len(members):
+        raise ValueError(f"root {root} outside communicator of size {len(members)}")
+    backend = _resolve_backend(inp, backend, members, "reduce")
+    me = _me(members)
+    if backend == "p2p" and inp.is_cuda:
+        return S.cuda_heap.reduce(inp, out, root, members, async_op=async_op)
+    if backend == "p2p":
+        arr = _lib.int_array(members)
+        check(lib.tmpi_shm_reduce(inp.data_ptr(), out.data_ptr(), inp.numel(), dtype_code(inp.dtype), root,
+                                  arr, len(members), me))
+        return Handle() if async_op else None
+    group = runtime.group_for(members)
+    # torch.distributed reduces in place and leaves non-root buffers undefined: work on a copy
+    tmp = (inp.detach().cpu() if (backend == "gloo" and inp.is_cuda) else inp.clone())
+    work = dist.reduce(tmp, dst=members[root], group=group, async_op=True)
+
+    def fin():
+        if me == root:
+            out.copy_(tmp)
+    h = Handle(works=[work], finalizers=[fin], keep=(tmp, out))
+    if async_op:
+        return h
+    h.wait()
+    return None
+
+
+# ---------------------------------------------------------------- span composition
+def _span_plan():
+    """('flat', members) or ('hier', inner, inter, cartesian) for the current collective span."""
+    b, e = runtime.collective_span()
+    outer = runtime.intra_members(b)
+    if b == e or not config.get("use_hierarchical_collectives"):
+        return ("flat", outer)
+    inner = runtime.intra_members(e)
+    inter = runtime.inter_members(e)
+    if len(inner) == len(outer) or (len(inter) <= 1 and runtime.is_cartesian_communicator(e)):
+        return ("flat", outer if len(inner) == len(outer) else inner)
+    return ("hier", inner, inter, runtime.is_cartesian_communicator(e))
+
+
+def _wait(h):
+    if h is not None:
+        h.wait()
+
+
+def allreduce_tensor(inp: torch.Tensor, out: Optional[torch.Tensor] = None, *, scale: float = 1.0,
+                     backend: Optional[str] = None, algo: str = "auto", async_op: bool = False):
+    """``out = scale * sum over ranks of inp`` on the collective span (``out`` defaults to ``inp``).
+
+    With a hierarchical span the sum runs inside each inner group, then across
+    groups (every rank on a cartesian level; only the group roots followed by a
+    broadcast on a tree level), as lib/collectives_cuda.cpp:501-581 does.
+    """
+    runtime._require_started()
+    out = inp if out is None else out
+    _check_tensor(inp, "input"), _check_tensor(out, "output")
+    if out.numel() != inp.numel() or out.dtype != inp.dtype:
+        raise ValueError("allreduce: input and output must have the same number of elements and dtype")
+    a = ALGOS[algo] if isinstance(algo, str) else int(algo)
+    plan = _span_plan()
+    if plan[0] == "flat":
+        return _flat_allreduce(inp, out, plan[1], backend, scale, a, async_op)
+    _, inner, inter, cartesian = plan
+    # staged composition; the stages depend on each other, so an async caller gets a completed handle
+    _wait(_flat_allreduce(inp, out, inner, backend, 1.0, a, False))
+    if cartesian:
+        _wait(_flat_allreduce(out, out, inter, backend, scale, a, False))
+    else:
+        if len(inter) > 1:
+            _wait(_flat_allreduce(out, out, inter, backend, scale, a, False))
+        _wait(_flat_broadcast(out, 0, inner, backend, False))
+    return Handle() if async_op else None
+
+
+def broadcast_tensor(root: int, t: torch.Tensor, *, backend: Optional[str] = None, async_op: bool = False):
+    """Copies ``t`` of rank ``root`` (rank in the outer communicator of the span) to every rank, in place."""
+    runtime._require_started()
+    _check_tensor(t)
+    b, _ = runtime.collective_span()
+    return _flat_broadcast(t, int(root), runtime.intra_members(b), backend, async_op)
+
+
+def reduce_tensor(root: int, inp: torch.Tensor, out: Optional[torch.Tensor] = None, *,
+                  backend: Optional[str] = None, async_op: bool = False):
+    """Sum to ``root``; only root's ``out`` is written, ``inp`` is left untouched when ``out`` is given."""
+    runtime._require_started()
+    out = inp if out is None else out
+    _check_tensor(inp, "input"), _check_tensor(out, "output")
+    b, _ = runtime.collective_span()
+    return _flat_reduce(inp, out, int(root), runtime.intra_members(b), backend, async_op)
+
+
+def sendreceive_tensor(t: torch.Tensor, src: int, dst: int, *, backend: Optional[str] = None):
+    """Sends ``t`` to rank ``dst`` and replaces it by what rank ``src`` sent (``MPI_Sendrecv_replace``).
+
+    Stays on the library point-to-point path (NCCL for GPU tensors, gloo for CPU).
+    """
+    runtime._require_started()
+    _check_tensor(t)
+    b, _ = runtime.collective_span()
+    members = runtime.intra_members(b)
+    if len(members) == 1:
+        return None
+    me = _me(members)
+    if src == me and dst == me:
+        return None
+    group = runtime.group_for(members)
+    use_host = t.is_cuda and backend == "gloo"
+    buf = t.detach().cpu() if use_host else t
+    recv = torch.empty_like(buf)
+    ops = [dist.P2POp(dist.isend, buf, members[dst], group=group),
+           dist.P2POp(dist.irecv, recv, members[src], group=group)]
+    for w in dist.batch_isend_irecv(ops):
+        w.wait()
+    t.copy_(recv)
+    return None
+
+
+def allgather_tensor(inp: torch.Tensor, out: torch.Tensor, *, backend: Optional[str] = None) -> torch.Tensor:
+    """Rank-ordered concatenation of every rank's ``inp`` (element counts may differ per rank).
+
+    ``out`` is resized when it is too small, as lib/collectives.cpp:253-286 does; the
+    tensor holding the result is returned.
+    """
+    runtime._require_started()
+    _check_tensor(inp, "input"), _check_tensor(out, "output")
+    b, _ = runtime.collective_span()
+    members = runtime.intra_members(b)
+    N, me = len(members), _me(members)
+    if N == 1:
+        if out.numel() < inp.numel():
+            out.resize_(inp.numel())
+        out.view(-1)[:inp.numel()].copy_(inp.view(-1))
+        return out
+    group = runtime.group_for(members)
+    counts_t = torch.zeros(N, dtype=torch.int64)
+    counts_t[me] = inp.numel()
+    dist.all_reduce(counts_t, group=group)  # control plane (gloo)
+    counts = counts_t.tolist()
+    total = sum(counts)
+    if out.numel() < total:
+        out.resize_(total)
+    flat = out.view(-1)
+    be = _resolve_backend(inp, backend, members, "allgather")
+    if be == "p2p" and inp.is_cuda:
+        S.cuda_heap.allgatherv(inp, flat, counts, members)
+    elif be == "p2p":
+        arr = _lib.int_array(members)
+        carr = (C.c_int64 * N)(*counts)
+        check(lib.tmpi_shm_allgather(inp.data_ptr(), flat.data_ptr(), inp.numel(), carr, dtype_code(inp.dtype),
+                                     arr, N, me))
+    else:
+        src = inp.detach().cpu() if (be == "gloo" and inp.is_cuda) else inp
+        outs = [torch.empty(c, dtype=src.dtype, device=src.device) for c in counts]
+        if len(set(counts)) == 1:
+            dist.all_gather(outs, src.view(-1), group=group)
+        else:
+            # unequal counts: pad to the largest
+            m = max(counts)
+            pad = torch.zeros(m, dtype=src.dtype, device=src.device)
+            pad[:src.numel()] = src.view(-1)
+            bufs = [torch.empty_like(pad) for _ in range(N)]
+            dist.all_gather(bufs, pad, group=group)
+            outs = [bufs[k][:counts[k]] for k in range(N)]
+        off = 0
+        for k in range(N):
+            flat[off:off + counts[k]].copy_(outs[k])
+            off += counts[k]
+    return out
+
+
+def reduce_scatter_tensor(inp: torch.Tensor, out: torch.Tensor, *, scale: float = 1.0,
+                          backend: Optional[str] = None):
+    """``out`` (n elements) = scale * sum over ranks of the caller-rank's slice of ``inp`` (n * size elements)."""
+    runtime._require_started()
+    _check_tensor(inp, "input"), _check_tensor(out, "output")
+    b, _ = runtime.collective_span()
+    members = runtime.intra_members(b)
+    N, me = len(members), _me(members)
+    if inp.numel() != out.numel() * N:
+        raise ValueError("reduce_scatter: input must hold size * output elements")
+    if N == 1:
+        out.view(-1).copy_(inp.view(-1))
+        _scale_inplace(out, scale)
+        return None
+    be = _resolve_backend(inp, backend, members, "reduce_scatter")
+    if be == "p2p" and inp.is_cuda:
+        S.cuda_heap.reduce_scatter(inp, out, members, scale=scale)
+        return None
+    group = runtime.group_for(members)
+    if be == "nccl":
+        dist.reduce_scatter_tensor(out.view(-1), inp.view(-1), group=group)
+        _scale_inplace(out, scale)
+        return None
+    tmp = inp.detach().cpu().clone() if inp.is_cuda else inp.clone()
+    if S.shm_ready and not inp.is_cuda and be == "p2p":
+        arr = _lib.int_array(members)
+        check(lib.tmpi_shm_allreduce(tmp.data_ptr(), tmp.data_ptr(), tmp.numel(), dtype_code(tmp.dtype),
+                                     float(scale), arr, N, me, 0))
+    else:
+        dist.all_reduce(tmp, group=group)
+        _scale_inplace(tmp, scale)
+    n = out.numel()
+    out.view(-1).copy_(tmp.view(-1)[me * n:(me + 1) * n])
+    return None

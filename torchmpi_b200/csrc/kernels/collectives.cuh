@@ -1,0 +1,340 @@
+// Device bodies of the peer-memory collectives (sm_100a, NVLink 5 / NVSwitch).
+//
+// NVSwitch gives every GPU full bandwidth to every peer, so nothing here is a
+// ring by necessity: a rank reads (or writes) all peers directly.  One launch
+// per collective; the host takes no part between its steps.  These kernels
+// replace the reference's copy-engine ring with a 2-block reduce kernel and a
+// host barrier per step (lib/detail/collectives_cuda.cpp:202-388), its IPC tree
+// / pipeline broadcast (:43-159) and its NCCL call sites
+// (lib/collectives_cuda.cpp:887-892,960-967,1046-1052).
+//
+// Bit-identical results on all ranks: every element is summed in member order
+// by exactly one rank (two-shot, NVLS, ring, reduce-scatter) or by every rank in
+// the same member order (one-shot).
+#pragma once
+#include "flags.cuh"
+#include "launch.h"
+#include "vec.cuh"
+
+namespace tmpi {
+
+template <typename T> __device__ __forceinline__ T* at(char* base, size_t off) {
+  return reinterpret_cast<T*>(base + off);
+}
+
+__device__ __forceinline__ size_t ceil_div(size_t a, size_t b) { return (a + b - 1) / b; }
+
+// ------------------------------------------------------------------ one-shot (push)
+// Slot of writer w with parity q inside a heap: in_off + (q * kMaxPeers + w) * aux.
+template <typename T, int V>
+__device__ void body_ar_oneshot(const CollArgs& a, int* s_abort) {
+  const Peers& P = a.P;
+  const size_t nv = a.n / V;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  const size_t start = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const T* in = reinterpret_cast<const T*>(a.in);
+  T* out = reinterpret_cast<T*>(a.out);
+  const int my_rank = P.rank_of[P.me];
+  for (size_t i = start; i < nv; i += stride) {
+    Pack<T, V> x = ld_pack<T, V>(in + i * V);
+    for (int m = 0; m < P.n; ++m) {
+      if (m == P.me) continue;
+      size_t slot = a.in_off + ((size_t)(P.epoch[m] & 1) * kMaxPeers + my_rank) * a.aux;
+      st_pack_peer<T, V>(at<T>(P.base[m], slot) + i * V, x);
+    }
+  }
+  if (!peer_barrier(P, 1, 10, s_abort)) return;
+  for (size_t i = start; i < nv; i += stride) {
+    Acc<T, V> acc;
+    for (int m = 0; m < P.n; ++m) {
+      Pack<T, V> x;
+      if (m == P.me) {
+        x = ld_pack<T, V>(in + i * V);
+      } else {
+        size_t slot = a.in_off + ((size_t)(P.epoch[m] & 1) * kMaxPeers + P.rank_of[m]) * a.aux;
+        x = ld_pack_peer<T, V>(at<T>(P.base[P.me], slot) + i * V);
+      }
+      if (m == 0) acc.set(x); else acc.add(x);
+    }
+    st_pack<T, V>(out + i * V, acc.pack(a.scale));
+  }
+}
+
+// ------------------------------------------------------------------ two-shot
+template <typename T, int V, int NP>
+__device__ __forceinline__ void twoshot_range(const CollArgs& a, size_t lo, size_t hi) {
+  const Peers& P = a.P;
+  const int n = NP ? NP : P.n;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = lo + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < hi; i += stride) {
+    Pack<T, V> x[NP ? NP : 1];
+    Acc<T, V> acc;
+    if constexpr (NP != 0) {
+#pragma unroll
+      for (int m = 0; m < NP; ++m) x[m] = ld_pack_peer<T, V>(at<T>(P.base[m], a.in_off) + i * V);
+      acc.set(x[0]);
+#pragma unroll
+      for (int m = 1; m < NP; ++m) acc.add(x[m]);
+    } else {
+      for (int m = 0; m < n; ++m) {
+        x[0] = ld_pack_peer<T, V>(at<T>(P.base[m], a.in_off) + i * V);
+        if (m == 0) acc.set(x[0]); else acc.add(x[0]);
+      }
+    }
+    Pack<T, V> r = acc.pack(a.scale);
+#pragma unroll
+    for (int m = 0; m < n; ++m) st_pack_peer<T, V>(at<T>(P.base[m], a.out_off) + i * V, r);
+  }
+}
+
+template <typename T, int V>
+__device__ void body_ar_twoshot(const CollArgs& a, int* s_abort) {
+  const Peers& P = a.P;
+  const size_t nv = a.n / V;
+  const size_t per = ceil_div(nv, P.n);
+  size_t lo = per * P.me, hi = lo + per;
+  if (lo > nv) lo = nv;
+  if (hi > nv) hi = nv;
+  if (!peer_barrier(P, 1, 20, s_abort)) return;
+  switch (P.n) {
+    case 2: twoshot_range<T, V, 2>(a, lo, hi); break;
+    case 4: twoshot_range<T, V, 4>(a, lo, hi); break;
+    case 8: twoshot_range<T, V, 8>(a, lo, hi); break;
+    default: twoshot_range<T, V, 0>(a, lo, hi); break;
+  }
+  peer_barrier(P, 2, 21, s_abort);
+}
+
+// ------------------------------------------------------------------ NVLS (multimem)
+template <typename T> struct Multimem {
+  static constexpr bool ok = false;
+  __device__ static uint4 ld_reduce(const void*) { return uint4{}; }
+};
+template <> struct Multimem<float> {
+  static constexpr bool ok = true;
+  __device__ static uint4 ld_reduce(const void* p) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+  }
+};
+template <> struct Multimem<__nv_bfloat16> {
+  static constexpr bool ok = true;
+  __device__ static uint4 ld_reduce(const void* p) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+  }
+};
+template <> struct Multimem<__half> {
+  static constexpr bool ok = true;
+  __device__ static uint4 ld_reduce(const void* p) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+  }
+};
+__device__ __forceinline__ void multimem_st(void* p, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};"
+               ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+template <typename T, int V>
+__device__ void body_ar_nvls(const CollArgs& a, int* s_abort) {
+  if constexpr (Multimem<T>::ok && V * sizeof(T) == 16) {
+    const Peers& P = a.P;
+    const size_t nv = a.n / V;
+    const size_t per = ceil_div(nv, P.n);
+    size_t lo = per * P.me, hi = lo + per;
+    if (lo > nv) lo = nv;
+    if (hi > nv) hi = nv;
+    if (!peer_barrier(P, 1, 30, s_abort)) return;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = lo + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < hi; i += stride) {
+      uint4 u = Multimem<T>::ld_reduce(at<T>(P.mc_base, a.in_off) + i * V);
+      if (a.scale != 1.0f) {
+        Pack<T, V> x = *reinterpret_cast<Pack<T, V>*>(&u);
+        Acc<T, V> acc; acc.set(x);
+        x = acc.pack(a.scale);
+        u = *reinterpret_cast<uint4*>(&x);
+      }
+      multimem_st(at<T>(P.mc_base, a.out_off) + i * V, u);
+    }
+    peer_barrier(P, 2, 31, s_abort);
+  }
+}
+
+// ------------------------------------------------------------------ ring (comparison variant)
+// In place on the buffer at out_off.  Chunk schedule of tmpi_ring_{send,recv}_chunk.
+template <typename T, int V>
+__device__ void body_ar_ring(const CollArgs& a, int* s_abort) {
+  const Peers& P = a.P;
+  const int N = P.n;
+  const size_t nv = a.n / V;
+  const size_t per = ceil_div(nv, N);
+  const int prev = (P.me + N - 1) % N;
+  T* mine = at<T>(P.base[P.me], a.out_off);
+  const T* theirs = at<T>(P.base[prev], a.out_off);
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  const size_t t0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  uint32_t k = 1;
+  if (!peer_barrier(P, k++, 40, s_abort)) return;
+  for (int s = 0; s < N - 1; ++s) {
+    int c = ((P.me - s - 1) % N + N) % N;
+    size_t lo = per * c, hi = lo + per;
+    if (lo > nv) lo = nv;
+    if (hi > nv) hi = nv;
+    const bool last = s == N - 2;
+    for (size_t i = lo + t0; i < hi; i += stride) {
+      Acc<T, V> acc;
+      // fixed order: what arrives from the ring first, then my own contribution
+      acc.set(ld_pack_peer<T, V>(theirs + i * V));
+      acc.add(ld_pack<T, V>(mine + i * V));
+      st_pack<T, V>(mine + i * V, acc.pack(last ? a.scale : 1.0f));
+    }
+    if (!peer_barrier(P, k++, 41, s_abort)) return;
+  }
+  for (int s = 0; s < N - 1; ++s) {
+    int c = ((P.me - s) % N + N) % N;
+    size_t lo = per * c, hi = lo + per;
+    if (lo > nv) lo = nv;
+    if (hi > nv) hi = nv;
+    for (size_t i = lo + t0; i < hi; i += stride)
+      st_pack<T, V>(mine + i * V, ld_pack_peer<T, V>(theirs + i * V));
+    if (!peer_barrier(P, k++, 42, s_abort)) return;
+  }
+}
+
+// ------------------------------------------------------------------ broadcast
+template <typename T, int V>
+__device__ void body_bcast_pull(const CollArgs& a, int* s_abort) {
+  const Peers& P = a.P;
+  const size_t nv = a.n / V;
+  if (!peer_barrier(P, 1, 50, s_abort)) return;
+  if (P.me != a.root) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    T* dst = at<T>(P.base[P.me], a.out_off);
+    const T* src = at<T>(P.base[a.root], a.out_off);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nv; i += stride)
+      st_pack<T, V>(dst + i * V, ld_pack_peer<T, V>(src + i * V));
+  }
+  peer_barrier(P, 2, 51, s_abort);
+}
+
+// Large messages: member m first pulls chunk m from the root (the root sends each byte once),
+// then everybody pulls the other chunks from their holders.
+template <typename T, int V>
+__device__ void body_bcast_chunked(const CollArgs& a, int* s_abort) {
+  const Peers& P = a.P;
+  const int N = P.n;
+  const size_t nv = a.n / V;
+  const size_t per = ceil_div(nv, N);
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  const size_t t0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  T* dst = at<T>(P.base[P.me], a.out_off);
+  auto pull = [&](int chunk, int from) {
+    size_t lo = per * chunk, hi = lo + per;
+    if (lo > nv) lo = nv;
+    if (hi > nv) hi = nv;
+    const T* src = at<T>(P.base[from], a.out_off);
+    for (size_t i = lo + t0; i < hi; i += stride) st_pack<T, V>(dst + i * V, ld_pack_peer<T, V>(src + i * V));
+  };
+  if (!peer_barrier(P, 1, 52, s_abort)) return;
+  if (P.me != a.root) pull(P.me, a.root);
+  if (!peer_barrier(P, 2, 53, s_abort)) return;
+  if (P.me != a.root)
+    for (int j = 1; j < N; ++j) {
+      int m = (P.me + j) % N;          // start at my neighbour so that holders are hit evenly
+      pull(m, m);                      // chunk m lives at member m (the root holds everything)
+    }
+  peer_barrier(P, 3, 54, s_abort);
+}
+
+template <typename T, int V>
+__device__ void body_bcast_mc(const CollArgs& a, int* s_abort) {
+  if constexpr (V * sizeof(T) == 16) {
+    const Peers& P = a.P;
+    const size_t nv = a.n / V;
+    if (!peer_barrier(P, 1, 55, s_abort)) return;
+    if (P.me == a.root) {
+      const size_t stride = (size_t)gridDim.x * blockDim.x;
+      const T* src = at<T>(P.base[P.me], a.out_off);
+      for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nv; i += stride) {
+        Pack<T, V> x = ld_pack<T, V>(src + i * V);
+        multimem_st(at<T>(P.mc_base, a.out_off) + i * V, *reinterpret_cast<uint4*>(&x));
+      }
+    }
+    peer_barrier(P, 2, 56, s_abort);
+  }
+}
+
+// ------------------------------------------------------------------ reduce to root
+template <typename T, int V>
+__device__ void body_reduce(const CollArgs& a, int* s_abort) {
+  const Peers& P = a.P;
+  const size_t nv = a.n / V;
+  if (!peer_barrier(P, 1, 60, s_abort)) return;
+  if (P.me == a.root) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    T* out = reinterpret_cast<T*>(a.out);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nv; i += stride) {
+      Acc<T, V> acc;
+      for (int m = 0; m < P.n; ++m) {
+        Pack<T, V> x = ld_pack_peer<T, V>(at<T>(P.base[m], a.in_off) + i * V);
+        if (m == 0) acc.set(x); else acc.add(x);
+      }
+      st_pack<T, V>(out + i * V, acc.pack(a.scale));
+    }
+  }
+  peer_barrier(P, 2, 61, s_abort);
+}
+
+// ------------------------------------------------------------------ all-gather (variable counts)
+template <typename T, int V>
+__device__ void body_allgather(const CollArgs& a, int* s_abort) {
+  const Peers& P = a.P;
+  if (!peer_barrier(P, 1, 70, s_abort)) return;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  const size_t t0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  T* out = reinterpret_cast<T*>(a.out);
+  size_t off = 0;
+  for (int j = 0; j < P.n; ++j) {
+    int m = (P.me + j) % P.n;
+    size_t o = 0;
+    for (int q = 0; q < m; ++q) o += a.cnt[q];
+    const T* src = at<T>(P.base[m], a.in_off);
+    const size_t nv = a.cnt[m] / V;
+    for (size_t i = t0; i < nv; i += stride) st_pack<T, V>(out + o + i * V, ld_pack_peer<T, V>(src + i * V));
+  }
+  (void)off;
+  peer_barrier(P, 2, 71, s_abort);
+}
+
+// ------------------------------------------------------------------ reduce-scatter
+template <typename T, int V>
+__device__ void body_reduce_scatter(const CollArgs& a, int* s_abort) {
+  const Peers& P = a.P;
+  const size_t nv = a.n / V;   // n = elements of the output slice
+  if (!peer_barrier(P, 1, 80, s_abort)) return;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  T* out = reinterpret_cast<T*>(a.out);
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nv; i += stride) {
+    Acc<T, V> acc;
+    for (int m = 0; m < P.n; ++m) {
+      Pack<T, V> x = ld_pack_peer<T, V>(at<T>(P.base[m], a.in_off) + (size_t)P.me * a.n + i * V);
+      if (m == 0) acc.set(x); else acc.add(x);
+    }
+    st_pack<T, V>(out + i * V, acc.pack(a.scale));
+  }
+  peer_barrier(P, 2, 81, s_abort);
+}
+
+template <typename T, int V>
+__device__ void body_barrier(const CollArgs& a, int* s_abort) {
+  peer_barrier(a.P, 1, 90, s_abort);
+}
+
+}  // namespace tmpi

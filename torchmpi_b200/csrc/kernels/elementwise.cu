@@ -1,0 +1,291 @@
+// Single-GPU hot ops: fused SGD step, softmax cross-entropy forward+backward,
+// abs-mean/variance statistics, EASGD elastic step, Downpour accumulation.
+//
+// The reference performs each of these as several cutorch kernels per tensor
+// (torchmpi/BlockSequential.lua:159-170, torchmpi/init.lua:372-381,
+// torchmpi/parameterserver/easgdupdate.lua:73-75,
+// torchmpi/parameterserver/downpourupdate.lua:49-59); each is one pass here.
+#include "collectives.cuh"
+#include "../include/tmpi_c_api.h"
+#include "../runtime/common.h"
+
+namespace tmpi {
+
+static int cuda_fail(cudaError_t e, const char* what) {
+  return fail(TMPI_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+static int sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+// ------------------------------------------------------------------ softmax cross-entropy
+// One block per row.  loss_rows[r] = logsumexp(x_r) - x_r[label]; dlogits = (softmax - onehot) * gscale.
+// The last block to finish adds the row losses in row order (deterministic) into loss_out[0].
+template <typename T>
+__global__ void __launch_bounds__(256) xent_kernel(const T* __restrict__ logits, const long long* __restrict__ labels,
+                                                   int rows, int cols, float* __restrict__ loss_out,
+                                                   T* __restrict__ dlogits, float gscale,
+                                                   float* __restrict__ row_loss, unsigned* __restrict__ counter) {
+  __shared__ float s_red[32];
+  __shared__ float s_bcast;
+  __shared__ bool s_last;
+  const int r = blockIdx.x;
+  const T* x = logits + (size_t)r * cols;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+
+  float m = -INFINITY;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) m = fmaxf(m, (float)to_acc<T>(x[c]));
+  for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(~0u, m, o));
+  if (lane == 0) s_red[warp] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float v = s_red[0];
+    for (int w = 1; w < nwarp; ++w) v = fmaxf(v, s_red[w]);
+    s_bcast = v;
+  }
+  __syncthreads();
+  m = s_bcast;
+  float sum = 0.f;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) sum += __expf((float)to_acc<T>(x[c]) - m);
+  for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(~0u, sum, o);
+  __syncthreads();
+  if (lane == 0) s_red[warp] = sum;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float v = 0.f;
+    for (int w = 0; w < nwarp; ++w) v += s_red[w];
+    s_bcast = v;
+  }
+  __syncthreads();
+  sum = s_bcast;
+  const float inv = 1.f / sum;
+  const int label = (int)labels[r];
+  if (dlogits) {
+    T* d = dlogits + (size_t)r * cols;
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+      float p = __expf((float)to_acc<T>(x[c]) - m) * inv;
+      d[c] = from_acc<T>((typename AccOf<T>::type)((p - (c == label ? 1.f : 0.f)) * gscale));
+    }
+  }
+  if (threadIdx.x == 0) {
+    float xl = (label >= 0 && label < cols) ? (float)to_acc<T>(x[label]) : m;
+    row_loss[r] = __logf(sum) + m - xl;
+    __threadfence();
+    s_last = atomicAdd(counter, 1u) == (unsigned)rows - 1;
+  }
+  __syncthreads();
+  if (s_last) {
+    __threadfence();
+    float v = 0.f;
+    for (int i = threadIdx.x; i < rows; i += blockDim.x) v += row_loss[i];   // fixed per-thread order
+    for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(~0u, v, o);
+    if (lane == 0) s_red[warp] = v;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float t = 0.f;
+      for (int w = 0; w < nwarp; ++w) t += s_red[w];
+      loss_out[0] = t;
+      *counter = 0;
+    }
+  }
+}
+
+// ------------------------------------------------------------------ abs-mean / variance
+constexpr int kStatBlocks = 1024;
+constexpr int kStatThreads = 256;
+
+template <typename T>
+__device__ __forceinline__ void absstat_body(const T* __restrict__ x, size_t n, double* __restrict__ out2,
+                                             double* __restrict__ partial, unsigned* __restrict__ counter) {
+  __shared__ double s1[kStatThreads / 32], s2[kStatThreads / 32];
+  __shared__ bool s_last;
+  double a = 0.0, b = 0.0;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    double v = fabs((double)to_acc<T>(x[i]));
+    a += v; b += v * v;
+  }
+  for (int o = 16; o; o >>= 1) { a += __shfl_xor_sync(~0u, a, o); b += __shfl_xor_sync(~0u, b, o); }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) { s1[warp] = a; s2[warp] = b; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double ta = 0.0, tb = 0.0;
+    for (int w = 0; w < kStatThreads / 32; ++w) { ta += s1[w]; tb += s2[w]; }
+    partial[2 * blockIdx.x] = ta; partial[2 * blockIdx.x + 1] = tb;
+    __threadfence();
+    s_last = atomicAdd(counter, 1u) == gridDim.x - 1;
+  }
+  __syncthreads();
+  if (s_last && threadIdx.x == 0) {
+    __threadfence();
+    double ta = 0.0, tb = 0.0;
+    for (unsigned i = 0; i < gridDim.x; ++i) { ta += partial[2 * i]; tb += partial[2 * i + 1]; }  // block order
+    out2[0] = ta; out2[1] = tb;
+    *counter = 0;   // ready for the next launch
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kStatThreads) absstat_kernel(const T* x, size_t n, double* out2, double* partial,
+                                                               unsigned* counter) {
+  absstat_body<T>(x, n, out2, partial, counter);
+}
+
+// ------------------------------------------------------------------ EASGD / Downpour
+template <typename T, int V>
+__global__ void __launch_bounds__(256) easgd_kernel(T* __restrict__ local, const T* __restrict__ center,
+                                                    T* __restrict__ delta, size_t nv, float alpha) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nv; i += (size_t)gridDim.x * blockDim.x) {
+    Pack<T, V> x = ld_pack<T, V>(local + i * V), c = ld_pack<T, V>(center + i * V), d;
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+      float xv = (float)to_acc<T>(x.v[k]);
+      float dv = (float)to_acc<T>(c.v[k]) - xv;
+      x.v[k] = from_acc<T>((typename AccOf<T>::type)(xv + alpha * dv));
+      d.v[k] = from_acc<T>((typename AccOf<T>::type)(-alpha * dv));
+    }
+    st_pack<T, V>(local + i * V, x);
+    st_pack<T, V>(delta + i * V, d);
+  }
+}
+
+template <typename T, int V>
+__global__ void __launch_bounds__(256) accum_kernel(T* __restrict__ acc, const T* __restrict__ g, size_t nv,
+                                                    float scale, int zero_first) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nv; i += (size_t)gridDim.x * blockDim.x) {
+    Pack<T, V> a = ld_pack<T, V>(acc + i * V), x = ld_pack<T, V>(g + i * V);
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+      float av = zero_first ? 0.f : (float)to_acc<T>(a.v[k]);
+      a.v[k] = from_acc<T>((typename AccOf<T>::type)(av + scale * (float)to_acc<T>(x.v[k])));
+    }
+    st_pack<T, V>(acc + i * V, a);
+  }
+}
+
+
+static bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
+
+}  // namespace tmpi
+
+using namespace tmpi;
+
+#define DISPATCH_FLOAT(dtype, ...)                                      \
+  switch (dtype) {                                                      \
+    case TMPI_F32: { using T = float; __VA_ARGS__; } break;                  \
+    case TMPI_BF16: { using T = __nv_bfloat16; __VA_ARGS__; } break;         \
+    case TMPI_F16: { using T = __half; __VA_ARGS__; } break;                 \
+    case TMPI_F64: { using T = double; __VA_ARGS__; } break;                 \
+    default: return fail(TMPI_ERR_UNSUPPORTED, "dtype %d not supported here", dtype); \
+  }
+
+extern "C" {
+
+int tmpi_sgd_momentum(void* weight, int wdt, const void* grad, int gdt, void* master, void* momentum, size_t n,
+                      float lr, float mc, float damp, float wd, float gscale, int nesterov, int first_step,
+                      int zero_grads, void* stream) {
+  if (wdt != gdt) return fail(TMPI_ERR_INVALID, "sgd: weight and gradient dtypes differ");
+  size_t es = dtype_size(wdt), V = 16 / es;
+  if (n % V || !aligned16(weight) || !aligned16(grad) || !aligned16(master) || !aligned16(momentum))
+    return fail(TMPI_ERR_INVALID, "sgd: buffers must be 16-byte aligned and hold a multiple of %zu elements", V);
+  SgdArgs a{};
+  a.P.n = 1; a.P.me = 0; a.P.base[0] = nullptr; a.P.status = nullptr;
+  // with a null heap base the "offsets" are the absolute addresses
+  a.grad_off = (size_t)grad; a.weight_off = (size_t)weight;
+  a.master = (float*)master; a.momentum = (float*)momentum; a.n = n;
+  a.lr = lr; a.momentum_coef = mc; a.dampening = damp; a.weight_decay = wd; a.grad_scale = gscale;
+  a.nesterov = nesterov; a.first_step = first_step; a.zero_grads = zero_grads; a.use_nvls = 0;
+  size_t nv = n / V;
+  int grid = (int)std::min<size_t>((nv + 511) / 512, (size_t)sm_count() * 2);
+  cudaError_t e = launch_allreduce_sgd(gdt, wdt, &a, 1, grid < 1 ? 1 : grid, 512, (cudaStream_t)stream);
+  return e == cudaSuccess ? TMPI_OK : cuda_fail(e, "sgd_momentum launch");
+}
+
+size_t tmpi_xent_scratch_bytes(int rows) { return (size_t)rows * sizeof(float) + 256; }
+
+int tmpi_xent_fwd_bwd(const void* logits, int dtype, const int64_t* labels, int rows, int cols, float* loss_sum,
+                      void* dlogits, float gscale, void* scratch, void* stream) {
+  if (rows < 1 || cols < 1) return fail(TMPI_ERR_INVALID, "xent: empty input");
+  // scratch layout: [counter (256 B, zero before first use)] [row losses]
+  unsigned* counter = (unsigned*)scratch;
+  float* row_loss = (float*)((char*)scratch + 256);
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (dtype) {
+    case TMPI_F32: xent_kernel<float><<<rows, 256, 0, s>>>((const float*)logits, (const long long*)labels, rows, cols,
+                                                           loss_sum, (float*)dlogits, gscale, row_loss, counter); break;
+    case TMPI_BF16: xent_kernel<__nv_bfloat16><<<rows, 256, 0, s>>>((const __nv_bfloat16*)logits, (const long long*)labels,
+                                                                    rows, cols, loss_sum, (__nv_bfloat16*)dlogits, gscale,
+                                                                    row_loss, counter); break;
+    case TMPI_F16: xent_kernel<__half><<<rows, 256, 0, s>>>((const __half*)logits, (const long long*)labels, rows, cols,
+                                                            loss_sum, (__half*)dlogits, gscale, row_loss, counter); break;
+    default: return fail(TMPI_ERR_UNSUPPORTED, "xent: dtype %d", dtype);
+  }
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? TMPI_OK : cuda_fail(e, "xent launch");
+}
+
+size_t tmpi_absmean_var_scratch_bytes(void) { return 256 + (size_t)kStatBlocks * 2 * sizeof(double); }
+
+// scratch: [counter, 256 B, zero before first use][2 doubles per block]
+int tmpi_absmean_var(const void* x, int dtype, size_t n, double* out2, void* scratch, void* stream) {
+  unsigned* counter = (unsigned*)scratch;
+  double* partial = (double*)((char*)scratch + 256);
+  int grid = (int)std::min<size_t>((n + kStatThreads - 1) / kStatThreads, (size_t)kStatBlocks);
+  if (grid < 1) grid = 1;
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (dtype) {
+    case TMPI_F32: absstat_kernel<float><<<grid, kStatThreads, 0, s>>>((const float*)x, n, out2, partial, counter); break;
+    case TMPI_F64: absstat_kernel<double><<<grid, kStatThreads, 0, s>>>((const double*)x, n, out2, partial, counter); break;
+    case TMPI_BF16: absstat_kernel<__nv_bfloat16><<<grid, kStatThreads, 0, s>>>((const __nv_bfloat16*)x, n, out2, partial, counter); break;
+    case TMPI_F16: absstat_kernel<__half><<<grid, kStatThreads, 0, s>>>((const __half*)x, n, out2, partial, counter); break;
+    default: return fail(TMPI_ERR_UNSUPPORTED, "absmean_var: dtype %d", dtype);
+  }
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? TMPI_OK : cuda_fail(e, "absmean_var launch");
+}
+
+int tmpi_easgd_elastic(void* local, const void* center, void* delta, size_t n, int dtype, float alpha, void* stream) {
+  cudaStream_t s = (cudaStream_t)stream;
+  bool vec = aligned16(local) && aligned16(center) && aligned16(delta);
+  DISPATCH_FLOAT(dtype, {
+    constexpr int V = 16 / sizeof(T);
+    if (vec && n % V == 0) {
+      size_t nv = n / V;
+      int grid = (int)std::min<size_t>((nv + 255) / 256, (size_t)sm_count() * 8);
+      easgd_kernel<T, V><<<grid < 1 ? 1 : grid, 256, 0, s>>>((T*)local, (const T*)center, (T*)delta, nv, alpha);
+    } else {
+      int grid = (int)std::min<size_t>((n + 255) / 256, (size_t)sm_count() * 8);
+      easgd_kernel<T, 1><<<grid < 1 ? 1 : grid, 256, 0, s>>>((T*)local, (const T*)center, (T*)delta, n, alpha);
+    }
+  });
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? TMPI_OK : cuda_fail(e, "easgd launch");
+}
+
+int tmpi_downpour_accum(void* accum, const void* grad, size_t n, int dtype, float scale, int zero_first, void* stream) {
+  cudaStream_t s = (cudaStream_t)stream;
+  bool vec = aligned16(accum) && aligned16(grad);
+  DISPATCH_FLOAT(dtype, {
+    constexpr int V = 16 / sizeof(T);
+    if (vec && n % V == 0) {
+      size_t nv = n / V;
+      int grid = (int)std::min<size_t>((nv + 255) / 256, (size_t)sm_count() * 8);
+      accum_kernel<T, V><<<grid < 1 ? 1 : grid, 256, 0, s>>>((T*)accum, (const T*)grad, nv, scale, zero_first);
+    } else {
+      int grid = (int)std::min<size_t>((n + 255) / 256, (size_t)sm_count() * 8);
+      accum_kernel<T, 1><<<grid < 1 ? 1 : grid, 256, 0, s>>>((T*)accum, (const T*)grad, n, scale, zero_first);
+    }
+  });
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? TMPI_OK : cuda_fail(e, "downpour launch");
+}
+
+}  // extern "C"
