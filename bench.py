@@ -1,0 +1,262 @@
+#!/usr/bin/env python
+"""Headline benchmark: ResNet-50 data-parallel synchronous SGD, images per second.
+
+``python bench.py --gpus N --steps K --warmup W`` trains ResNet-50 (bf16 weights and activations,
+fp32 master weights, SGD momentum 0.9, batch 256 per GPU, synthetic 3x224x224 inputs, random
+init) through ``AllReduceSGDEngine`` on N GPUs of one node (one rank per GPU; for N > 1 launch
+with torch.distributed.run) and prints ONE JSON line from rank 0.
+
+Two timed regions, both bracketed by barrier + device synchronize, both device-timed with CUDA
+events and reported as the max over ranks:
+  * ``value``  - K engine steps with the batch already on the device;
+  * ``e2e``    - K engine steps where each step's batch is copied from pinned host memory
+                 (prefetched on a copy stream, as the engine's iterator prefetch hook allows) and
+                 each step's loss is read back to the host.
+``--impl reference`` is the reference arm: the Lua/Torch7/MPI reference cannot be installed in this
+image, so it prints the ``unavailable`` line.  ``--impl nccl-pattern`` runs the reference's call
+pattern (one NCCL allreduce per parameter tensor + per-tensor SGD) for comparison.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "nccl-pattern"])
+    ap.add_argument("--batch", type=int, default=256, help="images per GPU")
+    ap.add_argument("--model", default="resnet50", choices=["resnet50", "resnet_tiny"])
+    ap.add_argument("--fused-bn", type=int, default=int(os.environ.get("TORCHMPI_FUSED_BN", "1")))
+    ap.add_argument("--bucket-mb", type=int, default=0)
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+REFERENCE_UNAVAILABLE = ("reference is Lua/Torch7 + MPI C++ (no setup.py/pyproject.toml; pip: 'not installable'); "
+                         "LuaJIT, Torch7 and MPI are absent from the image and there is no network")
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs (read-only)."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.index)],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 9:
+                continue
+            try:
+                sm.append(float(r[1])), mx.append(float(r[2]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, r[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
+        return 0
+
+    import torch
+    import torch.distributed as dist
+    import torchmpi_b200 as mpi
+    from torchmpi_b200 import config
+    from torchmpi_b200.engine import AllReduceSGDEngine
+    from torchmpi_b200.models import resnet
+    from torchmpi_b200.ops import xent
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus:
+        print(f"bench.py: --gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run", file=sys.stderr)
+        return 2
+    config.set("heap_bytes", 1 << 30)
+    if args.bucket_mb:
+        config.set("bucket_bytes", args.bucket_mb << 20)
+    mpi.start(with_cuda=True)
+    rank, dev = mpi.world_rank(), mpi.device
+    torch.manual_seed(1234)
+    torch.backends.cudnn.benchmark = True
+
+    B = args.batch
+    model = (resnet.resnet50(fused_bn=bool(args.fused_bn)) if args.model == "resnet50"
+             else resnet.resnet_tiny(1000, fused_bn=bool(args.fused_bn)))
+    from torchmpi_b200.models import to_bf16_mixed
+    model = to_bf16_mixed(model.to(dev)).to(memory_format=torch.channels_last)
+    nparams = sum(p.numel() for p in model.parameters())
+
+    # synthetic data, seeded per rank: a few distinct pinned host batches, cycled
+    g = torch.Generator().manual_seed(1000 + rank)
+    nhost = 3
+    host_x = [torch.randn(B, 3, 224, 224, generator=g).to(torch.bfloat16)
+              .contiguous(memory_format=torch.channels_last).pin_memory() for _ in range(nhost)]
+    host_y = [torch.randint(0, 1000, (B,), generator=g).pin_memory() for _ in range(nhost)]
+    dev_x = [x.to(dev, non_blocking=True) for x in host_x]
+    dev_y = [y.to(dev, non_blocking=True) for y in host_y]
+    h2d_bytes = host_x[0].numel() * host_x[0].element_size() + host_y[0].numel() * host_y[0].element_size()
+
+    if args.impl == "ours":
+        engine = AllReduceSGDEngine(usegpu=True, devicesync=False, fused=True, momentum=0.9,
+                                    gradient_scale=1.0 / world)
+        criterion = xent.CrossEntropyLoss()
+    else:
+        engine = AllReduceSGDEngine(usegpu=True, devicesync=False, fused=False, momentum=0.9,
+                                    gradient_scale=1.0 / world)
+        criterion = torch.nn.CrossEntropyLoss()
+        mpi.selector.configure()
+        for node in ("singlenode", "multinode"):
+            for mode in ("sync", "async"):
+                mpi.selector.collective_selector["gpu"][node][mode]["allreduceTensor"] = "nccl"
+                mpi.selector.collective_selector["gpu"][node][mode]["broadcastTensor"] = "nccl"
+    state = {"network": model, "criterion": criterion, "iterator": None, "lr": 0.1, "lrcriterion": 0.1,
+             "maxepoch": 1, "sample": None, "epoch": 0, "t": 0, "training": True}
+    engine._setup(model, criterion)
+    model.train()
+
+    def launches() -> int:
+        n = engine._opt.launches if engine._opt is not None else 0
+        n += getattr(xent, "launch_count", 0)
+        try:
+            from torchmpi_b200.ops import bn_relu
+            n += bn_relu.launch_count
+        except ImportError:
+            pass
+        return n
+
+    def sync_all():
+        torch.cuda.synchronize()
+        mpi.barrier()
+        torch.cuda.synchronize()
+
+    def timed(step_fn, steps):
+        sync_all()
+        sampler = ClockSampler(dev.index)
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        l0 = launches()
+        e0.record()
+        for i in range(steps):
+            step_fn(i)
+        e1.record()
+        sync_all()
+        clocks = sampler.stop()
+        ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return ms.item(), clocks, launches() - l0
+
+    # ---- device-resident input
+    def step_dev(i):
+        engine.train_step(state, {"input": dev_x[i % nhost], "target": dev_y[i % nhost]})
+
+    for i in range(args.warmup):
+        step_dev(i)
+    ms, clocks, nlaunch = timed(step_dev, args.steps)
+    value = world * B * args.steps / (ms / 1e3)
+
+    # ---- end to end: pinned host batch -> device (prefetched), loss -> host, every step
+    e2e = None
+    if not args.no_e2e:
+        copy_stream = torch.cuda.Stream()
+        bufs = [(torch.empty_like(dev_x[0]), torch.empty_like(dev_y[0])) for _ in range(2)]
+        ready = [torch.cuda.Event() for _ in range(2)]
+        consumed = [torch.cuda.Event() for _ in range(2)]
+        loss_host = torch.zeros(2, dtype=torch.float32).pin_memory()
+        loss_evt = [torch.cuda.Event() for _ in range(2)]
+        losses = []
+
+        def prefetch(i):
+            k = i % 2
+            with torch.cuda.stream(copy_stream):
+                copy_stream.wait_event(consumed[k])
+                bufs[k][0].copy_(host_x[i % nhost], non_blocking=True)
+                bufs[k][1].copy_(host_y[i % nhost], non_blocking=True)
+                ready[k].record(copy_stream)
+
+        def step_e2e(i):
+            k = i % 2
+            if i == 0:
+                prefetch(0)
+            prefetch(i + 1)                      # next batch travels while this one trains
+            torch.cuda.current_stream().wait_event(ready[k])
+            loss = engine.train_step(state, {"input": bufs[k][0], "target": bufs[k][1]})
+            consumed[k].record()
+            if i >= 1:                           # read the previous step's loss: the host never stalls on this step
+                loss_evt[(i - 1) % 2].synchronize()
+                losses.append(float(loss_host[(i - 1) % 2]))
+            loss_host[k:k + 1].copy_(loss.detach().float().reshape(1), non_blocking=True)
+            loss_evt[k].record()
+
+        for k in range(2):
+            consumed[k].record()
+        for i in range(max(3, args.warmup // 2)):
+            step_e2e(i)
+        torch.cuda.synchronize()
+        losses.clear()
+        ms_e, _, _ = timed(step_e2e, args.steps)
+        loss_evt[(args.steps - 1) % 2].synchronize()
+        losses.append(float(loss_host[(args.steps - 1) % 2]))
+        e2e = {"value": world * B * args.steps / (ms_e / 1e3), "unit": "images/s", "ms_per_step": ms_e / args.steps,
+               "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 4, "last_loss": losses[-1]}
+
+    if engine._opt is not None:
+        engine._opt.check()
+    out = {"metric": "ResNet-50 training throughput (images/s), data-parallel sync SGD via AllReduceSGDEngine",
+           "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+           "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+           "dtype": "bf16", "data": "synthetic (N(0,1) images, uniform labels, seed+rank), random-init weights",
+           "impl": args.impl,
+           "config": {"model": args.model, "params": nparams, "global_batch": B * world, "per_gpu_batch": B,
+                      "image": "3x224x224", "optimizer": "SGD momentum 0.9, fp32 master weights",
+                      "parallelism": f"dp{world}", "memory_format": "channels_last",
+                      "fused_bn": bool(args.fused_bn) and args.impl == "ours",
+                      "l2": "per-step working set (activations of 256 images) far exceeds the 126 MB L2"},
+           "clocks": clocks, "e2e": e2e, "gpu_launches": nlaunch}
+    if rank == 0:
+        print(json.dumps(out))
+    mpi.stop()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

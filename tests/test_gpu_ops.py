@@ -1,0 +1,138 @@
+"""Single-GPU hot ops against plain PyTorch fp32 references of the same op."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def test_native_library_is_loaded():
+    from torchmpi_b200 import _lib
+    assert _lib.lib.tmpi_has_cuda() == 1
+    for sym in ("tmpi_sgd_momentum", "tmpi_xent_fwd_bwd", "tmpi_bn_relu_fwd", "tmpi_cuda_allreduce_sgd"):
+        assert _lib.has_symbol(sym)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("nesterov", [False, True])
+def test_sgd_momentum_matches_torch(dtype, nesterov):
+    from torchmpi_b200.ops import elementwise
+    torch.manual_seed(0)
+    n = 8 * 12345
+    w0 = torch.randn(n, device="cuda")
+    w = w0.to(dtype).clone()
+    master = w.float().clone() if dtype != torch.float32 else None
+    mom = torch.zeros(n, device="cuda")
+    ref = torch.nn.Parameter(w.float().clone())
+    opt = torch.optim.SGD([ref], lr=0.05, momentum=0.9, weight_decay=1e-4, nesterov=nesterov)
+    for step in range(4):
+        g = torch.randn(n, device="cuda").to(dtype)
+        ref.grad = g.float() * 0.5
+        opt.step()
+        gbuf = g.clone()
+        elementwise.sgd_momentum_(w, gbuf, lr=0.05, momentum=0.9, weight_decay=1e-4, nesterov=nesterov,
+                                  grad_scale=0.5, master=master, momentum_buf=mom, first_step=(step == 0),
+                                  zero_grad=True)
+        got = master if master is not None else w
+        assert torch.allclose(got, ref.detach(), atol=2e-6, rtol=1e-5)
+        assert torch.count_nonzero(gbuf) == 0
+        if master is not None:
+            assert torch.equal(w, master.to(dtype))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_xent_forward_and_gradient(dtype):
+    from torchmpi_b200.ops import xent
+    torch.manual_seed(1)
+    for rows, cols in ((256, 1000), (7, 10), (33, 50257)):
+        logits = (torch.randn(rows, cols, device="cuda") * 3).to(dtype).requires_grad_(True)
+        labels = torch.randint(0, cols, (rows,), device="cuda")
+        loss = xent.cross_entropy(logits, labels)
+        loss.backward()
+        ref_in = logits.detach().float().requires_grad_(True)
+        ref = torch.nn.functional.cross_entropy(ref_in, labels)
+        ref.backward()
+        assert torch.allclose(loss.float(), ref, atol=1e-4, rtol=1e-5), (rows, cols, loss.item(), ref.item())
+        tol = 1e-6 if dtype == torch.float32 else 2e-3 / rows + 1e-5
+        assert torch.allclose(logits.grad.float(), ref_in.grad, atol=tol, rtol=2e-2)
+        # same input, same bits
+        loss2 = xent.cross_entropy(logits.detach(), labels)
+        assert torch.equal(loss.detach(), loss2)
+
+
+def test_absmean_var_and_check():
+    from torchmpi_b200.ops import stats
+    torch.manual_seed(2)
+    for dtype in (torch.float32, torch.bfloat16, torch.float64):
+        for n in (1, 1000, 3_000_001):
+            x = torch.randn(n, device="cuda").to(dtype)
+            m, v = stats.absmean_var(x)
+            a = x.double().abs()
+            assert abs(m - a.mean().item()) <= 1e-9 * max(1.0, abs(m))
+            if n > 1:
+                assert abs(v - a.var().item()) <= 1e-7 * max(1.0, v)
+            assert stats.absmean_var(x) == (m, v)      # deterministic
+
+
+def test_easgd_and_downpour_kernels():
+    from torchmpi_b200.ops import elementwise
+    torch.manual_seed(3)
+    for dtype, n in ((torch.float32, 100003), (torch.bfloat16, 8 * 4096), (torch.float32, 4096)):
+        x = torch.randn(n, device="cuda").to(dtype)
+        c = torch.randn(n, device="cuda").to(dtype)
+        d = torch.empty_like(x)
+        x0 = x.float().clone()
+        elementwise.easgd_elastic(x, c, d, 0.3)
+        diff = c.float() - x0
+        tol = 1e-6 if dtype == torch.float32 else 2e-2
+        assert torch.allclose(x.float(), x0 + 0.3 * diff, atol=tol, rtol=tol)
+        assert torch.allclose(d.float(), -0.3 * diff, atol=tol, rtol=tol)
+        acc = torch.randn(n, device="cuda").to(dtype)
+        g = torch.randn(n, device="cuda").to(dtype)
+        a0 = acc.float().clone()
+        elementwise.downpour_accum(acc, g, scale=2.0)
+        assert torch.allclose(acc.float(), a0 + 2.0 * g.float(), atol=tol, rtol=tol)
+        elementwise.downpour_accum(acc, g, zero_first=True)
+        assert torch.allclose(acc.float(), g.float(), atol=tol, rtol=tol)
+
+
+@pytest.mark.parametrize("C,hw,relu,res", [(64, 56, True, False), (256, 14, True, True), (2048, 7, False, False),
+                                           (16, 9, True, True)])
+def test_fused_bn_relu_matches_torch(C, hw, relu, res):
+    from torchmpi_b200.ops.bn_relu import FusedBatchNormReLU, supported
+    torch.manual_seed(4)
+    N = 16
+    x = (torch.randn(N, C, hw, hw, device="cuda") * 2 + 0.5).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    r = torch.randn(N, C, hw, hw, device="cuda").to(torch.bfloat16).contiguous(memory_format=torch.channels_last) if res else None
+    assert supported(x)
+    m = FusedBatchNormReLU(C, relu=relu).cuda()
+    with torch.no_grad():
+        m.weight.uniform_(0.5, 1.5)
+        m.bias.uniform_(-0.5, 0.5)
+    ref = torch.nn.BatchNorm2d(C).cuda()
+    ref.load_state_dict({k: v for k, v in m.state_dict().items()})
+    xa = x.clone().requires_grad_(True)
+    ra = r.clone().requires_grad_(True) if res else None
+    y = m(xa, ra)
+    xb = x.float().clone().requires_grad_(True)
+    rb = r.float().clone().requires_grad_(True) if res else None
+    z = ref(xb) + (rb if res else 0)
+    yr = torch.relu(z) if relu else z
+    assert torch.allclose(y.float(), yr, atol=3e-2, rtol=2e-2)
+    assert torch.allclose(m.running_mean, ref.running_mean, atol=1e-3, rtol=1e-3)
+    assert torch.allclose(m.running_var, ref.running_var, atol=1e-3, rtol=1e-3)
+    dy = torch.randn_like(y)
+    # use the same ReLU mask in both: derive the reference gradient from the fused output's mask
+    y.backward(dy)
+    mask = (y > 0).float() if relu else torch.ones_like(yr)
+    z.backward(dy.float() * mask)
+    scale = xb.grad.abs().max().item()
+    assert torch.allclose(xa.grad.float(), xb.grad, atol=3e-2 * scale + 1e-3, rtol=5e-2)
+    assert torch.allclose(m.weight.grad, ref.weight.grad, atol=2e-2 * ref.weight.grad.abs().max().item(), rtol=2e-2)
+    assert torch.allclose(m.bias.grad, ref.bias.grad, atol=2e-2 * ref.bias.grad.abs().max().item(), rtol=2e-2)
+    if res:
+        assert torch.allclose(ra.grad.float(), (dy.float() * mask), atol=1e-2, rtol=1e-2)
+    # eval mode uses the running statistics
+    m.eval(), ref.eval()
+    ye = m(x, r)
+    ze = ref(x.float()) + (r.float() if res else 0)
+    assert torch.allclose(ye.float(), torch.relu(ze) if relu else ze, atol=3e-2, rtol=2e-2)

@@ -239,13 +239,14 @@ int tmpi_cuda_reduce(const void* in, void* out, size_t n, int dtype, int root, c
   cudaStream_t s = (cudaStream_t)stream;
   size_t es = dtype_size(dtype), V = 16 / es;
   size_t chunk = h.bounce_bytes / es / V * V;
-  size_t whole;
-  bool direct = in_heap(in, n * es, &whole);
+  size_t whole = 0;
+  bool direct = h.emulated || in_heap(in, n * es, &whole);
+  if (h.emulated) whole = (size_t)in;              // emulation: `in` and `out` are heap offsets
   for (size_t o = 0; o < n; o += direct ? n : chunk) {
     size_t m = direct ? n : std::min(chunk, n - o);
     size_t off = whole;
     if (!direct && (st = stage_in((const char*)in + o * es, m * es, g, s, &off))) return st;
-    char* dst = (char*)out + o * es;
+    char* dst = h.emulated ? (char*)out : (char*)out + o * es;
     bool vec = al16(off) && al16((size_t)dst) && m % V == 0;
     st = run_op(OP_REDUCE, dtype, g, vec, vec ? m / V : m, s, [&](int me, CollArgs* a) {
       a->in_off = off; a->out = h.emulated ? (void*)(h.base[g->members[me]] + (size_t)out) : (void*)dst;

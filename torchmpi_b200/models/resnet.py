@@ -1,0 +1,99 @@
+"""ResNet (bottleneck) for the data-parallel benchmark: ResNet-50 = layers [3, 4, 6, 3], 25.6 M parameters.
+
+The reference ships no model beyond a logistic regressor
+(examples/mnist/mnist_allreduce.lua:31); this is the standard architecture
+(He et al. 2015, stride on the 3x3 convolution) written for channels_last bf16
+training.  Convolutions run in cuDNN; batch-norm + ReLU (+ residual add) can run
+as the fused kernels of ``ops.bn_relu`` (``fused_bn=True``).
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+import torch.nn as nn
+
+
+def _bn(ch: int, fused: bool, relu: bool, zero_init: bool = False) -> nn.Module:
+    if fused:
+        from ..ops.bn_relu import FusedBatchNormReLU
+        m = FusedBatchNormReLU(ch, relu=relu)
+    else:
+        m = nn.BatchNorm2d(ch)
+    if zero_init:
+        nn.init.zeros_(m.weight)
+    return m
+
+
+class Bottleneck(nn.Module):
+    expansion = 4
+
+    def __init__(self, inplanes: int, planes: int, stride: int = 1, downsample: Optional[nn.Module] = None,
+                 fused_bn: bool = False):
+        super().__init__()
+        self.fused = fused_bn
+        self.conv1 = nn.Conv2d(inplanes, planes, 1, bias=False)
+        self.bn1 = _bn(planes, fused_bn, relu=True)
+        self.conv2 = nn.Conv2d(planes, planes, 3, stride=stride, padding=1, bias=False)
+        self.bn2 = _bn(planes, fused_bn, relu=True)
+        self.conv3 = nn.Conv2d(planes, planes * 4, 1, bias=False)
+        self.bn3 = _bn(planes * 4, fused_bn, relu=True, zero_init=True)   # relu after the residual add
+        self.downsample = downsample
+
+    def forward(self, x):
+        identity = x if self.downsample is None else self.downsample(x)
+        if self.fused:
+            out = self.bn1(self.conv1(x))
+            out = self.bn2(self.conv2(out))
+            return self.bn3(self.conv3(out), residual=identity)
+        out = torch.relu(self.bn1(self.conv1(x)))
+        out = torch.relu(self.bn2(self.conv2(out)))
+        out = self.bn3(self.conv3(out))
+        return torch.relu(out + identity)
+
+
+class ResNet(nn.Module):
+    def __init__(self, layers: List[int], num_classes: int = 1000, fused_bn: bool = False, width: int = 64):
+        super().__init__()
+        self.fused = fused_bn
+        self.inplanes = width
+        self.conv1 = nn.Conv2d(3, width, 7, stride=2, padding=3, bias=False)
+        self.bn1 = _bn(width, fused_bn, relu=True)
+        self.maxpool = nn.MaxPool2d(3, stride=2, padding=1)
+        self.layer1 = self._make_layer(width, layers[0], 1)
+        self.layer2 = self._make_layer(width * 2, layers[1], 2)
+        self.layer3 = self._make_layer(width * 4, layers[2], 2)
+        self.layer4 = self._make_layer(width * 8, layers[3], 2)
+        self.avgpool = nn.AdaptiveAvgPool2d(1)
+        self.fc = nn.Linear(width * 8 * 4, num_classes)
+        for m in self.modules():
+            if isinstance(m, nn.Conv2d):
+                nn.init.kaiming_normal_(m.weight, mode="fan_out", nonlinearity="relu")
+
+    def _make_layer(self, planes: int, blocks: int, stride: int) -> nn.Sequential:
+        down = None
+        if stride != 1 or self.inplanes != planes * 4:
+            down = nn.Sequential(nn.Conv2d(self.inplanes, planes * 4, 1, stride=stride, bias=False),
+                                 _bn(planes * 4, self.fused, relu=False))
+        layers = [Bottleneck(self.inplanes, planes, stride, down, self.fused)]
+        self.inplanes = planes * 4
+        layers += [Bottleneck(self.inplanes, planes, fused_bn=self.fused) for _ in range(1, blocks)]
+        return nn.Sequential(*layers)
+
+    def forward(self, x):
+        x = self.bn1(self.conv1(x))
+        if not self.fused:
+            x = torch.relu(x)
+        x = self.maxpool(x)
+        x = self.layer4(self.layer3(self.layer2(self.layer1(x))))
+        x = torch.flatten(self.avgpool(x), 1)
+        return self.fc(x)
+
+
+def resnet50(num_classes: int = 1000, fused_bn: bool = False) -> ResNet:
+    return ResNet([3, 4, 6, 3], num_classes, fused_bn)
+
+
+def resnet_tiny(num_classes: int = 10, fused_bn: bool = False) -> ResNet:
+    """A two-stage miniature for tests and smoke runs."""
+    return ResNet([1, 1, 1, 1], num_classes, fused_bn, width=16)

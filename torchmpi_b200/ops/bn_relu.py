@@ -1,0 +1,104 @@
+"""Fused BatchNorm2d (+ residual add) (+ ReLU) for channels-last activations (csrc/kernels/bn_relu.cu).
+
+``FusedBatchNormReLU(C, relu=True)`` is a drop-in for ``BatchNorm2d`` followed by an optional residual
+add and ReLU: ``y = relu(bn(x) + residual)``.  Parameters and running statistics are fp32; activations
+may be bf16 / fp16 / fp32.  Training forward is three launches (statistics, finalize, apply), backward
+three more; eager PyTorch needs separate batch-norm, add and ReLU kernels each way.  CPU tensors and
+channel counts the kernel does not cover take the PyTorch ops.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .._lib import lib, check, dtype_code, has_symbol, stream_ptr
+
+launch_count = 0
+_scratch = {}
+
+
+def _scratch_for(dev: torch.device, C: int) -> torch.Tensor:
+    key = (dev.index, torch.cuda.current_stream().cuda_stream)
+    need = lib.tmpi_bn_scratch_bytes(C)
+    buf = _scratch.get(key)
+    if buf is None or buf.numel() < need:
+        buf = _scratch[key] = torch.empty(max(need, lib.tmpi_bn_scratch_bytes(2048)), dtype=torch.uint8, device=dev)
+    return buf
+
+
+def supported(x: torch.Tensor) -> bool:
+    if not (x.is_cuda and x.dim() == 4 and has_symbol("tmpi_bn_relu_fwd")):
+        return False
+    if x.dtype not in (torch.bfloat16, torch.float16, torch.float32):
+        return False
+    V = 16 // x.element_size()
+    C = x.shape[1]
+    return C % V == 0 and 256 % (C // V) == 0
+
+
+class _BnReluFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, residual, gamma, beta, running_mean, running_var, eps, momentum, relu, training):
+        global launch_count
+        x = x.contiguous(memory_format=torch.channels_last)
+        if residual is not None:
+            residual = residual.contiguous(memory_format=torch.channels_last)
+        N, C, H, W = x.shape
+        rows = N * H * W
+        y = torch.empty_like(x, memory_format=torch.channels_last)
+        if training:
+            mean = torch.empty(C, dtype=torch.float32, device=x.device)
+            invstd = torch.empty(C, dtype=torch.float32, device=x.device)
+        else:
+            mean = running_mean.float()
+            invstd = torch.rsqrt(running_var.float() + eps)
+        check(lib.tmpi_bn_relu_fwd(
+            x.data_ptr(), residual.data_ptr() if residual is not None else None, y.data_ptr(),
+            gamma.data_ptr(), beta.data_ptr(),
+            running_mean.data_ptr() if (training and running_mean is not None) else None,
+            running_var.data_ptr() if (training and running_var is not None) else None,
+            mean.data_ptr(), invstd.data_ptr(), rows, C, eps, momentum, int(relu), int(training),
+            dtype_code(x.dtype), _scratch_for(x.device, C).data_ptr(), stream_ptr()))
+        launch_count += 3 if training else 1
+        ctx.save_for_backward(x, y, gamma, mean, invstd)
+        ctx.relu, ctx.has_res = relu, residual is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        global launch_count
+        x, y, gamma, mean, invstd = ctx.saved_tensors
+        dy = dy.contiguous(memory_format=torch.channels_last)
+        N, C, H, W = x.shape
+        dx = torch.empty_like(x, memory_format=torch.channels_last)
+        dres = torch.empty_like(x, memory_format=torch.channels_last) if ctx.has_res else None
+        dgamma = torch.empty(C, dtype=torch.float32, device=x.device)
+        dbeta = torch.empty(C, dtype=torch.float32, device=x.device)
+        check(lib.tmpi_bn_relu_bwd(
+            x.data_ptr(), y.data_ptr(), dy.data_ptr(), dx.data_ptr(), dres.data_ptr() if dres is not None else None,
+            gamma.data_ptr(), mean.data_ptr(), invstd.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(),
+            N * H * W, C, int(ctx.relu), dtype_code(x.dtype), _scratch_for(x.device, C).data_ptr(), stream_ptr()))
+        launch_count += 3
+        return dx, dres, dgamma, dbeta, None, None, None, None, None, None
+
+
+class FusedBatchNormReLU(nn.BatchNorm2d):
+    """``forward(x, residual=None)`` = ``relu(batch_norm(x) + residual)`` (ReLU optional)."""
+
+    def __init__(self, num_features: int, relu: bool = True, eps: float = 1e-5, momentum: float = 0.1):
+        super().__init__(num_features, eps=eps, momentum=momentum)
+        self.relu = relu
+
+    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if supported(x) and self.weight.dtype == torch.float32:
+            # num_batches_tracked is only needed for momentum=None (cumulative average), not supported here
+            return _BnReluFn.apply(x, residual, self.weight, self.bias, self.running_mean, self.running_var,
+                                   self.eps, self.momentum, self.relu, self.training)
+        out = F.batch_norm(x, self.running_mean, self.running_var, self.weight, self.bias, self.training,
+                           self.momentum, self.eps)
+        if residual is not None:
+            out = out + residual
+        return torch.relu(out) if self.relu else out

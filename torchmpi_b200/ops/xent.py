@@ -1,0 +1,57 @@
+"""Softmax cross-entropy whose forward also produces the gradient (one kernel, one read of the logits).
+
+``cross_entropy(logits, labels)`` = mean over rows of ``logsumexp(x) - x[label]``.  On CUDA tensors the
+forward kernel writes ``(softmax - onehot) / rows`` next to the loss, so backward is a scalar multiply.
+The sum over rows is done by the last block in row order: the loss is bit-reproducible.
+"""
+from __future__ import annotations
+
+import torch
+
+from .._lib import lib, check, dtype_code, has_symbol, stream_ptr
+
+_scratch = {}
+launch_count = 0     # kernels launched by this module (read by the benchmark)
+
+
+def _scratch_for(dev: torch.device, rows: int) -> torch.Tensor:
+    key = (dev.index, rows)
+    if key not in _scratch:
+        _scratch[key] = torch.zeros(lib.tmpi_xent_scratch_bytes(rows), dtype=torch.uint8, device=dev)
+    return _scratch[key]
+
+
+class _XentFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits: torch.Tensor, labels: torch.Tensor):
+        global launch_count
+        launch_count += 1
+        rows, cols = logits.shape
+        x = logits.contiguous()
+        dlogits = torch.empty_like(x)
+        loss = torch.empty(1, dtype=torch.float32, device=x.device)
+        check(lib.tmpi_xent_fwd_bwd(x.data_ptr(), dtype_code(x.dtype), labels.data_ptr(), rows, cols,
+                                    loss.data_ptr(), dlogits.data_ptr(), 1.0 / rows,
+                                    _scratch_for(x.device, rows).data_ptr(), stream_ptr()))
+        ctx.save_for_backward(dlogits)
+        return loss[0] / rows
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        (dlogits,) = ctx.saved_tensors
+        return dlogits * grad_out.to(dlogits.dtype), None
+
+
+def cross_entropy(logits: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
+    if logits.is_cuda:
+        if not has_symbol("tmpi_xent_fwd_bwd"):
+            raise RuntimeError("torchmpi_b200: native kernel 'tmpi_xent_fwd_bwd' is missing")
+        if logits.dim() != 2 or labels.dtype != torch.int64:
+            raise ValueError("cross_entropy expects [rows, classes] logits and int64 labels")
+        return _XentFn.apply(logits, labels.contiguous())
+    return torch.nn.functional.cross_entropy(logits.float(), labels)
+
+
+class CrossEntropyLoss(torch.nn.Module):
+    def forward(self, logits, labels):
+        return cross_entropy(logits, labels)

@@ -80,7 +80,7 @@ class BlockSequential(nn.Sequential):
         groups = [[p for p in blk.parameters() if p.requires_grad] for blk in self._blocks]
         if any(groups):
             self._tmpi_buckets = FlatBuckets([p for g in groups for p in g], groups=groups,
-                                             allocator=self._allocator, pad_to=1)
+                                             allocator=self._allocator, pad_to=1, align_bytes=1)
         # re-register the blocks as the children, like `self.modules = blocks`
         for k in list(self._modules.keys()):
             del self._modules[k]

@@ -43,7 +43,8 @@ def _dense(p: torch.Tensor) -> bool:
 class FlatBuckets:
     def __init__(self, params: Sequence[torch.nn.Parameter], bucket_bytes: int = 32 << 20,
                  pad_to: int = 1024, allocator: Optional[Callable] = None, reverse: bool = True,
-                 groups: Optional[Sequence[Sequence[torch.nn.Parameter]]] = None):
+                 groups: Optional[Sequence[Sequence[torch.nn.Parameter]]] = None,
+                 align_bytes: int = ALIGN_BYTES):
         """``allocator(nbytes) -> (uint8 tensor, heap byte offset)`` places blocks in a symmetric heap.
 
         ``groups`` fixes the partition (used by BlockSequential); otherwise parameters are packed
@@ -55,16 +56,21 @@ class FlatBuckets:
             raise ValueError("FlatBuckets: no trainable parameters")
         if groups is None:
             order = list(reversed(params)) if reverse else list(params)
-            groups, cur, cur_bytes = [], [], 0
+            # one open block per (dtype, device): mixed-precision models (bf16 convolutions, fp32
+            # batch-norm scales) still get a few large blocks instead of one per dtype switch
+            groups, open_ = [], {}
             for p in order:
                 nb = p.numel() * p.element_size()
-                if cur and (cur_bytes + nb > bucket_bytes or p.dtype != cur[0].dtype or p.device != cur[0].device):
-                    groups.append(cur)
-                    cur, cur_bytes = [], 0
-                cur.append(p)
-                cur_bytes += nb
-            if cur:
-                groups.append(cur)
+                key = (p.dtype, p.device)
+                cur = open_.get(key)
+                if cur is not None and cur[1] + nb > bucket_bytes:
+                    groups.append(cur[0])
+                    cur = None
+                if cur is None:
+                    cur = open_[key] = [[], 0]
+                cur[0].append(p)
+                cur[1] += nb
+            groups += [c[0] for c in open_.values() if c[0]]
         self.buckets: List[Bucket] = []
         self._hooks = []
         for gi, grp in enumerate(groups):
@@ -73,7 +79,7 @@ class FlatBuckets:
                 continue
             dt, dev = grp[0].dtype, grp[0].device
             es = grp[0].element_size()
-            align = max(1, ALIGN_BYTES // es)
+            align = max(1, align_bytes // es)
             offs, n = [], 0
             for p in grp:
                 if p.dtype != dt or p.device != dev:
