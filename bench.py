@@ -31,7 +31,7 @@ import time
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "nccl-pattern"])
     ap.add_argument("--batch", type=int, default=256, help="images per GPU")
@@ -39,6 +39,8 @@ def parse():
     ap.add_argument("--fused-bn", type=int, default=int(os.environ.get("TORCHMPI_FUSED_BN", "1")))
     ap.add_argument("--bucket-mb", type=int, default=0)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--profile-one-step", action="store_true",
+                    help="after the warm-up run one step between cudaProfilerStart/Stop and exit (no timing)")
     return ap.parse_args()
 
 
@@ -191,6 +193,15 @@ def main():
 
     for i in range(args.warmup):
         step_dev(i)
+    if args.profile_one_step:
+        # for `ncu --profile-from-start off`: exactly one training step lies inside the profiler range
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        step_dev(0)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        mpi.stop()
+        return 0
     ms, clocks, nlaunch = timed(step_dev, args.steps)
     value = world * B * args.steps / (ms / 1e3)
 

@@ -29,7 +29,7 @@ def absmean_var(t: torch.Tensor):
     dev = t.device
     key = dev.index
     if key not in _scratch:
-        _scratch[key] = (torch.empty(lib.tmpi_absmean_var_scratch_bytes(), dtype=torch.uint8, device=dev),
+        _scratch[key] = (torch.zeros(lib.tmpi_absmean_var_scratch_bytes(), dtype=torch.uint8, device=dev),
                          torch.empty(2, dtype=torch.float64, device=dev))
     scratch, out = _scratch[key]
     check(lib.tmpi_absmean_var(t.data_ptr(), dtype_code(t.dtype), n, out.data_ptr(), scratch.data_ptr(), stream_ptr()))

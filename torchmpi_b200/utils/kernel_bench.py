@@ -1,0 +1,109 @@
+"""Times the single-GPU hot kernels in isolation and reports them against the measured HBM peak.
+
+``python -m torchmpi_b200.utils.kernel_bench [--kernel NAME] [--reps N] [--small]``
+
+Each kernel runs on inputs larger than the 126 MB L2 (``--small`` keeps them just above it, for
+profiler captures), after 3 warm-up launches, timed with CUDA events on the launching stream with a
+synchronize on both sides; an L2-sized buffer is rewritten between timed launches.  Output: one JSON
+line per kernel with the algorithmic bytes, the time, GB/s and the fraction of the copy bandwidth in
+MEASURED_PEAKS.json (fallback 6650 GB/s when the file is absent).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+from pathlib import Path
+
+import torch
+
+
+def peak_gbs() -> tuple:
+    f = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    if f.exists():
+        return json.loads(f.read_text())["hbm_gbs"], "measured"
+    return 6650.0, "fallback"
+
+
+def time_kernel(fn, reps: int, flush: torch.Tensor) -> float:
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(reps):
+        flush.add_(1)                      # rewrite > L2 bytes so the next launch starts cold
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    times.sort()
+    return times[len(times) // 2]
+
+
+def cases(small: bool):
+    from torchmpi_b200.ops import elementwise, xent, stats
+    from torchmpi_b200.ops.bn_relu import _BnReluFn
+    from torchmpi_b200._lib import lib, dtype_code, stream_ptr, check
+    dev = torch.device("cuda")
+    out = {}
+
+    n = (40 if small else 128) << 20
+    w = torch.randn(n, device=dev).to(torch.bfloat16)
+    g = torch.randn(n, device=dev).to(torch.bfloat16)
+    master, mom = w.float(), torch.zeros(n, device=dev)
+    out["sgd_momentum_bf16_master"] = (
+        lambda: elementwise.sgd_momentum_(w, g, lr=0.1, momentum=0.9, master=master, momentum_buf=mom, zero_grad=True),
+        n * (2 + 4 + 4 + 4 + 4 + 2 + 2))   # grad r, master r/w, momentum r/w, weight w, grad zero w
+
+    N, C, H = (64, 64, 112) if small else (256, 64, 112)
+    x = torch.randn(N, C, H, H, device=dev).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    res = torch.randn_like(x)
+    gamma, beta = torch.ones(C, device=dev), torch.zeros(C, device=dev)
+    rm, rv = torch.zeros(C, device=dev), torch.ones(C, device=dev)
+    nb = x.numel() * 2
+
+    def bn_fwd():
+        return _BnReluFn.apply(x, res, gamma, beta, rm, rv, 1e-5, 0.1, True, True)
+    out["bn_relu_add_fwd"] = (bn_fwd, nb * 4)          # x twice, residual once, y once
+
+    xg = x.clone().requires_grad_(True)
+    rg = res.clone().requires_grad_(True)
+    y = _BnReluFn.apply(xg, rg, gamma.requires_grad_(True), beta.requires_grad_(True), rm, rv, 1e-5, 0.1, True, True)
+    dy = torch.randn_like(y)
+
+    def bn_bwd():
+        torch.autograd.grad(y, (xg, rg), dy, retain_graph=True)
+    out["bn_relu_add_bwd"] = (bn_bwd, nb * 8)          # (x, y, dy) twice, dx, dresidual
+
+    rows, cols = (8192, 50257) if not small else (2048, 50257)
+    logits = torch.randn(rows, cols, device=dev).to(torch.bfloat16)
+    labels = torch.randint(0, cols, (rows,), device=dev)
+    out["xent_fwd_bwd"] = (lambda: xent._XentFn.apply(logits, labels), rows * cols * 2 * 4)  # x three times, dx once
+
+    big = torch.randn((64 if small else 256) << 20, device=dev)
+    out["absmean_var"] = (lambda: stats.absmean_var(big), big.numel() * 4)
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--kernel", default="all")
+    ap.add_argument("--reps", type=int, default=10)
+    ap.add_argument("--small", action="store_true")
+    args = ap.parse_args()
+    torch.cuda.set_device(0)
+    peak, how = peak_gbs()
+    flush = torch.zeros(160 << 20, dtype=torch.uint8, device="cuda")
+    for name, (fn, nbytes) in cases(args.small).items():
+        if args.kernel not in ("all", name):
+            continue
+        ms = time_kernel(fn, args.reps, flush)
+        gbs = nbytes / ms / 1e6
+        print(json.dumps({"kernel": name, "bytes": nbytes, "ms": round(ms, 4), "gbs": round(gbs, 1),
+                          "frac_of_hbm_peak": round(gbs / peak, 3), "peak": how}))
+
+
+if __name__ == "__main__":
+    main()
