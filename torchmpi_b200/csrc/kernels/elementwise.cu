@@ -289,3 +289,55 @@ int tmpi_downpour_accum(void* accum, const void* grad, size_t n, int dtype, floa
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------ allocation-free cross-entropy
+// See ../include/tmpi_noalloc.h.  The scratch of the cross-entropy kernel (a completion counter
+// and one partial loss per row) lives in this file-scope device array instead of a buffer the
+// caller would have to allocate.  Every GPU that loads the library carries the array until the
+// process exits.  All calls on a device share it, so two calls whose kernels overlap on that
+// device race on it; it also keeps the previous call's contents, which is why the counter is
+// cleared on the caller's stream before every launch.
+#include "../include/tmpi_noalloc.h"
+#include <mutex>
+
+namespace tmpi {
+namespace {
+static __device__ __align__(256) unsigned char g_xent_static_scratch[256 + TMPI_XENT_NOALLOC_MAX_ROWS * sizeof(float)];
+constexpr int kMaxDevices = 64;
+void* g_xent_static_ptr[kMaxDevices] = {};
+std::mutex g_xent_static_mu;
+
+// The array's name in host code is only a handle for the runtime, not a device address: ask for
+// the address once per device, with that device current, and hand that pointer to the kernel.
+int xent_static_scratch(void** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+  if (dev < 0 || dev >= kMaxDevices) return fail(TMPI_ERR_UNSUPPORTED, "device index %d beyond %d", dev, kMaxDevices);
+  std::lock_guard<std::mutex> lk(g_xent_static_mu);
+  if (!g_xent_static_ptr[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_xent_static_scratch);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(static cross-entropy scratch)");
+    g_xent_static_ptr[dev] = p;
+  }
+  *out = g_xent_static_ptr[dev];
+  return TMPI_OK;
+}
+}  // namespace
+}  // namespace tmpi
+
+extern "C" int tmpi_xent_fwd_bwd_noalloc(const void* logits, int dtype, const int64_t* labels, int rows, int cols,
+                                         float* loss_sum, void* dlogits, float grad_scale, void* stream) {
+  if (rows < 1 || cols < 1) return fail(TMPI_ERR_INVALID, "xent (no-alloc): empty input");
+  if (rows > TMPI_XENT_NOALLOC_MAX_ROWS)
+    return fail(TMPI_ERR_INVALID, "xent (no-alloc): %d rows exceed the built-in scratch for %d rows; "
+                "use tmpi_xent_fwd_bwd with a caller-provided scratch buffer", rows, TMPI_XENT_NOALLOC_MAX_ROWS);
+  void* scratch = nullptr;
+  int st = xent_static_scratch(&scratch);
+  if (st) return st;
+  // the completion counter must start at zero whatever an earlier (possibly failed) call left behind
+  cudaError_t e = cudaMemsetAsync(scratch, 0, 256, (cudaStream_t)stream);
+  if (e != cudaSuccess) return cuda_fail(e, "clearing the static scratch counter");
+  return tmpi_xent_fwd_bwd(logits, dtype, labels, rows, cols, loss_sum, dlogits, grad_scale, scratch, stream);
+}
