@@ -136,3 +136,21 @@ def test_fused_bn_relu_matches_torch(C, hw, relu, res):
     ye = m(x, r)
     ze = ref(x.float()) + (r.float() if res else 0)
     assert torch.allclose(ye.float(), torch.relu(ze) if relu else ze, atol=3e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("shape,k,s,p", [((8, 64, 112, 112), 3, 2, 1), ((3, 16, 17, 23), 3, 2, 1), ((2, 8, 9, 9), 2, 2, 0)])
+def test_maxpool_nhwc_matches_torch(shape, k, s, p):
+    from torchmpi_b200.ops.pool import MaxPool2d, supported
+    torch.manual_seed(5)
+    x = torch.relu(torch.randn(*shape, device="cuda")).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    assert supported(x)
+    xa = x.clone().requires_grad_(True)
+    y = MaxPool2d(k, s, p)(xa)
+    xb = x.clone().requires_grad_(True)
+    yr = torch.nn.functional.max_pool2d(xb, k, s, p)
+    assert torch.equal(y, yr)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    yr.backward(dy)
+    # many ties (zeros after ReLU): the first maximum of a window must receive the gradient
+    assert torch.allclose(xa.grad.float(), xb.grad.float(), atol=2e-2, rtol=2e-2)

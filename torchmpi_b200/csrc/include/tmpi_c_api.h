@@ -239,6 +239,11 @@ int tmpi_bn_relu_bwd(const void* x, const void* y, const void* dy, void* dx, voi
                      float* dgamma, float* dbeta, int64_t rows, int channels, int relu, int dtype,
                      void* scratch, void* stream);
 size_t tmpi_bn_scratch_bytes(int channels);
+// channels-last max pooling; idx holds one byte per output element (position inside the window)
+int tmpi_maxpool_fwd(const void* x, void* y, void* idx, int N, int H, int W, int C, int OH, int OW,
+                     int k, int s, int p, int dtype, void* stream);
+int tmpi_maxpool_bwd(const void* dy, const void* idx, void* dx, int N, int H, int W, int C, int OH, int OW,
+                     int k, int s, int p, int dtype, void* stream);
 
 // ---------------------------------------------------------------- tcgen05 GEMM family
 // C[M,N] = act(A[M,K] * B[N,K]^T (+ bias)), bf16 in, fp32 accumulate in TMEM.

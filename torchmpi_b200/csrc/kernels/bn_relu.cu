@@ -2,11 +2,11 @@
 //
 // The activation is a [rows, C] matrix (rows = N*H*W, C contiguous).  Training forward:
 //   stats    : per-channel sum and sum of squares (one read of x)
-//   finalize : mean, 1/std, running statistics (C threads)
+//   finalize : mean, 1/std, running statistics (32 x 32 threads per 32 channels)
 //   apply    : y = relu((x - mean) * invstd * gamma + beta + residual)   (read x [, residual], write y)
 // Backward, with dz = dy * (y > 0):
 //   reduce   : dbeta = sum dz, dgamma = sum dz * xhat
-//   finalize : (C threads)
+//   finalize : (same shape)
 //   apply    : dx = gamma * invstd * (dz - dbeta/M - xhat * dgamma/M); dresidual = dz
 // A framework graph runs batch-norm, add and ReLU as separate kernels with their own reads and
 // writes of the activation; the reference has no such ops at all (its only kernel is `out += in`,
@@ -75,13 +75,35 @@ __global__ void __launch_bounds__(kBnThreads) bn_reduce_kernel(
   }
 }
 
-__global__ void bn_finalize_fwd_kernel(const float* __restrict__ partial, int nblocks, int C, float inv_m, float m_corr,
-                                       float eps, float momentum, float* __restrict__ mean, float* __restrict__ invstd,
-                                       float* __restrict__ rmean, float* __restrict__ rvar) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= C) return;
-  float s1 = 0.f, s2 = 0.f;
-  for (int b = 0; b < nblocks; ++b) { s1 += partial[((size_t)b * 2) * C + c]; s2 += partial[((size_t)b * 2 + 1) * C + c]; }
+// Sums the per-block partials of 32 channels with a 32 x 32 thread block: thread (cx, ry) adds the
+// blocks ry, ry + 32, ... of channel cx (coalesced over cx), then row 0 adds the 32 slices in order.
+// A serial loop over ~600 partials per channel made this step as slow as the bandwidth-bound passes.
+__device__ __forceinline__ bool bn_partial_sums(const float* __restrict__ partial, int nblocks, int C, float* s1, float* s2) {
+  __shared__ float sh1[32][33], sh2[32][33];
+  const int c = blockIdx.x * 32 + threadIdx.x;
+  float a = 0.f, b = 0.f;
+  if (c < C)
+    for (int blk = threadIdx.y; blk < nblocks; blk += 32) {
+      a += partial[((size_t)blk * 2) * C + c];
+      b += partial[((size_t)blk * 2 + 1) * C + c];
+    }
+  sh1[threadIdx.y][threadIdx.x] = a;
+  sh2[threadIdx.y][threadIdx.x] = b;
+  __syncthreads();
+  if (threadIdx.y != 0 || c >= C) return false;
+  a = 0.f; b = 0.f;
+#pragma unroll
+  for (int r = 0; r < 32; ++r) { a += sh1[r][threadIdx.x]; b += sh2[r][threadIdx.x]; }
+  *s1 = a; *s2 = b;
+  return true;
+}
+
+__global__ void __launch_bounds__(1024) bn_finalize_fwd_kernel(
+    const float* __restrict__ partial, int nblocks, int C, float inv_m, float m_corr, float eps, float momentum,
+    float* __restrict__ mean, float* __restrict__ invstd, float* __restrict__ rmean, float* __restrict__ rvar) {
+  float s1, s2;
+  if (!bn_partial_sums(partial, nblocks, C, &s1, &s2)) return;
+  const int c = blockIdx.x * 32 + threadIdx.x;
   const float mu = s1 * inv_m;
   float var = s2 * inv_m - mu * mu;
   if (var < 0.f) var = 0.f;
@@ -91,12 +113,11 @@ __global__ void bn_finalize_fwd_kernel(const float* __restrict__ partial, int nb
   if (rvar) rvar[c] = (1.f - momentum) * rvar[c] + momentum * var * m_corr;   // unbiased, like torch
 }
 
-__global__ void bn_finalize_bwd_kernel(const float* __restrict__ partial, int nblocks, int C,
-                                       float* __restrict__ dgamma, float* __restrict__ dbeta) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= C) return;
-  float s1 = 0.f, s2 = 0.f;
-  for (int b = 0; b < nblocks; ++b) { s1 += partial[((size_t)b * 2) * C + c]; s2 += partial[((size_t)b * 2 + 1) * C + c]; }
+__global__ void __launch_bounds__(1024) bn_finalize_bwd_kernel(const float* __restrict__ partial, int nblocks, int C,
+                                                               float* __restrict__ dgamma, float* __restrict__ dbeta) {
+  float s1, s2;
+  if (!bn_partial_sums(partial, nblocks, C, &s1, &s2)) return;
+  const int c = blockIdx.x * 32 + threadIdx.x;
   dbeta[c] = s1;
   dgamma[c] = s2;
 }
@@ -186,7 +207,7 @@ static int bn_fwd_t(const void* x, const void* res, void* y, const float* gamma,
     bn_reduce_kernel<T, V, false><<<grid, kBnThreads, 0, s>>>((const T*)x, nullptr, nullptr, nullptr, nullptr, nvec, C, 0,
                                                               (float*)scratch);
     float m = (float)rows;
-    bn_finalize_fwd_kernel<<<(C + 127) / 128, 128, 0, s>>>((const float*)scratch, grid, C, 1.f / m,
+    bn_finalize_fwd_kernel<<<(C + 31) / 32, dim3(32, 32), 0, s>>>((const float*)scratch, grid, C, 1.f / m,
                                                            rows > 1 ? m / (m - 1.f) : 1.f, eps, momentum, smean, sinv,
                                                            rmean, rvar);
   }
@@ -206,7 +227,7 @@ static int bn_bwd_t(const void* x, const void* y, const void* dy, void* dx, void
   int grid = bn_grid(nvec);
   bn_reduce_kernel<T, V, true><<<grid, kBnThreads, 0, s>>>((const T*)x, (const T*)y, (const T*)dy, smean, sinv, nvec, C, relu,
                                                            (float*)scratch);
-  bn_finalize_bwd_kernel<<<(C + 127) / 128, 128, 0, s>>>((const float*)scratch, grid, C, dgamma, dbeta);
+  bn_finalize_bwd_kernel<<<(C + 31) / 32, dim3(32, 32), 0, s>>>((const float*)scratch, grid, C, dgamma, dbeta);
   bn_apply_bwd_kernel<T, V><<<grid, kBnThreads, 0, s>>>((const T*)x, (const T*)y, (const T*)dy, (T*)dx, (T*)dres, gamma, smean,
                                                         sinv, dgamma, dbeta, nvec, C, relu, 1.f / (float)rows);
   cudaError_t e = cudaGetLastError();

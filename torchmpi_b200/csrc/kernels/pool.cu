@@ -1,0 +1,134 @@
+// Max pooling for channels-last activations, forward (with window index) and backward.
+//
+// Forward: one thread per output position and group of V channels (one 16-byte pack); it scans
+// the k x k window, keeps the first maximum (strictly-greater comparison, NaN propagates) and stores
+// the value and the position inside the window as one byte per element.  Backward: one thread per
+// input position and channel group gathers from the (at most ceil(k/s)^2) outputs whose window
+// covers it and whose stored index points at it - no atomics, every byte of dx written once.
+// Traffic is one read of the input and one write of output + index forward, and a read of
+// dy + index and one write of dx backward.
+#include "vec.cuh"
+#include "../include/tmpi_c_api.h"
+#include "../runtime/common.h"
+#include <algorithm>
+
+namespace tmpi {
+
+struct PoolDims { int N, H, W, C, OH, OW, k, s, p; };
+
+template <typename T, int V>
+__global__ void __launch_bounds__(256) maxpool_fwd_kernel(const T* __restrict__ x, T* __restrict__ y,
+                                                          unsigned char* __restrict__ idx, PoolDims d) {
+  const int cvn = d.C / V;
+  const size_t total = (size_t)d.N * d.OH * d.OW * cvn;
+  for (size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (size_t)gridDim.x * blockDim.x) {
+    const int cv = (int)(t % cvn);
+    size_t r = t / cvn;
+    const int ow = (int)(r % d.OW); r /= d.OW;
+    const int oh = (int)(r % d.OH);
+    const int n = (int)(r / d.OH);
+    float best[V];
+    unsigned char bi[V];
+    bool first = true;
+    for (int kh = 0; kh < d.k; ++kh) {
+      const int ih = oh * d.s - d.p + kh;
+      if (ih < 0 || ih >= d.H) continue;
+      for (int kw = 0; kw < d.k; ++kw) {
+        const int iw = ow * d.s - d.p + kw;
+        if (iw < 0 || iw >= d.W) continue;
+        Pack<T, V> v = ld_pack<T, V>(x + (((size_t)n * d.H + ih) * d.W + iw) * d.C + (size_t)cv * V);
+#pragma unroll
+        for (int c = 0; c < V; ++c) {
+          const float f = (float)to_acc<T>(v.v[c]);
+          if (first || f > best[c] || f != f) { best[c] = f; bi[c] = (unsigned char)(kh * d.k + kw); }
+        }
+        first = false;
+      }
+    }
+    Pack<T, V> out;
+    Pack<unsigned char, V> oi;
+#pragma unroll
+    for (int c = 0; c < V; ++c) { out.v[c] = from_acc<T>((typename AccOf<T>::type)best[c]); oi.v[c] = bi[c]; }
+    st_pack<T, V>(y + t * V, out);
+    st_pack<unsigned char, V>(idx + t * V, oi);
+  }
+}
+
+template <typename T, int V>
+__global__ void __launch_bounds__(256) maxpool_bwd_kernel(const T* __restrict__ dy, const unsigned char* __restrict__ idx,
+                                                          T* __restrict__ dx, PoolDims d) {
+  const int cvn = d.C / V;
+  const size_t total = (size_t)d.N * d.H * d.W * cvn;
+  for (size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (size_t)gridDim.x * blockDim.x) {
+    const int cv = (int)(t % cvn);
+    size_t r = t / cvn;
+    const int iw = (int)(r % d.W); r /= d.W;
+    const int ih = (int)(r % d.H);
+    const int n = (int)(r / d.H);
+    float acc[V];
+#pragma unroll
+    for (int c = 0; c < V; ++c) acc[c] = 0.f;
+    // outputs whose window [o*s - p, o*s - p + k) contains the input coordinate
+    int oh_lo = ih + d.p - d.k + 1; oh_lo = oh_lo <= 0 ? 0 : (oh_lo + d.s - 1) / d.s;
+    int ow_lo = iw + d.p - d.k + 1; ow_lo = ow_lo <= 0 ? 0 : (ow_lo + d.s - 1) / d.s;
+    const int oh_hi = min((ih + d.p) / d.s, d.OH - 1), ow_hi = min((iw + d.p) / d.s, d.OW - 1);
+    for (int oh = oh_lo; oh <= oh_hi; ++oh)
+      for (int ow = ow_lo; ow <= ow_hi; ++ow) {
+        const unsigned char w = (unsigned char)((ih - (oh * d.s - d.p)) * d.k + (iw - (ow * d.s - d.p)));
+        const size_t o = ((((size_t)n * d.OH + oh) * d.OW + ow) * cvn + cv) * V;
+        Pack<unsigned char, V> iv = ld_pack<unsigned char, V>(idx + o);
+        Pack<T, V> gv = ld_pack<T, V>(dy + o);
+#pragma unroll
+        for (int c = 0; c < V; ++c)
+          if (iv.v[c] == w) acc[c] += (float)to_acc<T>(gv.v[c]);
+      }
+    Pack<T, V> out;
+#pragma unroll
+    for (int c = 0; c < V; ++c) out.v[c] = from_acc<T>((typename AccOf<T>::type)acc[c]);
+    st_pack<T, V>(dx + t * V, out);
+  }
+}
+
+template <typename T>
+static int pool_launch(bool fwd, const void* a, void* b, void* idx, PoolDims d, cudaStream_t s) {
+  constexpr int V = 16 / sizeof(T);
+  if (d.C % V) return fail(TMPI_ERR_INVALID, "maxpool: C=%d must be a multiple of %d", d.C, V);
+  if (d.k * d.k > 255) return fail(TMPI_ERR_INVALID, "maxpool: window too large");
+  size_t total = (size_t)d.N * (fwd ? d.OH * d.OW : d.H * d.W) * (d.C / V);
+  int grid = (int)std::max<size_t>(1, std::min<size_t>((total + 255) / 256, 148 * 16));
+  if (fwd) maxpool_fwd_kernel<T, V><<<grid, 256, 0, s>>>((const T*)a, (T*)b, (unsigned char*)idx, d);
+  else maxpool_bwd_kernel<T, V><<<grid, 256, 0, s>>>((const T*)a, (const unsigned char*)idx, (T*)b, d);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? TMPI_OK : fail(TMPI_ERR_CUDA, "maxpool launch: %s", cudaGetErrorString(e));
+}
+
+}  // namespace tmpi
+
+using namespace tmpi;
+
+extern "C" {
+
+// x: [N, H, W, C] channels-last; y, idx: [N, OH, OW, C]
+int tmpi_maxpool_fwd(const void* x, void* y, void* idx, int N, int H, int W, int C, int OH, int OW, int k, int s,
+                     int p, int dtype, void* stream) {
+  PoolDims d{N, H, W, C, OH, OW, k, s, p};
+  switch (dtype) {
+    case TMPI_BF16: return pool_launch<__nv_bfloat16>(true, x, y, idx, d, (cudaStream_t)stream);
+    case TMPI_F16: return pool_launch<__half>(true, x, y, idx, d, (cudaStream_t)stream);
+    case TMPI_F32: return pool_launch<float>(true, x, y, idx, d, (cudaStream_t)stream);
+  }
+  return fail(TMPI_ERR_UNSUPPORTED, "maxpool: dtype %d", dtype);
+}
+
+int tmpi_maxpool_bwd(const void* dy, const void* idx, void* dx, int N, int H, int W, int C, int OH, int OW, int k,
+                     int s, int p, int dtype, void* stream) {
+  PoolDims d{N, H, W, C, OH, OW, k, s, p};
+  switch (dtype) {
+    case TMPI_BF16: return pool_launch<__nv_bfloat16>(false, dy, dx, const_cast<void*>(idx), d, (cudaStream_t)stream);
+    case TMPI_F16: return pool_launch<__half>(false, dy, dx, const_cast<void*>(idx), d, (cudaStream_t)stream);
+    case TMPI_F32: return pool_launch<float>(false, dy, dx, const_cast<void*>(idx), d, (cudaStream_t)stream);
+  }
+  return fail(TMPI_ERR_UNSUPPORTED, "maxpool: dtype %d", dtype);
+}
+
+}  // extern "C"

@@ -59,7 +59,11 @@ class ResNet(nn.Module):
         self.inplanes = width
         self.conv1 = nn.Conv2d(3, width, 7, stride=2, padding=3, bias=False)
         self.bn1 = _bn(width, fused_bn, relu=True)
-        self.maxpool = nn.MaxPool2d(3, stride=2, padding=1)
+        if fused_bn:
+            from ..ops.pool import MaxPool2d
+            self.maxpool = MaxPool2d(3, stride=2, padding=1)
+        else:
+            self.maxpool = nn.MaxPool2d(3, stride=2, padding=1)
         self.layer1 = self._make_layer(width, layers[0], 1)
         self.layer2 = self._make_layer(width * 2, layers[1], 2)
         self.layer3 = self._make_layer(width * 4, layers[2], 2)
