@@ -258,3 +258,56 @@ def _absent_peer(rank, world):
 def test_bounded_wait_when_peer_never_launches():
     res = run_ranks(_absent_peer, 2, timeout=300)
     assert res[0].startswith("timeout"), res
+
+
+def _tp_mlp(rank, world):
+    """Tensor-parallel MLP (fused all-gather->GEMM, GEMM->reduce-scatter) against the unsharded model."""
+    import math
+    import torchmpi_b200 as mpi
+    from torchmpi_b200 import config
+    from torchmpi_b200.parallel.tensor_parallel import TensorParallelMLP, TensorParallelMLPBlock
+    config.set("device_wait_budget_ms", 5000)
+    mpi.start(with_cuda=True)
+    dev = mpi.device
+    rows, D, F = 256, 512, 2048
+    M = rows * world
+    model = TensorParallelMLP(rows, d_model=D, d_hidden=F, layers=4, bias=True)
+    f = F // world
+    # rebuild the unsharded weights from the per-slice seeds
+    w1 = torch.empty(2, F, D)
+    w2 = torch.empty(2, D, F)
+    for b in range(2):
+        for r in range(world):
+            g = torch.Generator().manual_seed(TensorParallelMLPBlock.slice_seed(r, F))
+            w1[b, r * f:(r + 1) * f] = torch.randn(f, D, generator=g) / math.sqrt(D)
+            w2[b, :, r * f:(r + 1) * f] = torch.randn(D, f, generator=g) / math.sqrt(F)
+    w1, w2 = w1.to(dev).to(torch.bfloat16).float(), w2.to(dev).to(torch.bfloat16).float()
+    gx = torch.Generator().manual_seed(99)
+    x_full = torch.randn(M, D, generator=gx).to(dev).to(torch.bfloat16)
+    dy_full = torch.randn(M, D, generator=gx).to(dev).to(torch.bfloat16)
+    xs = x_full[rank * rows:(rank + 1) * rows].clone().requires_grad_(True)
+    for rep in range(2):
+        y = model(xs)
+        y.backward(dy_full[rank * rows:(rank + 1) * rows])
+    torch.cuda.synchronize()
+    model.tp.check()
+    # reference in fp32 on the gathered data (two passes accumulate the gradients twice)
+    xr = x_full.float().requires_grad_(True)
+    p1 = [w1[b].clone().requires_grad_(True) for b in range(2)]
+    p2 = [w2[b].clone().requires_grad_(True) for b in range(2)]
+    h = xr
+    for b in range(2):
+        h = torch.nn.functional.gelu(h @ p1[b].t()) @ p2[b].t()
+    h.backward(dy_full.float())
+    sl = slice(rank * rows, (rank + 1) * rows)
+    assert torch.allclose(y.float(), h[sl], rtol=5e-2, atol=5e-2), (y.float() - h[sl]).abs().max()
+    assert torch.allclose(xs.grad.float(), 2 * xr.grad[sl], rtol=5e-2, atol=5e-2)
+    blk = model[0]
+    assert torch.allclose(blk.w1.grad.float(), 2 * p1[0].grad[rank * f:(rank + 1) * f], rtol=5e-2, atol=0.3)
+    assert torch.allclose(blk.w2.grad.float(), 2 * p2[0].grad[:, rank * f:(rank + 1) * f], rtol=5e-2, atol=0.3)
+    mpi.stop()
+    return True
+
+
+def test_tensor_parallel_mlp():
+    assert all(run_ranks(_tp_mlp, world_sizes()[-1], timeout=600))

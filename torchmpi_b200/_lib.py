@@ -180,6 +180,7 @@ _CUDA_PROTOS = {
     "tmpi_maxpool_fwd": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "tmpi_maxpool_bwd": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "tmpi_gemm_bf16": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "tmpi_gemm_status": (_i, []),
 }
 
 

@@ -114,6 +114,7 @@ def start(with_cuda: Optional[bool] = None,
     S.groups = {}
     check(lib.tmpi_set_tunable(b"use_cartesian_communicator", 1 if with_cartesian_communicator else 0))
     check(lib.tmpi_comm_reset(S.rank, S.world))
+    runtime.plan_cache.clear()
     S.started = True
 
     jid = [uuid.uuid4().hex[:12] if S.rank == 0 else None]

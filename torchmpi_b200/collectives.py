@@ -31,12 +31,20 @@ from .runtime import S
 ALGOS = {"auto": 0, "oneshot": 1, "twoshot": 2, "nvls": 3, "ring": 4}
 
 
-def _check_tensor(t: torch.Tensor, name: str = "tensor") -> None:
+def _check_tensor(t: torch.Tensor, name: str = "tensor") -> torch.Tensor:
+    """Validates ``t`` and returns a flat view of its memory.  Collectives ignore shape, so a dense
+    channels-last tensor is as good as a contiguous one; anything with gaps is rejected, as the
+    reference rejects non-contiguous tensors (lib/collectives.cpp:64-66)."""
     if not isinstance(t, torch.Tensor):
         raise TypeError(f"{name} must be a tensor")
-    if not t.is_contiguous():
-        raise ValueError(f"{name} must be contiguous")
     dtype_code(t.dtype)
+    if t.is_contiguous():
+        return t.view(-1)
+    if t.dim() == 4 and t.is_contiguous(memory_format=torch.channels_last):
+        return t.permute(0, 2, 3, 1).reshape(-1)
+    if t.dim() == 5 and t.is_contiguous(memory_format=torch.channels_last_3d):
+        return t.permute(0, 2, 3, 4, 1).reshape(-1)
+    raise ValueError(f"{name} must be contiguous")
 
 
 def _me(members: Sequence[int]) -> int:
@@ -178,15 +186,22 @@ def _flat_reduce(inp, out, root, members, backend, async_op) -> Optional[Handle]
 # ---------------------------------------------------------------- span composition
 def _span_plan():
     """('flat', members) or ('hier', inner, inter, cartesian) for the current collective span."""
+    cached = runtime.plan_cache.get("span_plan")
+    if cached is not None:
+        return cached
     b, e = runtime.collective_span()
     outer = runtime.intra_members(b)
     if b == e or not config.get("use_hierarchical_collectives"):
-        return ("flat", outer)
-    inner = runtime.intra_members(e)
-    inter = runtime.inter_members(e)
-    if len(inner) == len(outer) or (len(inter) <= 1 and runtime.is_cartesian_communicator(e)):
-        return ("flat", outer if len(inner) == len(outer) else inner)
-    return ("hier", inner, inter, runtime.is_cartesian_communicator(e))
+        plan = ("flat", outer)
+    else:
+        inner = runtime.intra_members(e)
+        inter = runtime.inter_members(e)
+        if len(inner) == len(outer) or (len(inter) <= 1 and runtime.is_cartesian_communicator(e)):
+            plan = ("flat", outer if len(inner) == len(outer) else inner)
+        else:
+            plan = ("hier", inner, inter, runtime.is_cartesian_communicator(e))
+    runtime.plan_cache["span_plan"] = plan        # dropped whenever communicators, span or tunables change
+    return plan
 
 
 def _wait(h):
@@ -203,8 +218,9 @@ def allreduce_tensor(inp: torch.Tensor, out: Optional[torch.Tensor] = None, *, s
     broadcast on a tree level), as lib/collectives_cuda.cpp:501-581 does.
     """
     runtime._require_started()
-    out = inp if out is None else out
-    _check_tensor(inp, "input"), _check_tensor(out, "output")
+    same = out is None or out is inp
+    inp = _check_tensor(inp, "input")
+    out = inp if same else _check_tensor(out, "output")
     if out.numel() != inp.numel() or out.dtype != inp.dtype:
         raise ValueError("allreduce: input and output must have the same number of elements and dtype")
     a = ALGOS[algo] if isinstance(algo, str) else int(algo)
@@ -226,7 +242,7 @@ def allreduce_tensor(inp: torch.Tensor, out: Optional[torch.Tensor] = None, *, s
 def broadcast_tensor(root: int, t: torch.Tensor, *, backend: Optional[str] = None, async_op: bool = False):
     """Copies ``t`` of rank ``root`` (rank in the outer communicator of the span) to every rank, in place."""
     runtime._require_started()
-    _check_tensor(t)
+    t = _check_tensor(t)
     b, _ = runtime.collective_span()
     return _flat_broadcast(t, int(root), runtime.intra_members(b), backend, async_op)
 
@@ -235,8 +251,9 @@ def reduce_tensor(root: int, inp: torch.Tensor, out: Optional[torch.Tensor] = No
                   backend: Optional[str] = None, async_op: bool = False):
     """Sum to ``root``; only root's ``out`` is written, ``inp`` is left untouched when ``out`` is given."""
     runtime._require_started()
-    out = inp if out is None else out
-    _check_tensor(inp, "input"), _check_tensor(out, "output")
+    same = out is None or out is inp
+    inp = _check_tensor(inp, "input")
+    out = inp if same else _check_tensor(out, "output")
     b, _ = runtime.collective_span()
     return _flat_reduce(inp, out, int(root), runtime.intra_members(b), backend, async_op)
 
@@ -247,7 +264,7 @@ def sendreceive_tensor(t: torch.Tensor, src: int, dst: int, *, backend: Optional
     Stays on the library point-to-point path (NCCL for GPU tensors, gloo for CPU).
     """
     runtime._require_started()
-    _check_tensor(t)
+    t = _check_tensor(t)
     b, _ = runtime.collective_span()
     members = runtime.intra_members(b)
     if len(members) == 1:
@@ -274,7 +291,8 @@ def allgather_tensor(inp: torch.Tensor, out: torch.Tensor, *, backend: Optional[
     tensor holding the result is returned.
     """
     runtime._require_started()
-    _check_tensor(inp, "input"), _check_tensor(out, "output")
+    inp = _check_tensor(inp, "input")
+    _check_tensor(out, "output")        # `out` may be resized below, so it stays as passed
     b, _ = runtime.collective_span()
     members = runtime.intra_members(b)
     N, me = len(members), _me(members)
@@ -324,7 +342,7 @@ def reduce_scatter_tensor(inp: torch.Tensor, out: torch.Tensor, *, scale: float 
                           backend: Optional[str] = None):
     """``out`` (n elements) = scale * sum over ranks of the caller-rank's slice of ``inp`` (n * size elements)."""
     runtime._require_started()
-    _check_tensor(inp, "input"), _check_tensor(out, "output")
+    inp, out = _check_tensor(inp, "input"), _check_tensor(out, "output")
     b, _ = runtime.collective_span()
     members = runtime.intra_members(b)
     N, me = len(members), _me(members)

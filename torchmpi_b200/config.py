@@ -19,6 +19,8 @@ def names() -> list:
 
 def set(name: str, value: int) -> None:  # noqa: A001 - mirrors the C API
     check(lib.tmpi_set_tunable(name.encode(), int(value)))
+    from . import runtime
+    runtime.plan_cache.clear()
 
 
 def get(name: str) -> int:

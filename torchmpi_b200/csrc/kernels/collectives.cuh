@@ -61,28 +61,42 @@ __device__ void body_ar_oneshot(const CollArgs& a, int* s_abort) {
 }
 
 // ------------------------------------------------------------------ two-shot
+// NP = number of members known at compile time (0: runtime loop).  Each thread keeps about eight
+// 16-byte peer loads in flight (U vectors x NP peers): NVLink round trips take microseconds, so the
+// bytes in flight per thread, not the thread count, decide the bandwidth.
 template <typename T, int V, int NP>
 __device__ __forceinline__ void twoshot_range(const CollArgs& a, size_t lo, size_t hi) {
   const Peers& P = a.P;
   const int n = NP ? NP : P.n;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
-  for (size_t i = lo + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < hi; i += stride) {
-    Pack<T, V> x[NP ? NP : 1];
-    Acc<T, V> acc;
-    if constexpr (NP != 0) {
+  size_t i = lo + (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if constexpr (NP != 0) {
+    constexpr int U = NP >= 8 ? 1 : 8 / NP;
+    for (; i + (U - 1) * stride < hi; i += U * stride) {
+      Pack<T, V> x[U][NP];
 #pragma unroll
-      for (int m = 0; m < NP; ++m) x[m] = ld_pack_peer<T, V>(at<T>(P.base[m], a.in_off) + i * V);
-      acc.set(x[0]);
+      for (int u = 0; u < U; ++u)
 #pragma unroll
-      for (int m = 1; m < NP; ++m) acc.add(x[m]);
-    } else {
-      for (int m = 0; m < n; ++m) {
-        x[0] = ld_pack_peer<T, V>(at<T>(P.base[m], a.in_off) + i * V);
-        if (m == 0) acc.set(x[0]); else acc.add(x[0]);
+        for (int m = 0; m < NP; ++m) x[u][m] = ld_pack_peer<T, V>(at<T>(P.base[m], a.in_off) + (i + u * stride) * V);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        Acc<T, V> acc;
+        acc.set(x[u][0]);
+#pragma unroll
+        for (int m = 1; m < NP; ++m) acc.add(x[u][m]);
+        Pack<T, V> r = acc.pack(a.scale);
+#pragma unroll
+        for (int m = 0; m < NP; ++m) st_pack_peer<T, V>(at<T>(P.base[m], a.out_off) + (i + u * stride) * V, r);
       }
     }
+  }
+  for (; i < hi; i += stride) {
+    Acc<T, V> acc;
+    for (int m = 0; m < n; ++m) {
+      Pack<T, V> x = ld_pack_peer<T, V>(at<T>(P.base[m], a.in_off) + i * V);
+      if (m == 0) acc.set(x); else acc.add(x);
+    }
     Pack<T, V> r = acc.pack(a.scale);
-#pragma unroll
     for (int m = 0; m < n; ++m) st_pack_peer<T, V>(at<T>(P.base[m], a.out_off) + i * V, r);
   }
 }
@@ -153,16 +167,25 @@ __device__ void body_ar_nvls(const CollArgs& a, int* s_abort) {
     if (hi > nv) hi = nv;
     if (!peer_barrier(P, 1, 30, s_abort)) return;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t i = lo + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < hi; i += stride) {
-      uint4 u = Multimem<T>::ld_reduce(at<T>(P.mc_base, a.in_off) + i * V);
+    size_t i = lo + (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    auto finish = [&](uint4 u, size_t at_i) {
       if (a.scale != 1.0f) {
         Pack<T, V> x = *reinterpret_cast<Pack<T, V>*>(&u);
         Acc<T, V> acc; acc.set(x);
         x = acc.pack(a.scale);
         u = *reinterpret_cast<uint4*>(&x);
       }
-      multimem_st(at<T>(P.mc_base, a.out_off) + i * V, u);
+      multimem_st(at<T>(P.mc_base, a.out_off) + at_i * V, u);
+    };
+    constexpr int U = 8;                      // eight switch reductions in flight per thread
+    for (; i + (U - 1) * stride < hi; i += U * stride) {
+      uint4 u[U];
+#pragma unroll
+      for (int k = 0; k < U; ++k) u[k] = Multimem<T>::ld_reduce(at<T>(P.mc_base, a.in_off) + (i + k * stride) * V);
+#pragma unroll
+      for (int k = 0; k < U; ++k) finish(u[k], i + k * stride);
     }
+    for (; i < hi; i += stride) finish(Multimem<T>::ld_reduce(at<T>(P.mc_base, a.in_off) + i * V), i);
     peer_barrier(P, 2, 31, s_abort);
   }
 }

@@ -1,0 +1,201 @@
+// Building blocks of the bf16 tcgen05 GEMM: C[M,N] = act(A[M,K] * B[N,K]^T + bias).
+//
+// One persistent CTA per SM, 192 threads in three roles:
+//   warp 0      TMA producer - one elected thread streams 128x64 A tiles and 256x64 B tiles
+//               (128-byte swizzle) into a 4-stage shared-memory ring, completion on mbarriers;
+//   warp 1      MMA issuer - owns the tensor memory (512 columns = two 128x256 fp32 accumulators);
+//               one thread issues four tcgen05.mma (K = 16 each) per stage and commits the stage
+//               back to the producer, then commits the accumulator to the epilogue;
+//   warps 2-5   epilogue - tcgen05.ld the accumulator (lane quarter = warp % 4), add bias, apply
+//               GELU, convert to bf16 and store, while the issuer already fills the other accumulator.
+// Every mbarrier wait is bounded; on expiry the CTA records an error, stops issuing work, drains
+// what is in flight within a second budget, frees its tensor memory and returns.
+//
+// The roles take three hooks so that the fused kernels (all-gather -> GEMM, GEMM -> reduce-scatter)
+// reuse them: a tile order, a "rows of A are ready" wait in the producer, and the row -> destination
+// mapping of the epilogue.
+#pragma once
+#include <cuda_bf16.h>
+#include "sm100_ptx.cuh"
+
+namespace tmpi {
+namespace gemm {
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16;
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr unsigned long long kWaitBudgetNs = 4000000000ull;   // 4 s: far beyond any legitimate wait
+
+enum { EPI_NONE = 0, EPI_BIAS = 1, EPI_GELU = 2, EPI_BIAS_GELU = 3 };
+
+struct Shared {
+  uint64_t full[STAGES], empty[STAGES], acc_full[2], acc_empty[2];
+  uint32_t tmem_base;
+  int error;
+};
+
+struct Problem {
+  int M, N, K;
+  int tiles_m, tiles_n, k_blocks;
+  int epilogue;
+  const __nv_bfloat16* bias;   // [N] or nullptr
+  int* status;                 // global error word (nullptr: none)
+};
+
+__device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); }
+
+__device__ __forceinline__ void setup(Shared* sh, unsigned char* tiles, int warp, const CUtensorMap* ma, const CUtensorMap* mb) {
+  if (warp == 0 && sm100::elect_one()) {
+    sm100::tma_prefetch_desc(ma);
+    sm100::tma_prefetch_desc(mb);
+    for (int s = 0; s < STAGES; ++s) { sm100::mbar_init(&sh->full[s], 1); sm100::mbar_init(&sh->empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { sm100::mbar_init(&sh->acc_full[a], 1); sm100::mbar_init(&sh->acc_empty[a], 4); }
+    sh->error = 0;
+    sm100::fence_barrier_init();
+  }
+  if (warp == 1) {
+    sm100::tmem_alloc(&sh->tmem_base, TMEM_COLS);
+    sm100::tmem_relinquish();
+  }
+  sm100::tc_fence_before();
+  __syncthreads();
+  sm100::tc_fence_after();
+}
+
+__device__ __forceinline__ void fail(Shared* sh, const Problem& p, int where) {
+  atomicExch(&sh->error, where);
+  if (p.status) atomicCAS(p.status, 0, 1000 + where);
+}
+
+// ---- producer: TileOrder(tile_iter, &m_blk, &n_blk) -> bool;  AReady(m_blk) -> bool (bounded wait)
+template <typename TileOrder, typename AReady>
+__device__ __forceinline__ void producer(Shared* sh, unsigned char* tiles, const Problem& p, const CUtensorMap* ma,
+                                         const CUtensorMap* mb, TileOrder order, AReady a_ready) {
+  int stage = 0;
+  uint32_t phase = 0;
+  int m_blk, n_blk;
+  for (int it = 0; order(it, &m_blk, &n_blk); ++it) {
+    if (!a_ready(m_blk)) { fail(sh, p, 1); return; }
+    for (int kb = 0; kb < p.k_blocks; ++kb) {
+      if (!sm100::mbar_wait(&sh->empty[stage], phase ^ 1, kWaitBudgetNs) || sh->error) { fail(sh, p, 2); return; }
+      unsigned char* a_dst = tiles + (size_t)stage * STAGE_BYTES;
+      sm100::mbar_expect_tx(&sh->full[stage], STAGE_BYTES);
+      sm100::tma_load_2d(a_dst, ma, kb * BK, m_blk * BM, &sh->full[stage]);
+      sm100::tma_load_2d(a_dst + A_BYTES, mb, kb * BK, n_blk * BN, &sh->full[stage]);
+      if (++stage == STAGES) { stage = 0; phase ^= 1; }
+    }
+  }
+}
+
+template <typename TileOrder>
+__device__ __forceinline__ void mma_issuer(Shared* sh, unsigned char* tiles, const Problem& p, TileOrder order) {
+  constexpr uint32_t idesc = sm100::make_idesc_f16(BM, BN, true);
+  int stage = 0;
+  uint32_t phase = 0;
+  int m_blk, n_blk;
+  for (int it = 0; order(it, &m_blk, &n_blk); ++it) {
+    const int acc = it & 1;
+    const uint32_t acc_phase = (it >> 1) & 1;
+    if (!sm100::mbar_wait(&sh->acc_empty[acc], acc_phase ^ 1, kWaitBudgetNs) || sh->error) { fail(sh, p, 3); return; }
+    sm100::tc_fence_after();
+    const uint32_t d_tmem = sh->tmem_base + (uint32_t)acc * BN;
+    for (int kb = 0; kb < p.k_blocks; ++kb) {
+      if (!sm100::mbar_wait(&sh->full[stage], phase, kWaitBudgetNs) || sh->error) { fail(sh, p, 4); return; }
+      sm100::tc_fence_after();
+      const uint32_t a_addr = sm100::smem_u32(tiles + (size_t)stage * STAGE_BYTES);
+      const uint32_t b_addr = a_addr + A_BYTES;
+#pragma unroll
+      for (int k = 0; k < BK / UMMA_K; ++k) {
+        const uint64_t da = sm100::make_desc_sw128(a_addr + k * UMMA_K * 2);
+        const uint64_t db = sm100::make_desc_sw128(b_addr + k * UMMA_K * 2);
+        sm100::umma_f16(d_tmem, da, db, idesc, (kb | k) != 0);
+      }
+      sm100::umma_commit(&sh->empty[stage]);          // stage reusable once these MMAs have read it
+      if (++stage == STAGES) { stage = 0; phase ^= 1; }
+    }
+    sm100::umma_commit(&sh->acc_full[acc]);           // accumulator complete
+  }
+}
+
+// ---- epilogue: Dest(m_blk, row_in_tile, &ptr_to_row_start_of_C_in_columns_space) gives, for a global
+// row, the address of element (row, 0) of the destination matrix with leading dimension N; nullptr
+// skips the row.  quarter = warp % 4 selects the 32 accumulator lanes this warp may read.
+template <typename TileOrder, typename Dest>
+__device__ __forceinline__ void epilogue(Shared* sh, const Problem& p, int quarter, int lane, TileOrder order, Dest dest) {
+  int m_blk, n_blk;
+  for (int it = 0; order(it, &m_blk, &n_blk); ++it) {
+    const int acc = it & 1;
+    const uint32_t acc_phase = (it >> 1) & 1;
+    if (!sm100::mbar_wait(&sh->acc_full[acc], acc_phase, kWaitBudgetNs) || sh->error) { fail(sh, p, 5); return; }
+    sm100::tc_fence_after();
+    const int row = m_blk * BM + quarter * 32 + lane;
+    __nv_bfloat16* crow = row < p.M ? dest(m_blk, row) : nullptr;
+    const uint32_t t_base = sh->tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)acc * BN;
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += 32) {
+      uint32_t r[32];
+      sm100::tmem_ld_32x32(t_base + c0, r);
+      sm100::tmem_ld_wait();
+      const int col0 = n_blk * BN + c0;
+      if (crow && col0 < p.N) {
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        if (p.epilogue & EPI_BIAS) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) if (col0 + j < p.N) v[j] += __bfloat162float(p.bias[col0 + j]);
+        }
+        if (p.epilogue & EPI_GELU) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
+        }
+        __nv_bfloat16* dst = crow + col0;
+        if (col0 + 32 <= p.N && ((uintptr_t)dst & 15) == 0) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j], v[j + 1]), h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+            uint4 u;
+            u.x = *reinterpret_cast<uint32_t*>(&h0); u.y = *reinterpret_cast<uint32_t*>(&h1);
+            u.z = *reinterpret_cast<uint32_t*>(&h2); u.w = *reinterpret_cast<uint32_t*>(&h3);
+            *reinterpret_cast<uint4*>(dst + j) = u;
+          }
+        } else {
+          for (int j = 0; j < 32 && col0 + j < p.N; ++j) dst[j] = __float2bfloat16_rn(v[j]);
+        }
+      }
+    }
+    sm100::tc_fence_before();
+    __syncwarp();
+    if (lane == 0) sm100::mbar_arrive(&sh->acc_empty[acc]);   // four warps arrive: accumulator drained
+  }
+}
+
+// Frees the tensor memory after every role is done (all threads call).  When an error was raised
+// the CTA first waits, bounded, for its outstanding TMA copies (the full barriers) so that no copy
+// lands in shared memory after exit.
+__device__ __forceinline__ void teardown(Shared* sh, int warp) {
+  sm100::tc_fence_before();
+  __syncthreads();
+  if (sh->error && warp == 0 && sm100::elect_one()) {
+    const unsigned long long t0 = sm100::now_ns();
+    while (sm100::now_ns() - t0 < 200000000ull) { __nanosleep(1000); }   // copies in flight complete within microseconds
+  }
+  __syncthreads();
+  if (warp == 1) {
+    sm100::tc_fence_after();
+    sm100::tmem_dealloc(sh->tmem_base, TMEM_COLS);
+  }
+}
+
+// Carves the dynamic shared memory: 1024-byte aligned tile ring followed by the barrier block.
+__device__ __forceinline__ void carve(unsigned char* raw, unsigned char** tiles, Shared** sh) {
+  uintptr_t base = ((uintptr_t)raw + 1023) & ~(uintptr_t)1023;
+  *tiles = (unsigned char*)base;
+  *sh = (Shared*)(base + (size_t)STAGES * STAGE_BYTES);
+}
+
+}  // namespace gemm
+}  // namespace tmpi

@@ -43,7 +43,8 @@ Tunable g_tunables[] = {
   // ---- B200 data plane
   {"oneshot_max_bytes", {512 << 10}},      // <= : one-shot push allreduce
   {"nvls_min_bytes", {1 << 20}},           // >= : multimem allreduce when multicast is bound
-  {"comm_max_ctas", {32}},                 // CTAs of a collective kernel (leave SMs to compute)
+  {"comm_max_ctas", {64}},                 // CTAs of a stand-alone collective kernel
+  {"opt_max_ctas", {32}},                  // CTAs of the fused allreduce+SGD kernel (runs beside backward)
   {"comm_threads", {512}},
   {"num_comm_lanes", {2}},                 // ordered launch lanes (stream + flag set each)
   {"device_wait_budget_ms", {20000}},      // bounded spin of device flag waits

@@ -88,7 +88,7 @@ int tmpi_cuda_allreduce_sgd(const tmpi_sgd_bucket_t* b, const tmpi_group_t* g, i
   bool nvls = h.mc_base && N == h.world && N > 1 && tunable("use_nvls") && (algo == 3 || (algo == 0 &&
               b->n * es >= (size_t)tunable("nvls_min_bytes")));
   int threads = 512;
-  int grid = grid_for(b->n / V / N, threads);
+  int grid = grid_for(b->n / V / N, threads, "opt_max_ctas");
   std::lock_guard<std::mutex> lk(h.mu);
   auto fill = [&](int me, SgdArgs* a) -> int {
     memset(a, 0, sizeof(*a));

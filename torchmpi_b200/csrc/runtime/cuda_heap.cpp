@@ -87,8 +87,8 @@ void advance_epochs(const int* members, int n, int me, int lane, int barriers) {
   for (int i = 0; i < n; ++i) h.epoch[lane][mine][members[i]] += (uint32_t)barriers;
 }
 
-int grid_for(size_t items, int threads) {
-  int cap = (int)tunable("comm_max_ctas");
+int grid_for(size_t items, int threads, const char* cap_name) {
+  int cap = (int)tunable(cap_name);
   if (cap < 1) cap = 1;
   if (cap > kMaxBlocks) cap = kMaxBlocks;
   size_t want = (items + threads - 1) / threads;

@@ -59,7 +59,7 @@ int fill_peers(Peers* P, const int* members, int n, int me, int lane);
 // Advances the pair epochs of `lane` for these members by `barriers`.
 void advance_epochs(const int* members, int n, int me, int lane, int barriers);
 
-int grid_for(size_t work_items, int threads);
+int grid_for(size_t work_items, int threads, const char* cap_name = "comm_max_ctas");
 
 // VMM / multicast backend (cuda_vmm.cpp)
 int vmm_create(CudaHeap& h);

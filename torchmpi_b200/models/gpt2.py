@@ -1,0 +1,108 @@
+"""GPT-2 decoder (medium: 24 layers, d = 1024, 16 heads, context 1024, vocabulary 50257).
+
+Used by the hierarchical-training config: synchronous fused allreduce inside a group of GPUs, a
+GPU-resident parameter server across groups.  The reference has no sequence model
+(its largest network is a 6-layer Linear stack, test/async.lua:37-43).  Attention uses PyTorch's
+scaled-dot-product attention; the matrix products of the MLP and projections go through
+``ops.gemm.linear`` (the tcgen05 kernel) when ``tc_linear=True``; the loss is ``ops.xent``.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+
+@dataclass
+class GPT2Config:
+    n_layer: int = 24
+    n_head: int = 16
+    n_embd: int = 1024
+    block_size: int = 1024
+    vocab_size: int = 50257
+    tc_linear: bool = False
+
+
+def gpt2_medium(**kw) -> "GPT2":
+    return GPT2(GPT2Config(**kw))
+
+
+def gpt2_tiny(**kw) -> "GPT2":
+    cfg = dict(n_layer=2, n_head=4, n_embd=128, block_size=64, vocab_size=512)
+    cfg.update(kw)
+    return GPT2(GPT2Config(**cfg))
+
+
+class _Linear(nn.Linear):
+    def __init__(self, i, o, tc, gelu=False):
+        super().__init__(i, o)
+        self.tc, self.gelu = tc, gelu
+
+    def forward(self, x):
+        if self.tc:
+            from ..ops import gemm
+            return gemm.linear(x, self.weight, self.bias, self.gelu)
+        y = F.linear(x, self.weight, self.bias)
+        return F.gelu(y) if self.gelu else y
+
+
+class Block(nn.Module):
+    def __init__(self, c: GPT2Config):
+        super().__init__()
+        self.n_head = c.n_head
+        self.ln1 = nn.LayerNorm(c.n_embd)
+        self.qkv = _Linear(c.n_embd, 3 * c.n_embd, c.tc_linear)
+        self.proj = _Linear(c.n_embd, c.n_embd, c.tc_linear)
+        self.ln2 = nn.LayerNorm(c.n_embd)
+        self.fc = _Linear(c.n_embd, 4 * c.n_embd, c.tc_linear, gelu=True)
+        self.out = _Linear(4 * c.n_embd, c.n_embd, c.tc_linear)
+
+    def forward(self, x):
+        B, T, C = x.shape
+        q, k, v = self.qkv(self.ln1(x).to(x.dtype)).split(C, dim=2)
+        q, k, v = (t.view(B, T, self.n_head, C // self.n_head).transpose(1, 2) for t in (q, k, v))
+        a = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+        x = x + self.proj(a.transpose(1, 2).reshape(B, T, C))
+        return x + self.out(self.fc(self.ln2(x).to(x.dtype)))
+
+
+class GPT2(nn.Module):
+    def __init__(self, config: GPT2Config):
+        super().__init__()
+        self.config = c = config
+        self.wte = nn.Embedding(c.vocab_size, c.n_embd)
+        self.wpe = nn.Embedding(c.block_size, c.n_embd)
+        self.blocks = nn.ModuleList([Block(c) for _ in range(c.n_layer)])
+        self.ln_f = nn.LayerNorm(c.n_embd)
+        self.apply(self._init)
+        for b in self.blocks:   # scaled init of the residual projections
+            for lin in (b.proj, b.out):
+                nn.init.normal_(lin.weight, std=0.02 / math.sqrt(2 * c.n_layer))
+
+    @staticmethod
+    def _init(m):
+        if isinstance(m, (nn.Linear, nn.Embedding)):
+            nn.init.normal_(m.weight, std=0.02)
+            if isinstance(m, nn.Linear) and m.bias is not None:
+                nn.init.zeros_(m.bias)
+
+    def forward(self, idx: torch.Tensor) -> torch.Tensor:
+        """Token ids [B, T] -> logits [B*T, vocab] (the embedding matrix is tied to the output layer)."""
+        B, T = idx.shape
+        pos = torch.arange(T, device=idx.device)
+        x = self.wte(idx) + self.wpe(pos)
+        for b in self.blocks:
+            x = b(x)
+        x = self.ln_f(x).to(self.wte.weight.dtype)
+        return F.linear(x.view(B * T, -1), self.wte.weight)
+
+
+class LMLoss(nn.Module):
+    """Next-token cross-entropy over flattened logits; the fused kernel on CUDA."""
+
+    def forward(self, logits: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        from ..ops import xent
+        return xent.cross_entropy(logits, targets.reshape(-1))

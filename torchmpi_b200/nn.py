@@ -49,8 +49,6 @@ def synchronize_parameters(net, with_allreduce: bool = False) -> None:
     b, _ = collectives.runtime.collective_span()
     world = len(collectives.runtime.intra_members(b))   # the span's outer communicator
     for w in tensors:
-        if not w.is_contiguous():
-            raise ValueError("synchronize_parameters: parameters must be contiguous")
         if with_allreduce:
             collectives.allreduce_tensor(w, scale=1.0 / world)
         else:

@@ -1,0 +1,97 @@
+"""bf16 GEMM on tcgen05 tensor cores (csrc/kernels/gemm_tcgen05.cu) and a Linear layer built on it.
+
+``matmul_nt(a, b)`` computes ``a @ b.T`` for row-major ``a [M, K]`` and ``b [N, K]`` (K contiguous,
+bf16), optionally with bias and GELU in the epilogue.  ``linear(x, w, bias, gelu)`` is the autograd
+version: backward runs the same kernel on transposed copies (``dX = dY @ W`` as
+``matmul_nt(dY, W.T)``, ``dW = dY.T @ X`` as ``matmul_nt(dY.T, X.T)``).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .._lib import lib, check, has_symbol, stream_ptr, TorchMPIError
+
+EPI_NONE, EPI_BIAS, EPI_GELU = 0, 1, 2
+launch_count = 0
+
+
+def supported(a: torch.Tensor, b: torch.Tensor) -> bool:
+    return (a.is_cuda and b.is_cuda and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and
+            a.dim() == 2 and b.dim() == 2 and a.shape[1] == b.shape[1] and a.shape[1] % 8 == 0 and
+            has_symbol("tmpi_gemm_bf16"))
+
+
+def matmul_nt(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor] = None, gelu: bool = False,
+              out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``act(a @ b.T + bias)`` with fp32 accumulation; a: [M, K], b: [N, K], both bf16 and contiguous."""
+    global launch_count
+    if not has_symbol("tmpi_gemm_bf16"):
+        raise RuntimeError("torchmpi_b200: native kernel 'tmpi_gemm_bf16' is missing")
+    if not supported(a, b):
+        raise ValueError("matmul_nt expects bf16 CUDA matrices [M, K] and [N, K] with K a multiple of 8")
+    a, b = a.contiguous(), b.contiguous()
+    M, K = a.shape
+    N = b.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+    epi = (EPI_BIAS if bias is not None else 0) | (EPI_GELU if gelu else 0)
+    check(lib.tmpi_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(),
+                             bias.contiguous().data_ptr() if bias is not None else None, M, N, K, epi, stream_ptr()))
+    launch_count += 1
+    return out
+
+
+def check_status() -> None:
+    """Raises if a GEMM CTA gave up on one of its bounded waits since the last call."""
+    st = lib.tmpi_gemm_status()
+    if st:
+        raise TorchMPIError(3, f"tcgen05 GEMM: a bounded wait ran out (code {st})")
+
+
+class _LinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, bias, gelu):
+        x2 = x.reshape(-1, x.shape[-1])
+        if gelu:
+            z = matmul_nt(x2, w, bias)                       # pre-activation is needed by backward
+            y = torch.nn.functional.gelu(z)
+            ctx.save_for_backward(x2, w, z)
+        else:
+            y = matmul_nt(x2, w, bias)
+            ctx.save_for_backward(x2, w, None)
+        ctx.has_bias, ctx.gelu, ctx.shape = bias is not None, gelu, x.shape
+        return y.reshape(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w, z = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1]).contiguous()
+        if ctx.gelu:
+            dy2 = torch.ops.aten.gelu_backward(dy2, z)
+        dx = matmul_nt(dy2, w.t().contiguous()) if ctx.needs_input_grad[0] else None
+        dw = matmul_nt(dy2.t().contiguous(), x2.t().contiguous()) if ctx.needs_input_grad[1] else None
+        db = dy2.sum(0) if ctx.has_bias and ctx.needs_input_grad[2] else None
+        return (dx.reshape(ctx.shape) if dx is not None else None), dw, db, None
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, gelu: bool = False) -> torch.Tensor:
+    """``gelu?(x @ w.T + bias)`` through the tcgen05 kernel when the operands qualify, else PyTorch."""
+    rows = x.numel() // max(1, x.shape[-1])
+    if x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0 \
+            and w.shape[0] % 8 == 0 and rows % 8 == 0 and has_symbol("tmpi_gemm_bf16"):
+        return _LinearFn.apply(x, w, bias, gelu)
+    y = torch.nn.functional.linear(x, w, bias)
+    return torch.nn.functional.gelu(y) if gelu else y
+
+
+class Linear(torch.nn.Linear):
+    """``nn.Linear`` whose matrix products run on the hand-written tcgen05 kernel."""
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = True, gelu: bool = False, **kw):
+        super().__init__(in_features, out_features, bias=bias, **kw)
+        self.gelu = gelu
+
+    def forward(self, x):
+        return linear(x, self.weight, self.bias, self.gelu)

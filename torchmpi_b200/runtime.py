@@ -49,6 +49,7 @@ class State:
 
 
 S = State()
+plan_cache: dict = {}       # derived from communicators / span / tunables; cleared when any of them changes
 
 
 def _require_started() -> None:
@@ -140,6 +141,7 @@ def push_communicator(key: str) -> int:
     dist.all_gather_object(everyone, mine)
     _ensure_groups([g for pair in everyone for g in pair])
     S.num_communicators = lib.tmpi_comm_num_levels()
+    plan_cache.clear()
     return level
 
 
@@ -155,6 +157,7 @@ def communicator_level() -> int:
 def set_collective_span(begin: int, end: int) -> None:
     _require_started()
     check(lib.tmpi_comm_set_span(int(begin), int(end)))
+    plan_cache.clear()
 
 
 def collective_span() -> tuple:
@@ -173,10 +176,12 @@ def is_cartesian_communicator(level: int = -1) -> bool:
 
 def set_cartesian_communicator() -> None:
     check(lib.tmpi_set_tunable(b"use_cartesian_communicator", 1))
+    plan_cache.clear()
 
 
 def set_tree_communicator() -> None:
     check(lib.tmpi_set_tunable(b"use_cartesian_communicator", 0))
+    plan_cache.clear()
 
 
 def communicator_names() -> str:

@@ -84,6 +84,18 @@ def cases(small: bool):
 
     big = torch.randn((64 if small else 256) << 20, device=dev)
     out["absmean_var"] = (lambda: stats.absmean_var(big), big.numel() * 4)
+
+    from torchmpi_b200.ops import gemm
+    for name, (M, N, K) in {"gemm_bf16_8192": (8192, 8192, 8192), "gemm_bf16_tp_col": (8192, 4096, 8192),
+                            "gemm_bf16_tp_row": (8192, 8192, 4096)}.items():
+        if small and name != "gemm_bf16_tp_col":
+            continue
+        a = torch.randn(M, K, device=dev).to(torch.bfloat16)
+        b = torch.randn(N, K, device=dev).to(torch.bfloat16)
+        c = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        out[name] = (lambda a=a, b=b, c=c: gemm.matmul_nt(a, b, out=c), (M * K + N * K + M * N) * 2, 2.0 * M * N * K)
+        out[name + "_cublas"] = (lambda a=a, b=b, c=c: torch.matmul(a, b.t(), out=c), (M * K + N * K + M * N) * 2,
+                                 2.0 * M * N * K)
     return out
 
 
@@ -96,13 +108,20 @@ def main():
     torch.cuda.set_device(0)
     peak, how = peak_gbs()
     flush = torch.zeros(160 << 20, dtype=torch.uint8, device="cuda")
-    for name, (fn, nbytes) in cases(args.small).items():
-        if args.kernel not in ("all", name):
+    f = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    tf_peak = json.loads(f.read_text())["bf16_tflops"] if f.exists() else 1590.0
+    for name, case in cases(args.small).items():
+        if args.kernel != "all" and not name.startswith(args.kernel):
             continue
+        fn, nbytes = case[0], case[1]
         ms = time_kernel(fn, args.reps, flush)
         gbs = nbytes / ms / 1e6
-        print(json.dumps({"kernel": name, "bytes": nbytes, "ms": round(ms, 4), "gbs": round(gbs, 1),
-                          "frac_of_hbm_peak": round(gbs / peak, 3), "peak": how}))
+        row = {"kernel": name, "bytes": nbytes, "ms": round(ms, 4), "gbs": round(gbs, 1),
+               "frac_of_hbm_peak": round(gbs / peak, 3), "peak": how}
+        if len(case) > 2:
+            tf = case[2] / ms / 1e9
+            row.update({"tflops": round(tf, 1), "frac_of_bf16_burst_peak": round(tf / tf_peak, 3)})
+        print(json.dumps(row))
 
 
 if __name__ == "__main__":
