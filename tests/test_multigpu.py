@@ -303,8 +303,12 @@ def _tp_mlp(rank, world):
     assert torch.allclose(y.float(), h[sl], rtol=5e-2, atol=5e-2), (y.float() - h[sl]).abs().max()
     assert torch.allclose(xs.grad.float(), 2 * xr.grad[sl], rtol=5e-2, atol=5e-2)
     blk = model[0]
-    assert torch.allclose(blk.w1.grad.float(), 2 * p1[0].grad[rank * f:(rank + 1) * f], rtol=5e-2, atol=0.3)
-    assert torch.allclose(blk.w2.grad.float(), 2 * p2[0].grad[:, rank * f:(rank + 1) * f], rtol=5e-2, atol=0.3)
+
+    def rel(a, b):       # bf16 operands and a bf16 result: compare in the Frobenius norm
+        return ((a - b).norm() / b.norm()).item()
+    assert rel(blk.w1.grad.float(), 2 * p1[0].grad[rank * f:(rank + 1) * f]) < 0.02
+    assert rel(blk.w2.grad.float(), 2 * p2[0].grad[:, rank * f:(rank + 1) * f]) < 0.02
+    assert rel(model[1].w2.grad.float(), 2 * p2[1].grad[:, rank * f:(rank + 1) * f]) < 0.02
     mpi.stop()
     return True
 

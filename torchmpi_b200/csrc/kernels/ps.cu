@@ -1,13 +1,13 @@
 // One-sided parameter-server kernels: shards stay resident in GPU memory.
 //
-// The tensor of n elements is split into contiguous shards (floor(n/size) each,
-// the first n mod size ranks one more - lib/parameterserver.cpp:282-294); shard
-// i lives in the symmetric heap of member i at `shard_off`.  A push applies the
-// client's slice to every owner's shard directly over NVLink - plain stores for
-// `zero` and `copy`, atomic adds for `add`, which are exact under concurrency -
-// and a pull loads every shard into the client's tensor.  No server thread, no
-// host staging (the reference stages GPU tensors through pinned host memory and
-// MPI messages, torchmpi/parameterserver/init.lua:129-135,189-211).
+// The tensor of n elements is split into contiguous shards (floor(n/size) each, the first
+// n mod size ranks one more - lib/parameterserver.cpp:282-294); shard i lives in the symmetric heap
+// of member i at `shard_off`.  A push applies the client's slice to every owner's shard directly
+// over NVLink - plain stores for `zero` and `copy`, atomic adds (`red`) for `add`, which are exact
+// under concurrency - and a pull loads every shard into the client's tensor.  No server thread, no
+// host staging (the reference stages GPU tensors through pinned host memory and MPI messages,
+// torchmpi/parameterserver/init.lua:129-135,189-211).  Slices whose client-side address is
+// 16-byte aligned move as 16-byte packs (vector `red` for fp32 adds); the rest element by element.
 #include "collectives.cuh"
 #include "../include/tmpi_c_api.h"
 
@@ -24,9 +24,51 @@ template <> __device__ __forceinline__ void atomic_add_elem<long long>(long long
   atomicAdd(reinterpret_cast<unsigned long long*>(p), (unsigned long long)v);
 }
 
+// 16 bytes of additions in one reduction message where the type allows it
+template <typename T, int V>
+__device__ __forceinline__ void red_add_pack(T* p, const Pack<T, V>& x) {
+#pragma unroll
+  for (int k = 0; k < V; ++k) atomic_add_elem<T>(p + k, x.v[k]);
+}
+template <>
+__device__ __forceinline__ void red_add_pack<float, 4>(float* p, const Pack<float, 4>& x) {
+  asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1,%2,%3,%4};"
+               ::"l"(p), "f"(x.v[0]), "f"(x.v[1]), "f"(x.v[2]), "f"(x.v[3]) : "memory");
+}
+template <>
+__device__ __forceinline__ void red_add_pack<__nv_bfloat16, 8>(__nv_bfloat16* p, const Pack<__nv_bfloat16, 8>& x) {
+  const uint4 u = *reinterpret_cast<const uint4*>(&x);
+  asm volatile("red.relaxed.sys.global.add.noftz.v4.bf16x2 [%0], {%1,%2,%3,%4};"
+               ::"l"(p), "r"(u.x), "r"(u.y), "r"(u.z), "r"(u.w) : "memory");
+}
+template <>
+__device__ __forceinline__ void red_add_pack<__half, 8>(__half* p, const Pack<__half, 8>& x) {
+  const uint4 u = *reinterpret_cast<const uint4*>(&x);
+  asm volatile("red.relaxed.sys.global.add.noftz.v4.f16x2 [%0], {%1,%2,%3,%4};"
+               ::"l"(p), "r"(u.x), "r"(u.y), "r"(u.z), "r"(u.w) : "memory");
+}
+
+template <typename T, int V>
+__device__ __forceinline__ void ps_range(T* shard, T* data, size_t len, int rule, size_t t0, size_t stride) {
+  const size_t nv = len / V;
+  if (rule < 0) {
+    for (size_t i = t0; i < nv; i += stride) st_pack<T, V>(data + i * V, ld_pack_peer<T, V>(shard + i * V));
+  } else if (rule == 0) {
+    Pack<T, V> z;
+#pragma unroll
+    for (int k = 0; k < V; ++k) z.v[k] = from_acc<T>((typename AccOf<T>::type)0);
+    for (size_t i = t0; i < nv; i += stride) st_pack_peer<T, V>(shard + i * V, z);
+  } else if (rule == 1) {
+    for (size_t i = t0; i < nv; i += stride) st_pack_peer<T, V>(shard + i * V, ld_pack<T, V>(data + i * V));
+  } else {
+    for (size_t i = t0; i < nv; i += stride) red_add_pack<T, V>(shard + i * V, ld_pack<T, V>(data + i * V));
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(512) ps_kernel(const __grid_constant__ PsArgs a) {
   const Peers& P = a.P;
+  constexpr int V = 16 / sizeof(T);
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   const size_t t0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   T* data = reinterpret_cast<T*>(a.data);
@@ -34,16 +76,14 @@ __global__ void __launch_bounds__(512) ps_kernel(const __grid_constant__ PsArgs 
     const int m = (P.me + j) % P.n;          // start at my own shard: clients spread over owners
     size_t b, e;
     shard_range(a.n, P.n, m, &b, &e);
-    T* shard = at<T>(P.base[m], a.shard_off);
+    T* shard = at<T>(P.base[m], a.shard_off);   // 256-byte aligned
     const size_t len = e - b;
-    if (a.rule < 0) {
-      for (size_t i = t0; i < len; i += stride) data[b + i] = ld_pack_peer<T, 1>(shard + i).v[0];
-    } else if (a.rule == 0) {
-      for (size_t i = t0; i < len; i += stride) shard[i] = from_acc<T>((typename AccOf<T>::type)0);
-    } else if (a.rule == 1) {
-      for (size_t i = t0; i < len; i += stride) shard[i] = data[b + i];
+    if (((uintptr_t)(data + b) & 15) == 0) {
+      const size_t body = len / V * V;
+      ps_range<T, V>(shard, data + b, body, a.rule, t0, stride);
+      ps_range<T, 1>(shard + body, data + b + body, len - body, a.rule, t0, stride);
     } else {
-      for (size_t i = t0; i < len; i += stride) atomic_add_elem<T>(shard + i, data[b + i]);
+      ps_range<T, 1>(shard, data + b, len, a.rule, t0, stride);
     }
   }
   __threadfence_system();

@@ -39,7 +39,8 @@ static int pick_algo(int algo, size_t bytes, int dtype, const tmpi_group_t* g) {
   if (algo == 3 && !nvls_ok) algo = 2;
   if (algo != 0) return algo;
   if (bytes <= (size_t)tunable("oneshot_max_bytes") && bytes <= h.slot_bytes) return 1;
-  if (nvls_ok && bytes >= (size_t)tunable("nvls_min_bytes")) return 3;
+  // with two ranks the switch reduction moves more bytes per link than the peer-to-peer two-shot
+  if (nvls_ok && g->nmembers > 2 && bytes >= (size_t)tunable("nvls_min_bytes")) return 3;
   return 2;
 }
 

@@ -38,6 +38,7 @@ class Update:
         self.handles_send: List = []
         self.handles_prefetch: List = []
         self.debug = debug
+        self.on_parameters_changed = None    # optional callback after an integration changed the parameters
 
     def params(self) -> List[torch.Tensor]:
         blocks = mpinn._blocks(self.network)
@@ -97,4 +98,6 @@ class Update:
                     runtime.set_collective_span(b, e)
                 if self.debug:
                     mpinn.check_with_allreduce(self.network)
+        if need_broadcast and self.on_parameters_changed is not None:
+            self.on_parameters_changed()     # e.g. refresh fp32 master weights kept by a fused optimizer
         runtime.set_communicator(0)
