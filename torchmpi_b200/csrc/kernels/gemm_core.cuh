@@ -69,20 +69,24 @@ __device__ __forceinline__ void fail(Shared* sh, const Problem& p, int where) {
   if (p.status) atomicCAS(p.status, 0, 1000 + where);
 }
 
-// ---- producer: TileOrder(tile_iter, &m_blk, &n_blk) -> bool;  AReady(m_blk) -> bool (bounded wait)
-template <typename TileOrder, typename AReady>
+// ---- producer: TileOrder(tile_iter, &m_blk, &n_blk) -> bool;
+// ASource(m_blk, &map, &row0) -> bool picks the tensor map and first row of the A tile (and may wait,
+// bounded, until those rows are ready)
+template <typename TileOrder, typename ASource>
 __device__ __forceinline__ void producer(Shared* sh, unsigned char* tiles, const Problem& p, const CUtensorMap* ma,
-                                         const CUtensorMap* mb, TileOrder order, AReady a_ready) {
+                                         const CUtensorMap* mb, TileOrder order, ASource a_source) {
   int stage = 0;
   uint32_t phase = 0;
   int m_blk, n_blk;
   for (int it = 0; order(it, &m_blk, &n_blk); ++it) {
-    if (!a_ready(m_blk)) { fail(sh, p, 1); return; }
+    const CUtensorMap* a_map = ma;
+    int a_row0 = m_blk * BM;
+    if (!a_source(m_blk, &a_map, &a_row0)) { fail(sh, p, 1); return; }
     for (int kb = 0; kb < p.k_blocks; ++kb) {
       if (!sm100::mbar_wait(&sh->empty[stage], phase ^ 1, kWaitBudgetNs) || sh->error) { fail(sh, p, 2); return; }
       unsigned char* a_dst = tiles + (size_t)stage * STAGE_BYTES;
       sm100::mbar_expect_tx(&sh->full[stage], STAGE_BYTES);
-      sm100::tma_load_2d(a_dst, ma, kb * BK, m_blk * BM, &sh->full[stage]);
+      sm100::tma_load_2d(a_dst, a_map, kb * BK, a_row0, &sh->full[stage]);
       sm100::tma_load_2d(a_dst + A_BYTES, mb, kb * BK, n_blk * BN, &sh->full[stage]);
       if (++stage == STAGES) { stage = 0; phase ^= 1; }
     }

@@ -75,9 +75,9 @@ __device__ __forceinline__ void st_release_gpu(uint32_t* p, uint32_t v) {
 // The CTA's tiles (128 rows = tile_bytes contiguous bytes each, own shard first, then the peers in
 // ring order) are cut into 32 KB pieces numbered q = 0, 1, ...; piece q uses ring stage q % 6 and
 // mbarrier parity (q / 6) & 1.  Steady state of iteration k: piece k has landed -> start its store
-// -> wait until all stores but the two newest are complete -> publish the tiles they finish ->
-// start the load of piece k + 3 (its stage was last used by piece k - 3, whose store is complete).
-// Three loads (96 KB) and up to three stores are in flight per CTA.
+// -> wait until all stores but the newest are complete -> publish the tiles they finish ->
+// start the load of piece k + 4 (its stage was last used by piece k - 2, whose store is complete).
+// Four loads (128 KB) and up to two stores are in flight per CTA.
 __device__ void ag_comm(const FusedArgs& g, const Problem& p, unsigned char* tiles, Shared* sh, int* s_abort) {
   const Peers& P = g.P;
   const int R = P.n;
@@ -92,7 +92,8 @@ __device__ void ag_comm(const FusedArgs& g, const Problem& p, unsigned char* til
     uint64_t* bars = sh->full;                                   // full[0..3], empty[0..1]: six contiguous barriers
     auto src_of = [&](int q, const char** sp, char** dp, int* m_tile) {
       const int u = q / ppt, pi = q % ppt;
-      const int src = (P.me + u / cnt) % R, c = b + (u % cnt) * g.n_comm;
+      // peers in ring order first; my own shard last (the GEMM reads it in place, the copy only completes A_full)
+      const int src = (P.me + 1 + u / cnt) % R, c = b + (u % cnt) * g.n_comm;
       *m_tile = src * tiles_per_rank + c;
       *sp = P.base[src] + g.sym_off + (size_t)c * tile_bytes + (size_t)pi * COPY_BYTES;
       *dp = (char*)g.local + (size_t)(*m_tile) * tile_bytes + (size_t)pi * COPY_BYTES;
@@ -113,7 +114,7 @@ __device__ void ag_comm(const FusedArgs& g, const Problem& p, unsigned char* til
       st_release_gpu(&g.ready[mt], g.ready_value);
     };
     bool ok = true;
-    for (int q = 0; q < 3 && q < total; ++q) load(q);
+    for (int q = 0; q < 4 && q < total; ++q) load(q);
     for (int k = 0; k < total; ++k) {
       const int st = k % COPY_STAGES;
       if (!sm100::mbar_wait(&bars[st], (uint32_t)((k / COPY_STAGES) & 1), kWaitBudgetNs)) { ok = false; break; }
@@ -121,13 +122,12 @@ __device__ void ag_comm(const FusedArgs& g, const Problem& p, unsigned char* til
       src_of(k, &sp, &dp, &mt);
       bulk_store(dp, tiles + (size_t)st * COPY_BYTES, COPY_BYTES);
       bulk_commit();
-      asm volatile("cp.async.bulk.wait_group 2;" ::: "memory"); // stores of pieces <= k - 2 are complete
-      if (k >= 2) publish(k - 2);
-      if (k + 3 < total) load(k + 3);
+      asm volatile("cp.async.bulk.wait_group 1;" ::: "memory"); // stores of pieces <= k - 1 are complete
+      if (k >= 1) publish(k - 1);
+      if (k + 4 < total) load(k + 4);                           // its stage was last used by piece k - 2
     }
     bulk_wait_all();
     if (ok) {
-      if (total >= 2) publish(total - 2);
       publish(total - 1);
     } else {
       fail(sh, p, 10);
@@ -138,8 +138,9 @@ __device__ void ag_comm(const FusedArgs& g, const Problem& p, unsigned char* til
 }
 
 __global__ void __launch_bounds__(THREADS, 1)
-ag_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               __nv_bfloat16* __restrict__ C, const Problem p, const __grid_constant__ FusedArgs g) {
+ag_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_own,
+               const __grid_constant__ CUtensorMap map_b, __nv_bfloat16* __restrict__ C, const Problem p,
+               const __grid_constant__ FusedArgs g) {
   extern __shared__ unsigned char smem_raw[];
   __shared__ int s_abort;
   unsigned char* tiles;
@@ -174,7 +175,12 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   };
   if (warp == 0) {
     if (sm100::elect_one()) {
-      producer(sh, tiles, p, &map_a, &map_b, order, [&](int m_blk) {
+      producer(sh, tiles, p, &map_a, &map_b, order, [&](int m_blk, const CUtensorMap** amap, int* row0) {
+        if (m_blk >= rot && m_blk < rot + tiles_per_rank) {      // my own rows: read the shard where it lies
+          *amap = &map_own;
+          *row0 = (m_blk - rot) * BM;
+          return true;
+        }
         const unsigned long long t0 = sm100::now_ns();
         while (ld_acquire_gpu(&g.ready[m_blk]) != g.ready_value) {
           __nanosleep(200);
@@ -220,7 +226,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   };
   const size_t slot_elems = (size_t)g.rows_per_rank * p.N;
   if (warp == 0) {
-    if (sm100::elect_one()) producer(sh, tiles, p, &map_a, &map_b, order, [](int) { return true; });
+    if (sm100::elect_one()) producer(sh, tiles, p, &map_a, &map_b, order, [](int, const CUtensorMap**, int*) { return true; });
   } else if (warp == 1) {
     if (sm100::elect_one()) mma_issuer(sh, tiles, p, order);
   } else {
@@ -340,6 +346,8 @@ int tmpi_cuda_ag_gemm(size_t a_shard_off, size_t a_full_off, const void* B, void
   CUtensorMap ma, mb;
   if ((st = make_tmap_bf16(&ma, a_full, (uint64_t)M, (uint64_t)K, (uint64_t)K, gemm::BM))) return st;
   if ((st = make_tmap_bf16(&mb, B, (uint64_t)N, (uint64_t)K, (uint64_t)K, gemm::BN))) return st;
+  CUtensorMap mown;
+  if ((st = make_tmap_bf16(&mown, h.base[h.rank] + a_shard_off, (uint64_t)(M / R), (uint64_t)K, (uint64_t)K, gemm::BM))) return st;
   int sms = gemm_sm_count();
   if (n_comm <= 0) n_comm = 8;
   if (n_comm > sms / 4) n_comm = sms / 4;
@@ -349,7 +357,7 @@ int tmpi_cuda_ag_gemm(size_t a_shard_off, size_t a_full_off, const void* B, void
   std::call_once(once, [] {
     cudaFuncSetAttribute(gemm::ag_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gemm::SMEM_BYTES);
   });
-  gemm::ag_gemm_kernel<<<sms, gemm::THREADS, gemm::SMEM_BYTES, (cudaStream_t)stream>>>(ma, mb, (__nv_bfloat16*)C, p, fa);
+  gemm::ag_gemm_kernel<<<sms, gemm::THREADS, gemm::SMEM_BYTES, (cudaStream_t)stream>>>(ma, mown, mb, (__nv_bfloat16*)C, p, fa);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "ag_gemm launch");
   std::lock_guard<std::mutex> hk(h.mu);

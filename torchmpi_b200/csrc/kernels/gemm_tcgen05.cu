@@ -45,7 +45,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     return true;
   };
   if (warp == 0) {
-    if (sm100::elect_one()) producer(sh, tiles, p, &map_a, &map_b, order, [](int) { return true; });
+    if (sm100::elect_one()) producer(sh, tiles, p, &map_a, &map_b, order, [](int, const CUtensorMap**, int*) { return true; });
   } else if (warp == 1) {
     if (sm100::elect_one()) mma_issuer(sh, tiles, p, order);
   } else {

@@ -52,7 +52,17 @@ template <typename T, int V>
 __device__ __forceinline__ void ps_range(T* shard, T* data, size_t len, int rule, size_t t0, size_t stride) {
   const size_t nv = len / V;
   if (rule < 0) {
-    for (size_t i = t0; i < nv; i += stride) st_pack<T, V>(data + i * V, ld_pack_peer<T, V>(shard + i * V));
+    // pulls are remote loads: keep eight of them in flight per thread
+    constexpr int U = 8;
+    size_t i = t0;
+    for (; i + (U - 1) * stride < nv; i += U * stride) {
+      Pack<T, V> x[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) x[u] = ld_pack_peer<T, V>(shard + (i + u * stride) * V);
+#pragma unroll
+      for (int u = 0; u < U; ++u) st_pack<T, V>(data + (i + u * stride) * V, x[u]);
+    }
+    for (; i < nv; i += stride) st_pack<T, V>(data + i * V, ld_pack_peer<T, V>(shard + i * V));
   } else if (rule == 0) {
     Pack<T, V> z;
 #pragma unroll

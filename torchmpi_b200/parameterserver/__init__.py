@@ -155,7 +155,9 @@ def init_tensors(tensors: Sequence[torch.Tensor], prefetch_allocator: Optional[C
     for t in tensors:
         if cache.key(t) in cache.parameter_servers:
             continue
-        pre = prefetch_allocator(t) if prefetch_allocator else torch.empty_like(t)
+        # the prefetch clone starts as a copy of the tensor: the first integration may come before
+        # the first prefetch (update.lua: integrate at delay + f, prefetch at delay + f + prefetch)
+        pre = prefetch_allocator(t) if prefetch_allocator else t.detach().clone()
         cache.prefetch_tensor_references[cache.key(t)] = pre
         ps = init(t)
         cache.parameter_servers[cache.key(t)] = (t, ps)
