@@ -25,7 +25,8 @@ constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int THREADS = 192;
 constexpr int TMEM_COLS = 512;
-constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int EPI_STAGING_BYTES = 2 * BM * 64 * 2;           // two 128 x 64 bf16 staging tiles for TMA stores
+constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + EPI_STAGING_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 constexpr unsigned long long kWaitBudgetNs = 4000000000ull;   // 4 s: far beyond any legitimate wait
 
 enum { EPI_NONE = 0, EPI_BIAS = 1, EPI_GELU = 2, EPI_BIAS_GELU = 3 };
@@ -41,6 +42,7 @@ struct Problem {
   int tiles_m, tiles_n, k_blocks;
   int epilogue;
   const __nv_bfloat16* bias;   // [N] or nullptr
+  int tma_store;               // epilogue writes through TMA (needs 16-byte aligned rows of C)
   int* status;                 // global error word (nullptr: none)
 };
 
@@ -177,6 +179,97 @@ __device__ __forceinline__ void epilogue(Shared* sh, const Problem& p, int quart
   }
 }
 
+// ---- epilogue with TMA stores.  The four epilogue warps convert 64-column slices of the accumulator
+// to bf16 into a 128-byte-swizzled staging tile (two of them, 16 KB each) and one thread hands each
+// slice to the TMA engine, which writes full 128-byte rows - to local memory or straight into a
+// peer's memory - while the warps already convert the next slice.  Direct stores from the
+// accumulator layout would issue 32 separate 16-byte writes per warp instruction.
+// DestMap(m_blk, &map, &row0) picks the destination tensor map (box 64 columns x 128 rows) and the
+// first row inside it.  Rows and columns beyond the tensor are clipped by the TMA unit.
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(sm100::smem_u32(smem_src)), "r"(c0), "r"(c1) : "memory");
+}
+
+template <typename TileOrder, typename DestMap>
+__device__ __forceinline__ void epilogue_tma(Shared* sh, unsigned char* staging, const Problem& p, int quarter, int lane,
+                                             TileOrder order, DestMap dest) {
+  constexpr int SLICE = 64, SLICE_BYTES = BM * SLICE * 2;
+  const int r_in_tile = quarter * 32 + lane;
+  const bool leader = quarter == 2 && lane == 0;      // warp 2 of the CTA holds quarter 2
+  int m_blk, n_blk;
+  int slice_no = 0;
+  for (int it = 0; order(it, &m_blk, &n_blk); ++it) {
+    const int acc = it & 1;
+    const uint32_t acc_phase = (it >> 1) & 1;
+    // the 128 epilogue threads meet at named barriers below, so they must agree on going on:
+    // vote (every thread gets here, its wait being bounded) and leave together on a failure
+    const uint32_t ok = sm100::mbar_wait(&sh->acc_full[acc], acc_phase, kWaitBudgetNs) && !sh->error;
+    uint32_t all_ok;
+    asm volatile("{\n .reg .pred p, q;\n setp.ne.b32 p, %1, 0;\n barrier.cta.red.and.pred q, 1, 128, p;\n selp.u32 %0, 1, 0, q;\n}\n"
+                 : "=r"(all_ok) : "r"(ok) : "memory");
+    if (!all_ok) { fail(sh, p, 5); break; }
+    sm100::tc_fence_after();
+    const CUtensorMap* cmap = nullptr;
+    int row0 = 0;
+    dest(m_blk, &cmap, &row0);
+    const uint32_t t_base = sh->tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)acc * BN;
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += SLICE, ++slice_no) {
+      const int col0 = n_blk * BN + c0;
+      unsigned char* stg = staging + (size_t)(slice_no & 1) * SLICE_BYTES;
+      uint32_t r[2][32];
+      sm100::tmem_ld_32x32(t_base + c0, r[0]);
+      sm100::tmem_ld_32x32(t_base + c0 + 32, r[1]);
+      sm100::tmem_ld_wait();
+      // the store that used this staging buffer two slices ago must have read it
+      if (leader) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+      epi_bar_sync();
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[h][j]);
+        if (p.epilogue & EPI_BIAS) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int c = col0 + h * 32 + j;
+            if (c < p.N) v[j] += __bfloat162float(p.bias[c]);
+          }
+        }
+        if (p.epilogue & EPI_GELU) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+          __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j], v[j + 1]), h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+          __nv_bfloat162 h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+          uint4 u;
+          u.x = *reinterpret_cast<uint32_t*>(&h0); u.y = *reinterpret_cast<uint32_t*>(&h1);
+          u.z = *reinterpret_cast<uint32_t*>(&h2); u.w = *reinterpret_cast<uint32_t*>(&h3);
+          const int chunk = h * 4 + j / 8;                               // 16-byte chunk inside the 128-byte row
+          *reinterpret_cast<uint4*>(stg + (size_t)r_in_tile * 128 + ((chunk ^ (r_in_tile & 7)) << 4)) = u;
+        }
+      }
+      sm100::fence_proxy_async();        // generic-proxy writes to shared memory -> visible to the TMA unit
+      epi_bar_sync();
+      if (leader && col0 < p.N) {
+        tma_store_2d(cmap, stg, col0, row0);
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+      }
+    }
+    sm100::tc_fence_before();
+    __syncwarp();
+    if (lane == 0) sm100::mbar_arrive(&sh->acc_empty[acc]);   // four warps arrive: accumulator drained
+  }
+  if (leader) {
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // all stores complete before exit
+    sm100::fence_proxy_async();
+  }
+}
+
 // Frees the tensor memory after every role is done (all threads call).  When an error was raised
 // the CTA first waits, bounded, for its outstanding TMA copies (the full barriers) so that no copy
 // lands in shared memory after exit.
@@ -194,11 +287,12 @@ __device__ __forceinline__ void teardown(Shared* sh, int warp) {
   }
 }
 
-// Carves the dynamic shared memory: 1024-byte aligned tile ring followed by the barrier block.
-__device__ __forceinline__ void carve(unsigned char* raw, unsigned char** tiles, Shared** sh) {
+// Carves the dynamic shared memory: 1024-byte aligned tile ring, the epilogue staging tiles, the barrier block.
+__device__ __forceinline__ void carve(unsigned char* raw, unsigned char** tiles, Shared** sh, unsigned char** staging = nullptr) {
   uintptr_t base = ((uintptr_t)raw + 1023) & ~(uintptr_t)1023;
   *tiles = (unsigned char*)base;
-  *sh = (Shared*)(base + (size_t)STAGES * STAGE_BYTES);
+  if (staging) *staging = (unsigned char*)(base + (size_t)STAGES * STAGE_BYTES);
+  *sh = (Shared*)(base + (size_t)STAGES * STAGE_BYTES + EPI_STAGING_BYTES);
 }
 
 }  // namespace gemm

@@ -25,6 +25,7 @@
 #include "../include/tmpi_c_api.h"
 #include "../runtime/common.h"
 #include "../runtime/cuda_state.h"
+#include <cstring>
 #include <mutex>
 
 namespace tmpi {
@@ -139,13 +140,13 @@ __device__ void ag_comm(const FusedArgs& g, const Problem& p, unsigned char* til
 
 __global__ void __launch_bounds__(THREADS, 1)
 ag_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_own,
-               const __grid_constant__ CUtensorMap map_b, __nv_bfloat16* __restrict__ C, const Problem p,
-               const __grid_constant__ FusedArgs g) {
+               const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c,
+               __nv_bfloat16* __restrict__ C, const Problem p, const __grid_constant__ FusedArgs g) {
   extern __shared__ unsigned char smem_raw[];
   __shared__ int s_abort;
-  unsigned char* tiles;
+  unsigned char *tiles, *staging;
   Shared* sh;
-  carve(smem_raw, &tiles, &sh);
+  carve(smem_raw, &tiles, &sh, &staging);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) s_abort = 0;
   if ((int)blockIdx.x < g.n_comm) {
@@ -193,20 +194,23 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   } else if (warp == 1) {
     if (sm100::elect_one()) mma_issuer(sh, tiles, p, order);
   } else {
-    epilogue(sh, p, warp & 3, lane, order, [&](int, int row) { return C + (size_t)row * p.N; });
+    epilogue_tma(sh, staging, p, warp & 3, lane, order,
+                 [&](int m_blk, const CUtensorMap** m, int* row0) { *m = &map_c; *row0 = m_blk * BM; });
   }
   teardown(sh, warp);
 }
 
 // ------------------------------------------------------------------ GEMM -> reduce-scatter
+struct SlotMaps { CUtensorMap m[8]; };   // destination slot (mine) inside every owner's memory
+
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_rs_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               const Problem p, const __grid_constant__ FusedArgs g) {
+               const __grid_constant__ SlotMaps slot_maps, const Problem p, const __grid_constant__ FusedArgs g) {
   extern __shared__ unsigned char smem_raw[];
   __shared__ int s_abort;
-  unsigned char* tiles;
+  unsigned char *tiles, *staging;
   Shared* sh;
-  carve(smem_raw, &tiles, &sh);
+  carve(smem_raw, &tiles, &sh, &staging);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) s_abort = 0;
   setup(sh, tiles, warp, &map_a, &map_b);
@@ -230,10 +234,11 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   } else if (warp == 1) {
     if (sm100::elect_one()) mma_issuer(sh, tiles, p, order);
   } else {
-    epilogue(sh, p, warp & 3, lane, order, [&](int, int row) {
-      const int owner = row / g.rows_per_rank;
-      __nv_bfloat16* slots = reinterpret_cast<__nv_bfloat16*>(P.base[owner] + g.sym_off);
-      return slots + (size_t)P.me * slot_elems + (size_t)(row - owner * g.rows_per_rank) * p.N;
+    // the tile goes straight into my slot inside the owner's memory (TMA store over NVLink for peers)
+    epilogue_tma(sh, staging, p, warp & 3, lane, order, [&](int m_blk, const CUtensorMap** m, int* row0) {
+      const int owner = m_blk / tiles_per_rank;
+      *m = &slot_maps.m[owner];
+      *row0 = (m_blk - owner * tiles_per_rank) * BM;
     });
   }
   // all tiles of this CTA are stored; make them visible system-wide, then meet the rest of the grid
@@ -346,6 +351,8 @@ int tmpi_cuda_ag_gemm(size_t a_shard_off, size_t a_full_off, const void* B, void
   CUtensorMap ma, mb;
   if ((st = make_tmap_bf16(&ma, a_full, (uint64_t)M, (uint64_t)K, (uint64_t)K, gemm::BM))) return st;
   if ((st = make_tmap_bf16(&mb, B, (uint64_t)N, (uint64_t)K, (uint64_t)K, gemm::BN))) return st;
+  CUtensorMap mc;
+  if ((st = make_tmap_bf16(&mc, C, (uint64_t)M, (uint64_t)N, (uint64_t)N, gemm::BM))) return st;
   CUtensorMap mown;
   if ((st = make_tmap_bf16(&mown, h.base[h.rank] + a_shard_off, (uint64_t)(M / R), (uint64_t)K, (uint64_t)K, gemm::BM))) return st;
   int sms = gemm_sm_count();
@@ -357,7 +364,7 @@ int tmpi_cuda_ag_gemm(size_t a_shard_off, size_t a_full_off, const void* B, void
   std::call_once(once, [] {
     cudaFuncSetAttribute(gemm::ag_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gemm::SMEM_BYTES);
   });
-  gemm::ag_gemm_kernel<<<sms, gemm::THREADS, gemm::SMEM_BYTES, (cudaStream_t)stream>>>(ma, mown, mb, (__nv_bfloat16*)C, p, fa);
+  gemm::ag_gemm_kernel<<<sms, gemm::THREADS, gemm::SMEM_BYTES, (cudaStream_t)stream>>>(ma, mown, mb, mc, (__nv_bfloat16*)C, p, fa);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "ag_gemm launch");
   std::lock_guard<std::mutex> hk(h.mu);
@@ -390,6 +397,14 @@ int tmpi_cuda_gemm_rs(const void* A, const void* B, size_t slots_off, void* out,
   CUtensorMap ma, mb;
   if ((st = make_tmap_bf16(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)K, gemm::BM))) return st;
   if ((st = make_tmap_bf16(&mb, B, (uint64_t)N, (uint64_t)K, (uint64_t)K, gemm::BN))) return st;
+  if (R > 8) return fail(TMPI_ERR_UNSUPPORTED, "gemm_rs supports at most 8 ranks");
+  gemm::SlotMaps sm;
+  memset(&sm, 0, sizeof(sm));
+  const size_t slot_bytes = (size_t)(M / R) * N * 2;
+  for (int o = 0; o < R; ++o) {
+    char* slot = fa.P.base[o] + slots_off + (size_t)grp->me * slot_bytes;
+    if ((st = make_tmap_bf16(&sm.m[o], slot, (uint64_t)(M / R), (uint64_t)N, (uint64_t)N, gemm::BM))) return st;
+  }
   int grid = std::min(gemm_sm_count(), p.tiles_m * p.tiles_n);
   fa.sym_off = slots_off; fa.local = (__nv_bfloat16*)out; fa.rows_per_rank = M / R;
   fa.grid_counter = ws->grid_counter;
@@ -399,7 +414,7 @@ int tmpi_cuda_gemm_rs(const void* A, const void* B, size_t slots_off, void* out,
   std::call_once(once, [] {
     cudaFuncSetAttribute(gemm::gemm_rs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gemm::SMEM_BYTES);
   });
-  gemm::gemm_rs_kernel<<<grid, gemm::THREADS, gemm::SMEM_BYTES, (cudaStream_t)stream>>>(ma, mb, p, fa);
+  gemm::gemm_rs_kernel<<<grid, gemm::THREADS, gemm::SMEM_BYTES, (cudaStream_t)stream>>>(ma, mb, sm, p, fa);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "gemm_rs launch");
   std::lock_guard<std::mutex> hk(h.mu);

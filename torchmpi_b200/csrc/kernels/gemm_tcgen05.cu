@@ -9,6 +9,7 @@
 #include "gemm_core.cuh"
 #include "../include/tmpi_c_api.h"
 #include "../runtime/common.h"
+#include <cstring>
 #include <mutex>
 
 namespace tmpi {
@@ -29,11 +30,11 @@ __device__ __forceinline__ void band_order(int t, int tiles_m, int tiles_n, int*
 
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                 __nv_bfloat16* __restrict__ C, const Problem p) {
+                 const __grid_constant__ CUtensorMap map_c, __nv_bfloat16* __restrict__ C, const Problem p) {
   extern __shared__ unsigned char smem_raw[];
-  unsigned char* tiles;
+  unsigned char *tiles, *staging;
   Shared* sh;
-  carve(smem_raw, &tiles, &sh);
+  carve(smem_raw, &tiles, &sh, &staging);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   setup(sh, tiles, warp, &map_a, &map_b);
 
@@ -48,6 +49,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     if (sm100::elect_one()) producer(sh, tiles, p, &map_a, &map_b, order, [](int, const CUtensorMap**, int*) { return true; });
   } else if (warp == 1) {
     if (sm100::elect_one()) mma_issuer(sh, tiles, p, order);
+  } else if (p.tma_store) {
+    epilogue_tma(sh, staging, p, warp & 3, lane, order,
+                 [&](int m_blk, const CUtensorMap** m, int* row0) { *m = &map_c; *row0 = m_blk * BM; });
   } else {
     epilogue(sh, p, warp & 3, lane, order,
              [&](int, int row) { return C + (size_t)row * p.N; });
@@ -140,12 +144,16 @@ int tmpi_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int 
   p.epilogue = epilogue;
   p.bias = (const __nv_bfloat16*)bias;
   p.status = gemm_status_word();
+  CUtensorMap mc;
+  memset(&mc, 0, sizeof(mc));
+  p.tma_store = (N % 8 == 0 && ((uintptr_t)C & 15) == 0) ? 1 : 0;
+  if (p.tma_store && (st = make_tmap_bf16(&mc, C, (uint64_t)M, (uint64_t)N, (uint64_t)N, gemm::BM))) return st;
   static std::once_flag attr_once;
   std::call_once(attr_once, [] {
     cudaFuncSetAttribute(gemm::gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gemm::SMEM_BYTES);
   });
   int grid = std::min(p.tiles_m * p.tiles_n, gemm_sm_count());
-  gemm::gemm_bf16_kernel<<<grid, gemm::THREADS, gemm::SMEM_BYTES, (cudaStream_t)stream>>>(ma, mb, (__nv_bfloat16*)C, p);
+  gemm::gemm_bf16_kernel<<<grid, gemm::THREADS, gemm::SMEM_BYTES, (cudaStream_t)stream>>>(ma, mb, mc, (__nv_bfloat16*)C, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? TMPI_OK : fail(TMPI_ERR_CUDA, "gemm launch: %s", cudaGetErrorString(e));
 }
