@@ -128,12 +128,14 @@ class _TPMLPFn(torch.autograd.Function):
         dy_shard = dy_shard.contiguous()
         dh = tp.ag_gemm(dy_shard, tp.dfull_off, tp.dfull_buf, w2.t().contiguous(), None)     # [M, F/R]
         dy_full = tp.dfull_buf[:tp.M * tp.d].view(tp.M, tp.d)
-        dw2 = gemm.matmul_nt(dy_full.t().contiguous(), h.t().contiguous())                    # [D, F/R]
-        db2 = dy_full.float().sum(0).to(dy_full.dtype) if ctx.has_b2 else None
+        # the two weight gradients are plain local GEMMs on operands whose contraction dimension is the
+        # slow one: the library GEMM takes them as they lie, without materialising transposes
+        dw2 = torch.matmul(dy_full.t(), h)                                                    # [D, F/R]
+        db2 = dy_full.sum(0, dtype=torch.float32).to(dy_full.dtype) if ctx.has_b2 else None
         dz = torch.ops.aten.gelu_backward(dh, z)
         dx = tp.gemm_rs(dz, w1.t().contiguous())                                              # [rows, D]
-        dw1 = gemm.matmul_nt(dz.t().contiguous(), x_full.t().contiguous())                    # [F/R, D]
-        db1 = dz.float().sum(0).to(dz.dtype) if ctx.has_b1 else None
+        dw1 = torch.matmul(dz.t(), x_full)                                                    # [F/R, D]
+        db1 = dz.sum(0, dtype=torch.float32).to(dz.dtype) if ctx.has_b1 else None
         return dx, dw1, db1, dw2, db2, None, None, None
 
 
