@@ -27,6 +27,7 @@ from . import _lib, config, runtime
 from ._lib import lib, check, dtype_code
 from .handles import Handle
 from .runtime import S
+from .utils import trace as _trace
 
 ALGOS = {"auto": 0, "oneshot": 1, "twoshot": 2, "nvls": 3, "ring": 4}
 
@@ -226,7 +227,10 @@ def allreduce_tensor(inp: torch.Tensor, out: Optional[torch.Tensor] = None, *, s
     a = ALGOS[algo] if isinstance(algo, str) else int(algo)
     plan = _span_plan()
     if plan[0] == "flat":
-        return _flat_allreduce(inp, out, plan[1], backend, scale, a, async_op)
+        if async_op or not _trace.enabled():
+            return _flat_allreduce(inp, out, plan[1], backend, scale, a, async_op)
+        with _trace.timed("allreduce", str(algo), inp.numel() * inp.element_size(), inp.is_cuda):
+            return _flat_allreduce(inp, out, plan[1], backend, scale, a, False)
     _, inner, inter, cartesian = plan
     # staged composition; the stages depend on each other, so an async caller gets a completed handle
     _wait(_flat_allreduce(inp, out, inner, backend, 1.0, a, False))
@@ -244,7 +248,10 @@ def broadcast_tensor(root: int, t: torch.Tensor, *, backend: Optional[str] = Non
     runtime._require_started()
     t = _check_tensor(t)
     b, _ = runtime.collective_span()
-    return _flat_broadcast(t, int(root), runtime.intra_members(b), backend, async_op)
+    if async_op or not _trace.enabled():
+        return _flat_broadcast(t, int(root), runtime.intra_members(b), backend, async_op)
+    with _trace.timed("broadcast", "auto", t.numel() * t.element_size(), t.is_cuda):
+        return _flat_broadcast(t, int(root), runtime.intra_members(b), backend, False)
 
 
 def reduce_tensor(root: int, inp: torch.Tensor, out: Optional[torch.Tensor] = None, *,
