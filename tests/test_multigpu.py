@@ -70,6 +70,22 @@ def _collectives(rank, world, backend):
             mpi.p2p.allreduce_tensor(y, algo=algo, scale=0.25)
             assert torch.allclose(y.float(), ref.float() * 0.25, atol=tol * n, rtol=tol), (dt, algo)
             _gather_equal(mpi, y)
+    # larger than the scratch region (several launches), and pointers whose alignment differs by rank
+    big = torch.full((45_000_003,), float(rank + 1), device=dev)
+    mpi.p2p.allreduce_tensor(big)
+    assert torch.all(big == n * (n + 1) / 2)
+    big.fill_(float(rank))
+    mpi.p2p.broadcast_tensor(0, big)
+    assert torch.all(big == 0)
+    del big
+    store = torch.full((100_004,), float(rank), device=dev)
+    odd = store[rank % 2:][:100_000]
+    mpi.p2p.allreduce_tensor(odd)
+    assert torch.all(odd == n * (n - 1) / 2)
+    odd.fill_(float(rank))
+    mpi.p2p.broadcast_tensor(n - 1, odd)
+    assert torch.all(odd == n - 1)
+    heap.check_status(0)
     # tensors living in the symmetric heap take the zero-copy path
     sym = heap.empty(1 << 20, torch.bfloat16)
     sym.fill_(rank + 1)

@@ -13,11 +13,13 @@ template <int OP, typename T, int V>
 __device__ __forceinline__ void run_body(const CollArgs& a, int* s_abort) {
   if constexpr (OP == OP_AR_ONESHOT) body_ar_oneshot<T, V>(a, s_abort);
   else if constexpr (OP == OP_AR_TWOSHOT) body_ar_twoshot<T, V>(a, s_abort);
+  else if constexpr (OP == OP_AR_TWOSHOT_ANY) body_ar_twoshot_any<T, V>(a, s_abort);
   else if constexpr (OP == OP_AR_NVLS) body_ar_nvls<T, V>(a, s_abort);
   else if constexpr (OP == OP_AR_RING) body_ar_ring<T, V>(a, s_abort);
   else if constexpr (OP == OP_BCAST_PULL) body_bcast_pull<T, V>(a, s_abort);
   else if constexpr (OP == OP_BCAST_CHUNKED) body_bcast_chunked<T, V>(a, s_abort);
   else if constexpr (OP == OP_BCAST_MC) body_bcast_mc<T, V>(a, s_abort);
+  else if constexpr (OP == OP_BCAST_ANY) body_bcast_any<T, V>(a, s_abort);
   else if constexpr (OP == OP_REDUCE) body_reduce<T, V>(a, s_abort);
   else if constexpr (OP == OP_ALLGATHER) body_allgather<T, V>(a, s_abort);
   else if constexpr (OP == OP_REDUCE_SCATTER) body_reduce_scatter<T, V>(a, s_abort);
@@ -46,6 +48,7 @@ int barriers_used(int op, int n) {
     case OP_AR_ONESHOT: return 1;
     case OP_AR_RING: return 1 + 2 * (n - 1);
     case OP_BCAST_CHUNKED: return 3;
+    case OP_AR_TWOSHOT_ANY: return 3;
     case OP_BARRIER: return 1;
     default: return 2;
   }
@@ -111,6 +114,7 @@ cudaError_t launch_collective(int op, int dtype, const CollArgs* args, int nrank
     case OP_AR_ONESHOT: return launch_reduction<OP_AR_ONESHOT>(dtype, args, nranks, vec, grid, threads, s);
     case OP_AR_TWOSHOT: return launch_reduction<OP_AR_TWOSHOT>(dtype, args, nranks, vec, grid, threads, s);
     case OP_AR_RING: return launch_reduction<OP_AR_RING>(dtype, args, nranks, vec, grid, threads, s);
+    case OP_AR_TWOSHOT_ANY: return launch_reduction<OP_AR_TWOSHOT_ANY>(dtype, args, nranks, vec, grid, threads, s);
     case OP_REDUCE: return launch_reduction<OP_REDUCE>(dtype, args, nranks, vec, grid, threads, s);
     case OP_REDUCE_SCATTER: return launch_reduction<OP_REDUCE_SCATTER>(dtype, args, nranks, vec, grid, threads, s);
     case OP_AR_NVLS: return launch_float_only<OP_AR_NVLS>(dtype, args, nranks, grid, threads, s);
@@ -118,6 +122,7 @@ cudaError_t launch_collective(int op, int dtype, const CollArgs* args, int nrank
     case OP_BCAST_CHUNKED: return launch_bytes<OP_BCAST_CHUNKED>(args, nranks, vec, grid, threads, s);
     case OP_BCAST_MC: return launch_typed<OP_BCAST_MC, uint8_t, 16>(args, nranks, grid, threads, s);
     case OP_ALLGATHER: return launch_bytes<OP_ALLGATHER>(args, nranks, vec, grid, threads, s);
+    case OP_BCAST_ANY: return launch_bytes<OP_BCAST_ANY>(args, nranks, vec, grid, threads, s);
     case OP_BARRIER: return launch_typed<OP_BARRIER, uint8_t, 1>(args, nranks, grid, threads, s);
   }
   return cudaErrorInvalidValue;

@@ -119,6 +119,61 @@ __device__ void body_ar_twoshot(const CollArgs& a, int* s_abort) {
   peer_barrier(P, 2, 21, s_abort);
 }
 
+// ------------------------------------------------------------------ two-shot for tensors outside the heap
+// `in` and `out` are ordinary local tensors; the heap only provides scratch.  Phase A scatters: the
+// slice that member m owns is pushed from my input into slot [me] of m's scratch (in_off, R slots of
+// `per` vectors).  Phase B: every rank sums the R slots of its own slice into its result region
+// (out_off).  Phase C gathers: each rank pulls every owner's result straight into its output.  The
+// same NVLink bytes as the symmetric two-shot, and no separate copy kernels around the collective.
+template <typename T, int V>
+__device__ void body_ar_twoshot_any(const CollArgs& a, int* s_abort) {
+  const Peers& P = a.P;
+  const int R = P.n;
+  const size_t nv = a.n / V;
+  const size_t per = ceil_div(nv, R);
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  const size_t t0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const T* in = reinterpret_cast<const T*>(a.in);
+  T* out = reinterpret_cast<T*>(a.out);
+  if (!peer_barrier(P, 1, 25, s_abort)) return;           // everybody is done with the previous use of the scratch
+  for (int j = 0; j < R; ++j) {
+    const int m = (P.me + j) % R;
+    const size_t lo = per * m, len = lo < nv ? (nv - lo < per ? nv - lo : per) : 0;
+    T* slot = at<T>(P.base[m], a.in_off) + (size_t)P.me * per * V;
+    for (size_t i = t0; i < len; i += stride) st_pack_peer<T, V>(slot + i * V, ld_pack<T, V>(in + (lo + i) * V));
+  }
+  if (!peer_barrier(P, 2, 26, s_abort)) return;
+  {
+    const size_t lo = per * P.me, len = lo < nv ? (nv - lo < per ? nv - lo : per) : 0;
+    const T* slots = at<T>(P.base[P.me], a.in_off);
+    T* res = at<T>(P.base[P.me], a.out_off);
+    for (size_t i = t0; i < len; i += stride) {
+      Acc<T, V> acc;
+      for (int w = 0; w < R; ++w) {
+        Pack<T, V> x = ld_pack_peer<T, V>(slots + ((size_t)w * per + i) * V);
+        if (w == 0) acc.set(x); else acc.add(x);
+      }
+      st_pack<T, V>(res + i * V, acc.pack(a.scale));
+    }
+  }
+  if (!peer_barrier(P, 3, 27, s_abort)) return;
+  for (int j = 0; j < R; ++j) {
+    const int m = (P.me + j) % R;
+    const size_t lo = per * m, len = lo < nv ? (nv - lo < per ? nv - lo : per) : 0;
+    const T* res = at<T>(P.base[m], a.out_off);
+    size_t i = t0;
+    constexpr int U = 4;
+    for (; i + (U - 1) * stride < len; i += U * stride) {
+      Pack<T, V> x[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) x[u] = ld_pack_peer<T, V>(res + (i + u * stride) * V);
+#pragma unroll
+      for (int u = 0; u < U; ++u) st_pack<T, V>(out + (lo + i + u * stride) * V, x[u]);
+    }
+    for (; i < len; i += stride) st_pack<T, V>(out + (lo + i) * V, ld_pack_peer<T, V>(res + i * V));
+  }
+}
+
 // ------------------------------------------------------------------ NVLS (multimem)
 template <typename T> struct Multimem {
   static constexpr bool ok = false;
@@ -291,6 +346,36 @@ __device__ void body_bcast_mc(const CollArgs& a, int* s_abort) {
       }
     }
     peer_barrier(P, 2, 56, s_abort);
+  }
+}
+
+// Broadcast of a tensor that lives outside the heap: the root pushes its buffer into every peer's
+// scratch (one multicast store through the switch when the heap has a multicast mapping, else one
+// store per peer), and after the barrier every other rank copies its scratch into its own tensor.
+template <typename T, int V>
+__device__ void body_bcast_any(const CollArgs& a, int* s_abort) {
+  const Peers& P = a.P;
+  const size_t nv = a.n / V;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  const size_t t0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  T* buf = reinterpret_cast<T*>(a.out);
+  if (!peer_barrier(P, 1, 57, s_abort)) return;            // the scratch is free on every rank
+  if (P.me == a.root) {
+    const bool mc = a.aux != 0 && V * sizeof(T) == 16;
+    for (size_t i = t0; i < nv; i += stride) {
+      Pack<T, V> x = ld_pack<T, V>(buf + i * V);
+      if (mc) {
+        if constexpr (V * sizeof(T) == 16) multimem_st(at<T>(P.mc_base, a.in_off) + i * V, *reinterpret_cast<uint4*>(&x));
+      } else {
+        for (int m = 0; m < P.n; ++m)
+          if (m != P.me) st_pack_peer<T, V>(at<T>(P.base[m], a.in_off) + i * V, x);
+      }
+    }
+  }
+  if (!peer_barrier(P, 2, 58, s_abort)) return;
+  if (P.me != a.root) {
+    const T* src = at<T>(P.base[P.me], a.in_off);
+    for (size_t i = t0; i < nv; i += stride) st_pack<T, V>(buf + i * V, ld_pack_peer<T, V>(src + i * V));
   }
 }
 

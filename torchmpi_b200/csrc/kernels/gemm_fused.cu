@@ -356,7 +356,14 @@ int tmpi_cuda_ag_gemm(size_t a_shard_off, size_t a_full_off, const void* B, void
   CUtensorMap mown;
   if ((st = make_tmap_bf16(&mown, h.base[h.rank] + a_shard_off, (uint64_t)(M / R), (uint64_t)K, (uint64_t)K, gemm::BM))) return st;
   int sms = gemm_sm_count();
-  if (n_comm <= 0) n_comm = 8;
+  if (n_comm <= 0) {
+    // as many copy CTAs as the tile count leaves idle anyway: the largest count that does not add
+    // a wave of output tiles over what 8 copy CTAs would give
+    const int tiles = p.tiles_m * p.tiles_n;
+    const int waves = (tiles + sms - 8 - 1) / (sms - 8);
+    n_comm = 8;
+    while (n_comm + 1 <= sms / 4 && (tiles + sms - n_comm - 2) / (sms - n_comm - 1) == waves) ++n_comm;
+  }
   if (n_comm > sms / 4) n_comm = sms / 4;
   fa.sym_off = a_shard_off; fa.local = (__nv_bfloat16*)a_full; fa.ready = ws->ready;
   fa.ready_value = ++ws->ready_value; fa.rows_per_rank = M / R; fa.n_comm = n_comm;

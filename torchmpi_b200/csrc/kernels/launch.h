@@ -18,6 +18,8 @@ enum CollOp {
   OP_ALLGATHER,         // everybody reads every peer's chunk
   OP_REDUCE_SCATTER,    // everybody sums its own slice of every peer's buffer
   OP_BARRIER,
+  OP_AR_TWOSHOT_ANY,    // two-shot on tensors outside the heap: scatter-push, local reduce, gather-pull
+  OP_BCAST_ANY,         // broadcast of a tensor outside the heap: root pushes into scratch, peers copy out
   OP_COUNT
 };
 

@@ -130,9 +130,31 @@ static int allreduce_any(const void* in, void* out, size_t n, int dtype, double 
       ar->n = n; ar->scale = (float)scale; ar->root = h.world;
     });
   }
-  // bounce through the heap in chunks: copy in, reduce in place, copy out
   if (g->lane > 1) return fail(TMPI_ERR_INVALID, "lane %d has no bounce buffer", g->lane);
   size_t boff = bounce_off(h, g->lane);
+  if (a == 2 || a == 1) {
+    // two-shot straight from / to the caller's tensors: the bounce region is only scratch
+    // (R slots + one result slice per chunk), no copy kernels around the collective
+    const int R = g->nmembers;
+    bool vec = al16((size_t)in) && al16((size_t)out) && n % V == 0;
+    const size_t W = vec ? V : 1;                                  // elements per pack
+    size_t per_max = h.bounce_bytes / ((size_t)(R + 1) * W * es);  // packs per slot that fit
+    per_max = per_max / 16 * 16;                                   // keep slot starts 16-pack aligned
+    if (per_max == 0) return fail(TMPI_ERR_STATE, "staging_bytes too small for a %d-rank two-shot", R);
+    const size_t chunk = per_max * R * W;                          // elements per launch
+    for (size_t off = 0; off < n; off += chunk) {
+      const size_t m = std::min(chunk, n - off);
+      const size_t per = ((m / W) + R - 1) / R;
+      int st = run_op(OP_AR_TWOSHOT_ANY, dtype, g, vec, per, s, [&](int, CollArgs* ar) {
+        ar->in = (const char*)in + off * es; ar->out = (char*)out + off * es;
+        ar->in_off = boff; ar->out_off = boff + (size_t)R * per * W * es;
+        ar->n = m; ar->scale = (float)scale;
+      });
+      if (st) return st;
+    }
+    return TMPI_OK;
+  }
+  // NVLS and ring keep the symmetric kernels: bounce through the heap in chunks (copy in, reduce, copy out)
   size_t chunk = h.bounce_bytes / es / (V * g->nmembers) * (V * g->nmembers);
   for (size_t off = 0; off < n; off += chunk) {
     size_t m = std::min(chunk, n - off);
@@ -170,15 +192,19 @@ static int broadcast_any(void* buf, size_t n, int dtype, int root, const tmpi_gr
   size_t es = dtype_size(dtype), bytes = n * es, off;
   if (in_heap(buf, bytes, &off)) return broadcast_heap(off, n, dtype, root, g, 0, s);
   if (g->lane > 1) return fail(TMPI_ERR_INVALID, "lane %d has no bounce buffer", g->lane);
+  // the root pushes straight from its tensor into every peer's scratch; the peers copy out inside
+  // the same kernel (no copy kernels around the collective)
   size_t boff = bounce_off(h, g->lane);
   size_t chunk = h.bounce_bytes & ~size_t(15);
+  const bool mc = h.mc_base && whole_heap(g) && g->nmembers > 2 && tunable("use_nvls");
   for (size_t o = 0; o < bytes; o += chunk) {
     size_t m = std::min(chunk, bytes - o);
-    size_t padded = (m + 15) & ~size_t(15);
-    if (g->me == root) CK(cudaMemcpyAsync(h.base[h.rank] + boff, (char*)buf + o, m, cudaMemcpyDeviceToDevice, s));
-    int st = broadcast_heap(boff, padded, TMPI_U8, root, g, 0, s);
+    char* p = (char*)buf + o;
+    bool vec = al16((size_t)p) && m % 16 == 0;
+    int st = run_op(OP_BCAST_ANY, TMPI_U8, g, vec, vec ? m / 16 : m, s, [&](int, CollArgs* a) {
+      a->out = p; a->in_off = boff; a->n = m; a->root = root; a->aux = (mc && vec) ? 1 : 0;
+    });
     if (st) return st;
-    if (g->me != root) CK(cudaMemcpyAsync((char*)buf + o, h.base[h.rank] + boff, m, cudaMemcpyDeviceToDevice, s));
   }
   return TMPI_OK;
 }

@@ -45,7 +45,7 @@ def main():
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--n-comm", type=int, default=8)
+    ap.add_argument("--n-comm", type=int, default=0, help="copy CTAs of ag_gemm (0: chosen from the tile count)")
     ap.add_argument("--baseline", action="store_true")
     ap.add_argument("--link-gbs", type=float, default=770.0)
     args = ap.parse_args()

@@ -140,21 +140,40 @@ class CudaHeap:
             raise cls(code.value, f"device-side wait gave up at point {where.value} waiting for rank {peer.value}")
 
     # ---- collectives on tensors
+    def _needs_staging(self, t: torch.Tensor) -> bool:
+        """Every rank must pick the same kernel variant (16-byte packs or single elements) without
+        seeing the other ranks' pointers.  Heap offsets are symmetric, so heap tensors agree by
+        construction; a tensor outside the heap agrees only if its pointer is 16-byte aligned, in
+        which case the variant depends on the element count alone."""
+        return t.data_ptr() % 16 != 0 and self.offset_of(t) < 0
+
     def allreduce(self, inp, out, members, scale=1.0, algo=0, async_op=False):
+        fin, dst = [], out
+        if self._needs_staging(inp) or self._needs_staging(out):
+            tmp = torch.empty(inp.numel(), dtype=inp.dtype, device=inp.device).copy_(inp)
+            fin, inp, out = [lambda: dst.copy_(tmp)], tmp, tmp
         g, arr = self._group(members)
         args = (inp.data_ptr(), out.data_ptr(), inp.numel(), dtype_code(inp.dtype), float(scale), C.byref(g), int(algo),
                 stream_ptr())
         if async_op:
-            return Handle(ids=[lib.tmpi_cuda_allreduce_async(*args)], keep=(inp, out, arr, g))
+            return Handle(ids=[lib.tmpi_cuda_allreduce_async(*args)], finalizers=fin, keep=(inp, out, arr, g))
         check(lib.tmpi_cuda_allreduce(*args))
+        for f in fin:
+            f()
         return None
 
     def broadcast(self, t, root, members, async_op=False):
+        fin, dst = [], t
+        if self._needs_staging(t):
+            tmp = torch.empty(t.numel(), dtype=t.dtype, device=t.device).copy_(t)
+            fin, t = [lambda: dst.copy_(tmp)], tmp
         g, arr = self._group(members)
         args = (t.data_ptr(), t.numel(), dtype_code(t.dtype), int(root), C.byref(g), stream_ptr())
         if async_op:
-            return Handle(ids=[lib.tmpi_cuda_broadcast_async(*args)], keep=(t, arr, g))
+            return Handle(ids=[lib.tmpi_cuda_broadcast_async(*args)], finalizers=fin, keep=(t, arr, g))
         check(lib.tmpi_cuda_broadcast(*args))
+        for f in fin:
+            f()
         return None
 
     def reduce(self, inp, out, root, members, async_op=False):

@@ -50,7 +50,7 @@ launch_count = 0
 class TPGroup:
     """The ranks a tensor-parallel block spans, with the symmetric buffers its kernels need."""
 
-    def __init__(self, rows_per_rank: int, d_model: int, members: Optional[Sequence[int]] = None, n_comm: int = 8):
+    def __init__(self, rows_per_rank: int, d_model: int, members: Optional[Sequence[int]] = None, n_comm: int = 0):
         if S.cuda_heap is None or _ag_gemm is None:
             raise RuntimeError("tensor parallelism needs the CUDA symmetric heap and the fused GEMM kernels")
         self.heap = S.cuda_heap
@@ -172,7 +172,7 @@ class TensorParallelMLP(nn.Sequential):
     hidden width ``d_hidden``; activations travel between blocks as row shards."""
 
     def __init__(self, rows_per_rank: int, d_model: int = 8192, d_hidden: int = 32768, layers: int = 4,
-                 bias: bool = True, members: Optional[Sequence[int]] = None, n_comm: int = 8):
+                 bias: bool = True, members: Optional[Sequence[int]] = None, n_comm: int = 0):
         assert layers % 2 == 0
         tp = TPGroup(rows_per_rank, d_model, members, n_comm)
         super().__init__(*[TensorParallelMLPBlock(tp, d_model, d_hidden, bias) for _ in range(layers // 2)])
