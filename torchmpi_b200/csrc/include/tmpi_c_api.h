@@ -235,7 +235,7 @@ int tmpi_bn_relu_fwd(const void* x, const void* residual, void* y, const float* 
                      float eps, float momentum, int relu, int training, int dtype,
                      void* scratch, void* stream);
 int tmpi_bn_relu_bwd(const void* x, const void* y, const void* dy, void* dx, void* dresidual,
-                     const float* gamma, const float* save_mean, const float* save_invstd,
+                     const float* gamma, const float* beta, const float* save_mean, const float* save_invstd,
                      float* dgamma, float* dbeta, int64_t rows, int channels, int relu, int dtype,
                      void* scratch, void* stream);
 size_t tmpi_bn_scratch_bytes(int channels);

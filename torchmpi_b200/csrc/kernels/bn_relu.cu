@@ -12,6 +12,10 @@
 // writes of the activation; the reference has no such ops at all (its only kernel is `out += in`,
 // lib/detail/reduce_kernel.cu).  Every thread owns a fixed group of V channels, so partial sums
 // stay in registers; block partials go to scratch and are reduced in block order (deterministic).
+// (Walking the statistics pass from the end of the tensor towards its start, to begin on lines the
+// producer left in L2, was measured: the descending walk itself ran a third slower from HBM.)
+// A ReLU layer without a residual does not read y in backward: y > 0 exactly when the affine
+// transform of x is positive, and x is read anyway.
 #include "vec.cuh"
 #include "../include/tmpi_c_api.h"
 #include "../runtime/common.h"
@@ -32,17 +36,23 @@ template <typename T, int V, bool BWD>
 __global__ void __launch_bounds__(kBnThreads) bn_reduce_kernel(
     const T* __restrict__ x, const T* __restrict__ y, const T* __restrict__ dy,
     const float* __restrict__ mean, const float* __restrict__ invstd,
+    const float* __restrict__ gamma, const float* __restrict__ beta,
     size_t nvec, int C, int relu, float* __restrict__ partial) {
   const int cvn = C / V;
   const size_t T0 = (size_t)blockIdx.x * kBnThreads + threadIdx.x;
   const size_t stride = (size_t)gridDim.x * kBnThreads;
   const int cv = (int)(T0 % cvn);                 // fixed: stride is a multiple of cvn
-  float a[V], b[V], mu[V], is[V];
+  const bool mask_from_x = BWD && relu && y == nullptr;
+  float a[V], b[V], mu[V], is[V], sc[V], sh[V];
 #pragma unroll
   for (int k = 0; k < V; ++k) { a[k] = 0.f; b[k] = 0.f; }
   if (BWD) {
 #pragma unroll
     for (int k = 0; k < V; ++k) { mu[k] = mean[cv * V + k]; is[k] = invstd[cv * V + k]; }
+    if (mask_from_x) {
+#pragma unroll
+      for (int k = 0; k < V; ++k) { sc[k] = is[k] * gamma[cv * V + k]; sh[k] = beta[cv * V + k] - mu[k] * sc[k]; }
+    }
   }
   for (size_t v = T0; v < nvec; v += stride) {
     Pack<T, V> xv = ld_pack<T, V>(x + v * V);
@@ -51,11 +61,13 @@ __global__ void __launch_bounds__(kBnThreads) bn_reduce_kernel(
       for (int k = 0; k < V; ++k) { float f = (float)to_acc<T>(xv.v[k]); a[k] += f; b[k] += f * f; }
     } else {
       Pack<T, V> gv = ld_pack<T, V>(dy + v * V), yv;
-      if (relu) yv = ld_pack<T, V>(y + v * V);
+      if (relu && !mask_from_x) yv = ld_pack<T, V>(y + v * V);
 #pragma unroll
       for (int k = 0; k < V; ++k) {
         float g = (float)to_acc<T>(gv.v[k]);
-        if (relu && !((float)to_acc<T>(yv.v[k]) > 0.f)) g = 0.f;
+        if (mask_from_x) {
+          if (!((float)to_acc<T>(xv.v[k]) * sc[k] + sh[k] > 0.f)) g = 0.f;
+        } else if (relu && !((float)to_acc<T>(yv.v[k]) > 0.f)) g = 0.f;
         a[k] += g;
         b[k] += g * ((float)to_acc<T>(xv.v[k]) - mu[k]) * is[k];
       }
@@ -155,29 +167,33 @@ __global__ void __launch_bounds__(kBnThreads) bn_apply_fwd_kernel(
 template <typename T, int V>
 __global__ void __launch_bounds__(kBnThreads) bn_apply_bwd_kernel(
     const T* __restrict__ x, const T* __restrict__ y, const T* __restrict__ dy, T* __restrict__ dx,
-    T* __restrict__ dres, const float* __restrict__ gamma, const float* __restrict__ mean,
+    T* __restrict__ dres, const float* __restrict__ gamma, const float* __restrict__ beta, const float* __restrict__ mean,
     const float* __restrict__ invstd, const float* __restrict__ dgamma, const float* __restrict__ dbeta,
     size_t nvec, int C, int relu, float inv_m) {
   const int cvn = C / V;
   const size_t T0 = (size_t)blockIdx.x * kBnThreads + threadIdx.x;
   const size_t stride = (size_t)gridDim.x * kBnThreads;
   const int cv = (int)(T0 % cvn);
-  float mu[V], is[V], k1[V], k2[V], k3[V];
+  const bool mask_from_x = relu && y == nullptr;
+  float mu[V], is[V], k1[V], k2[V], k3[V], sh[V];
 #pragma unroll
   for (int k = 0; k < V; ++k) {
     const int c = cv * V + k;
     mu[k] = mean[c]; is[k] = invstd[c];
-    k1[k] = gamma[c] * is[k];            // dx = k1 * (dz - k2 - xhat * k3)
+    k1[k] = gamma[c] * is[k];            // dx = k1 * (dz - k2 - xhat * k3); also the forward scale
     k2[k] = dbeta[c] * inv_m;
     k3[k] = dgamma[c] * inv_m;
+    sh[k] = mask_from_x ? beta[c] - mu[k] * k1[k] : 0.f;
   }
   for (size_t v = T0; v < nvec; v += stride) {
     Pack<T, V> xv = ld_pack<T, V>(x + v * V), gv = ld_pack<T, V>(dy + v * V), yv, ox, orr;
-    if (relu) yv = ld_pack<T, V>(y + v * V);
+    if (relu && !mask_from_x) yv = ld_pack<T, V>(y + v * V);
 #pragma unroll
     for (int k = 0; k < V; ++k) {
       float g = (float)to_acc<T>(gv.v[k]);
-      if (relu && !((float)to_acc<T>(yv.v[k]) > 0.f)) g = 0.f;
+      if (mask_from_x) {
+        if (!((float)to_acc<T>(xv.v[k]) * k1[k] + sh[k] > 0.f)) g = 0.f;
+      } else if (relu && !((float)to_acc<T>(yv.v[k]) > 0.f)) g = 0.f;
       float xhat = ((float)to_acc<T>(xv.v[k]) - mu[k]) * is[k];
       ox.v[k] = from_acc<T>((typename AccOf<T>::type)(k1[k] * (g - k2[k] - xhat * k3[k])));
       orr.v[k] = from_acc<T>((typename AccOf<T>::type)g);
@@ -204,7 +220,7 @@ static int bn_fwd_t(const void* x, const void* res, void* y, const float* gamma,
   size_t nvec = (size_t)rows * (C / V);
   int grid = bn_grid(nvec);
   if (training) {
-    bn_reduce_kernel<T, V, false><<<grid, kBnThreads, 0, s>>>((const T*)x, nullptr, nullptr, nullptr, nullptr, nvec, C, 0,
+    bn_reduce_kernel<T, V, false><<<grid, kBnThreads, 0, s>>>((const T*)x, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nvec, C, 0,
                                                               (float*)scratch);
     float m = (float)rows;
     bn_finalize_fwd_kernel<<<(C + 31) / 32, dim3(32, 32), 0, s>>>((const float*)scratch, grid, C, 1.f / m,
@@ -218,17 +234,18 @@ static int bn_fwd_t(const void* x, const void* res, void* y, const float* gamma,
 
 template <typename T>
 static int bn_bwd_t(const void* x, const void* y, const void* dy, void* dx, void* dres, const float* gamma,
-                    const float* smean, const float* sinv, float* dgamma, float* dbeta, int64_t rows, int C, int relu,
+                    const float* beta, const float* smean, const float* sinv, float* dgamma, float* dbeta, int64_t rows, int C, int relu,
                     void* scratch, cudaStream_t s) {
   constexpr int V = 16 / sizeof(T);
   int st = bn_check(rows, C, V);
   if (st) return st;
+  if (relu && !y && (!beta || dres)) return fail(TMPI_ERR_INVALID, "bn backward: without y the layer needs beta and no residual");
   size_t nvec = (size_t)rows * (C / V);
   int grid = bn_grid(nvec);
-  bn_reduce_kernel<T, V, true><<<grid, kBnThreads, 0, s>>>((const T*)x, (const T*)y, (const T*)dy, smean, sinv, nvec, C, relu,
+  bn_reduce_kernel<T, V, true><<<grid, kBnThreads, 0, s>>>((const T*)x, (const T*)y, (const T*)dy, smean, sinv, gamma, beta, nvec, C, relu,
                                                            (float*)scratch);
   bn_finalize_bwd_kernel<<<(C + 31) / 32, dim3(32, 32), 0, s>>>((const float*)scratch, grid, C, dgamma, dbeta);
-  bn_apply_bwd_kernel<T, V><<<grid, kBnThreads, 0, s>>>((const T*)x, (const T*)y, (const T*)dy, (T*)dx, (T*)dres, gamma, smean,
+  bn_apply_bwd_kernel<T, V><<<grid, kBnThreads, 0, s>>>((const T*)x, (const T*)y, (const T*)dy, (T*)dx, (T*)dres, gamma, beta, smean,
                                                         sinv, dgamma, dbeta, nvec, C, relu, 1.f / (float)rows);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? TMPI_OK : fail(TMPI_ERR_CUDA, "bn backward launch: %s", cudaGetErrorString(e));
@@ -260,16 +277,17 @@ int tmpi_bn_relu_fwd(const void* x, const void* residual, void* y, const float* 
   return fail(TMPI_ERR_UNSUPPORTED, "bn: dtype %d", dtype);
 }
 
+// y == nullptr (ReLU layers without a residual only): the ReLU mask is recomputed from x, gamma and beta.
 int tmpi_bn_relu_bwd(const void* x, const void* y, const void* dy, void* dx, void* dresidual, const float* gamma,
-                     const float* save_mean, const float* save_invstd, float* dgamma, float* dbeta, int64_t rows,
+                     const float* beta, const float* save_mean, const float* save_invstd, float* dgamma, float* dbeta, int64_t rows,
                      int channels, int relu, int dtype, void* scratch, void* stream) {
   cudaStream_t s = (cudaStream_t)stream;
   switch (dtype) {
-    case TMPI_BF16: return bn_bwd_t<__nv_bfloat16>(x, y, dy, dx, dresidual, gamma, save_mean, save_invstd, dgamma, dbeta,
+    case TMPI_BF16: return bn_bwd_t<__nv_bfloat16>(x, y, dy, dx, dresidual, gamma, beta, save_mean, save_invstd, dgamma, dbeta,
                                                    rows, channels, relu, scratch, s);
-    case TMPI_F16: return bn_bwd_t<__half>(x, y, dy, dx, dresidual, gamma, save_mean, save_invstd, dgamma, dbeta, rows,
+    case TMPI_F16: return bn_bwd_t<__half>(x, y, dy, dx, dresidual, gamma, beta, save_mean, save_invstd, dgamma, dbeta, rows,
                                            channels, relu, scratch, s);
-    case TMPI_F32: return bn_bwd_t<float>(x, y, dy, dx, dresidual, gamma, save_mean, save_invstd, dgamma, dbeta, rows,
+    case TMPI_F32: return bn_bwd_t<float>(x, y, dy, dx, dresidual, gamma, beta, save_mean, save_invstd, dgamma, dbeta, rows,
                                           channels, relu, scratch, s);
   }
   return fail(TMPI_ERR_UNSUPPORTED, "bn: dtype %d", dtype);

@@ -125,6 +125,20 @@ __device__ void body_ar_twoshot(const CollArgs& a, int* s_abort) {
 // `per` vectors).  Phase B: every rank sums the R slots of its own slice into its result region
 // (out_off).  Phase C gathers: each rank pulls every owner's result straight into its output.  The
 // same NVLink bytes as the symmetric two-shot, and no separate copy kernels around the collective.
+// grid-strided copy of `len` packs with U loads in flight per thread; either side may be peer memory
+template <typename T, int V, int U>
+__device__ __forceinline__ void copy_packs(T* dst, const T* src, size_t len, size_t t0, size_t stride) {
+  size_t i = t0;
+  for (; i + (U - 1) * stride < len; i += U * stride) {
+    Pack<T, V> x[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) x[u] = ld_pack_peer<T, V>(src + (i + u * stride) * V);
+#pragma unroll
+    for (int u = 0; u < U; ++u) st_pack_peer<T, V>(dst + (i + u * stride) * V, x[u]);
+  }
+  for (; i < len; i += stride) st_pack_peer<T, V>(dst + i * V, ld_pack_peer<T, V>(src + i * V));
+}
+
 template <typename T, int V>
 __device__ void body_ar_twoshot_any(const CollArgs& a, int* s_abort) {
   const Peers& P = a.P;
@@ -135,42 +149,54 @@ __device__ void body_ar_twoshot_any(const CollArgs& a, int* s_abort) {
   const size_t t0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const T* in = reinterpret_cast<const T*>(a.in);
   T* out = reinterpret_cast<T*>(a.out);
+  constexpr int U = V * sizeof(T) == 16 ? 8 : 4;
   if (!peer_barrier(P, 1, 25, s_abort)) return;           // everybody is done with the previous use of the scratch
-  for (int j = 0; j < R; ++j) {
+  for (int j = 1; j < R; ++j) {                           // my own slice stays where it is
     const int m = (P.me + j) % R;
     const size_t lo = per * m, len = lo < nv ? (nv - lo < per ? nv - lo : per) : 0;
-    T* slot = at<T>(P.base[m], a.in_off) + (size_t)P.me * per * V;
-    for (size_t i = t0; i < len; i += stride) st_pack_peer<T, V>(slot + i * V, ld_pack<T, V>(in + (lo + i) * V));
+    copy_packs<T, V, U>(at<T>(P.base[m], a.in_off) + (size_t)P.me * per * V, in + lo * V, len, t0, stride);
   }
   if (!peer_barrier(P, 2, 26, s_abort)) return;
+  const size_t mylo = per * P.me, mylen = mylo < nv ? (nv - mylo < per ? nv - mylo : per) : 0;
   {
-    const size_t lo = per * P.me, len = lo < nv ? (nv - lo < per ? nv - lo : per) : 0;
     const T* slots = at<T>(P.base[P.me], a.in_off);
     T* res = at<T>(P.base[P.me], a.out_off);
-    for (size_t i = t0; i < len; i += stride) {
-      Acc<T, V> acc;
+    constexpr int UB = 2;
+    size_t i = t0;
+    for (; i + (UB - 1) * stride < mylen; i += UB * stride) {
+      Acc<T, V> acc[UB];
+#pragma unroll
+      for (int u = 0; u < UB; ++u) acc[u].set(ld_pack<T, V>(in + (mylo + i + u * stride) * V));
       for (int w = 0; w < R; ++w) {
-        Pack<T, V> x = ld_pack_peer<T, V>(slots + ((size_t)w * per + i) * V);
-        if (w == 0) acc.set(x); else acc.add(x);
+        if (w == P.me) continue;
+        Pack<T, V> x[UB];
+#pragma unroll
+        for (int u = 0; u < UB; ++u) x[u] = ld_pack_peer<T, V>(slots + ((size_t)w * per + i + u * stride) * V);
+#pragma unroll
+        for (int u = 0; u < UB; ++u) acc[u].add(x[u]);
       }
-      st_pack<T, V>(res + i * V, acc.pack(a.scale));
+#pragma unroll
+      for (int u = 0; u < UB; ++u) {
+        Pack<T, V> r = acc[u].pack(a.scale);
+        st_pack<T, V>(res + (i + u * stride) * V, r);       // for the peers
+        st_pack<T, V>(out + (mylo + i + u * stride) * V, r); // and my own output
+      }
+    }
+    for (; i < mylen; i += stride) {
+      Acc<T, V> acc;
+      acc.set(ld_pack<T, V>(in + (mylo + i) * V));
+      for (int w = 0; w < R; ++w)
+        if (w != P.me) acc.add(ld_pack_peer<T, V>(slots + ((size_t)w * per + i) * V));
+      Pack<T, V> r = acc.pack(a.scale);
+      st_pack<T, V>(res + i * V, r);
+      st_pack<T, V>(out + (mylo + i) * V, r);
     }
   }
   if (!peer_barrier(P, 3, 27, s_abort)) return;
-  for (int j = 0; j < R; ++j) {
+  for (int j = 1; j < R; ++j) {
     const int m = (P.me + j) % R;
     const size_t lo = per * m, len = lo < nv ? (nv - lo < per ? nv - lo : per) : 0;
-    const T* res = at<T>(P.base[m], a.out_off);
-    size_t i = t0;
-    constexpr int U = 4;
-    for (; i + (U - 1) * stride < len; i += U * stride) {
-      Pack<T, V> x[U];
-#pragma unroll
-      for (int u = 0; u < U; ++u) x[u] = ld_pack_peer<T, V>(res + (i + u * stride) * V);
-#pragma unroll
-      for (int u = 0; u < U; ++u) st_pack<T, V>(out + (lo + i + u * stride) * V, x[u]);
-    }
-    for (; i < len; i += stride) st_pack<T, V>(out + (lo + i) * V, ld_pack_peer<T, V>(res + i * V));
+    copy_packs<T, V, U>(out + lo * V, at<T>(P.base[m], a.out_off), len, t0, stride);
   }
 }
 
@@ -362,20 +388,32 @@ __device__ void body_bcast_any(const CollArgs& a, int* s_abort) {
   if (!peer_barrier(P, 1, 57, s_abort)) return;            // the scratch is free on every rank
   if (P.me == a.root) {
     const bool mc = a.aux != 0 && V * sizeof(T) == 16;
-    for (size_t i = t0; i < nv; i += stride) {
-      Pack<T, V> x = ld_pack<T, V>(buf + i * V);
-      if (mc) {
-        if constexpr (V * sizeof(T) == 16) multimem_st(at<T>(P.mc_base, a.in_off) + i * V, *reinterpret_cast<uint4*>(&x));
-      } else {
-        for (int m = 0; m < P.n; ++m)
-          if (m != P.me) st_pack_peer<T, V>(at<T>(P.base[m], a.in_off) + i * V, x);
+    if (mc) {
+      if constexpr (V * sizeof(T) == 16) {
+        constexpr int U = 4;
+        size_t i = t0;
+        for (; i + (U - 1) * stride < nv; i += U * stride) {
+          Pack<T, V> x[U];
+#pragma unroll
+          for (int u = 0; u < U; ++u) x[u] = ld_pack<T, V>(buf + (i + u * stride) * V);
+#pragma unroll
+          for (int u = 0; u < U; ++u)
+            multimem_st(at<T>(P.mc_base, a.in_off) + (i + u * stride) * V, *reinterpret_cast<uint4*>(&x[u]));
+        }
+        for (; i < nv; i += stride) {
+          Pack<T, V> x = ld_pack<T, V>(buf + i * V);
+          multimem_st(at<T>(P.mc_base, a.in_off) + i * V, *reinterpret_cast<uint4*>(&x));
+        }
       }
+    } else {
+      for (int j = 1; j < P.n; ++j)
+        copy_packs<T, V, 8>(at<T>(P.base[(P.me + j) % P.n], a.in_off), buf, nv, t0, stride);
     }
   }
   if (!peer_barrier(P, 2, 58, s_abort)) return;
   if (P.me != a.root) {
     const T* src = at<T>(P.base[P.me], a.in_off);
-    for (size_t i = t0; i < nv; i += stride) st_pack<T, V>(buf + i * V, ld_pack_peer<T, V>(src + i * V));
+    copy_packs<T, V, 8>(buf, src, nv, t0, stride);
   }
 }
 

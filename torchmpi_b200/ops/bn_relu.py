@@ -63,14 +63,16 @@ class _BnReluFn(torch.autograd.Function):
             mean.data_ptr(), invstd.data_ptr(), rows, C, eps, momentum, int(relu), int(training),
             dtype_code(x.dtype), _scratch_for(x.device, C).data_ptr(), stream_ptr()))
         launch_count += 3 if training else 1
-        ctx.save_for_backward(x, y, gamma, mean, invstd)
+        # a ReLU layer without a residual rebuilds its mask from x in backward and does not keep y
+        ctx.mask_from_x = relu and residual is None
+        ctx.save_for_backward(x, None if ctx.mask_from_x else y, gamma, beta, mean, invstd)
         ctx.relu, ctx.has_res = relu, residual is not None
         return y
 
     @staticmethod
     def backward(ctx, dy):
         global launch_count
-        x, y, gamma, mean, invstd = ctx.saved_tensors
+        x, y, gamma, beta, mean, invstd = ctx.saved_tensors
         dy = dy.contiguous(memory_format=torch.channels_last)
         N, C, H, W = x.shape
         dx = torch.empty_like(x, memory_format=torch.channels_last)
@@ -78,8 +80,8 @@ class _BnReluFn(torch.autograd.Function):
         dgamma = torch.empty(C, dtype=torch.float32, device=x.device)
         dbeta = torch.empty(C, dtype=torch.float32, device=x.device)
         check(lib.tmpi_bn_relu_bwd(
-            x.data_ptr(), y.data_ptr(), dy.data_ptr(), dx.data_ptr(), dres.data_ptr() if dres is not None else None,
-            gamma.data_ptr(), mean.data_ptr(), invstd.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(),
+            x.data_ptr(), y.data_ptr() if y is not None else None, dy.data_ptr(), dx.data_ptr(),
+            dres.data_ptr() if dres is not None else None, gamma.data_ptr(), beta.data_ptr(), mean.data_ptr(), invstd.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(),
             N * H * W, C, int(ctx.relu), dtype_code(x.dtype), _scratch_for(x.device, C).data_ptr(), stream_ptr()))
         launch_count += 3
         return dx, dres, dgamma, dbeta, None, None, None, None, None, None
