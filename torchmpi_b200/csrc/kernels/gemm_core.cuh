@@ -66,7 +66,8 @@ __device__ __forceinline__ void setup(Shared* sh, unsigned char* tiles, int warp
   sm100::tc_fence_after();
 }
 
-__device__ __forceinline__ void fail(Shared* sh, const Problem& p, int where) {
+template <typename Sh>
+__device__ __forceinline__ void fail(Sh* sh, const Problem& p, int where) {
   atomicExch(&sh->error, where);
   if (p.status) atomicCAS(p.status, 0, 1000 + where);
 }
@@ -192,9 +193,10 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void*
                ::"l"(map), "r"(sm100::smem_u32(smem_src)), "r"(c0), "r"(c1) : "memory");
 }
 
-template <typename TileOrder, typename DestMap>
-__device__ __forceinline__ void epilogue_tma(Shared* sh, unsigned char* staging, const Problem& p, int quarter, int lane,
-                                             TileOrder order, DestMap dest) {
+// Release(acc) is called by one lane of each of the four warps once the accumulator is drained.
+template <typename Sh, typename TileOrder, typename DestMap, typename Release>
+__device__ __forceinline__ void epilogue_tma_impl(Sh* sh, unsigned char* staging, const Problem& p, int quarter, int lane,
+                                                  TileOrder order, DestMap dest, Release release) {
   constexpr int SLICE = 64, SLICE_BYTES = BM * SLICE * 2;
   const int r_in_tile = quarter * 32 + lane;
   const bool leader = quarter == 2 && lane == 0;      // warp 2 of the CTA holds quarter 2
@@ -255,19 +257,25 @@ __device__ __forceinline__ void epilogue_tma(Shared* sh, unsigned char* staging,
       }
       sm100::fence_proxy_async();        // generic-proxy writes to shared memory -> visible to the TMA unit
       epi_bar_sync();
-      if (leader && col0 < p.N) {
+      if (leader && col0 < p.N && cmap) {
         tma_store_2d(cmap, stg, col0, row0);
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
       }
     }
     sm100::tc_fence_before();
     __syncwarp();
-    if (lane == 0) sm100::mbar_arrive(&sh->acc_empty[acc]);   // four warps arrive: accumulator drained
+    if (lane == 0) release(acc);                                // four warps arrive: accumulator drained
   }
   if (leader) {
     asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // all stores complete before exit
     sm100::fence_proxy_async();
   }
+}
+
+template <typename TileOrder, typename DestMap>
+__device__ __forceinline__ void epilogue_tma(Shared* sh, unsigned char* staging, const Problem& p, int quarter, int lane,
+                                             TileOrder order, DestMap dest) {
+  epilogue_tma_impl(sh, staging, p, quarter, lane, order, dest, [sh](int acc) { sm100::mbar_arrive(&sh->acc_empty[acc]); });
 }
 
 // Frees the tensor memory after every role is done (all threads call).  When an error was raised

@@ -107,6 +107,10 @@ int gemm_sm_count() {
   return n;
 }
 
+bool gemm_pair_applicable(const void* C, int M, int N, int K);
+int launch_gemm_pair(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int epilogue,
+                     int* status_word, cudaStream_t stream);
+
 static int* gemm_status_word() {
   static int* dev_ptr = nullptr;
   static int* host_ptr = nullptr;
@@ -131,6 +135,8 @@ int tmpi_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int 
   if (M < 1 || N < 1 || K < 1) return fail(TMPI_ERR_INVALID, "gemm: empty problem");
   if (K % 8) return fail(TMPI_ERR_INVALID, "gemm: K must be a multiple of 8 (16-byte rows for TMA)");
   if ((epilogue & gemm::EPI_BIAS) && !bias) return fail(TMPI_ERR_INVALID, "gemm: bias epilogue without bias");
+  if (tunable("gemm_pair") && gemm_pair_applicable(C, M, N, K))
+    return launch_gemm_pair(A, B, C, bias, M, N, K, epilogue, gemm_status_word(), (cudaStream_t)stream);
   CUtensorMap ma, mb;
   int st = make_tmap_bf16(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)K, gemm::BM);
   if (st) return st;

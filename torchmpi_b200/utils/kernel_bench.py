@@ -85,6 +85,7 @@ def cases(small: bool):
     big = torch.randn((64 if small else 256) << 20, device=dev)
     out["absmean_var"] = (lambda: stats.absmean_var(big), big.numel() * 4)
 
+    from torchmpi_b200 import config
     from torchmpi_b200.ops import gemm
     for name, (M, N, K) in {"gemm_bf16_8192": (8192, 8192, 8192), "gemm_bf16_tp_col": (8192, 4096, 8192),
                             "gemm_bf16_tp_row": (8192, 8192, 4096)}.items():
@@ -94,6 +95,14 @@ def cases(small: bool):
         b = torch.randn(N, K, device=dev).to(torch.bfloat16)
         c = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
         out[name] = (lambda a=a, b=b, c=c: gemm.matmul_nt(a, b, out=c), (M * K + N * K + M * N) * 2, 2.0 * M * N * K)
+
+        def single(a=a, b=b, c=c):          # the 128 x 256 kernel on one CTA per tile
+            config.set("gemm_pair", 0)
+            try:
+                gemm.matmul_nt(a, b, out=c)
+            finally:
+                config.set("gemm_pair", 1)
+        out[name + "_1cta"] = (single, (M * K + N * K + M * N) * 2, 2.0 * M * N * K)
         out[name + "_cublas"] = (lambda a=a, b=b, c=c: torch.matmul(a, b.t(), out=c), (M * K + N * K + M * N) * 2,
                                  2.0 * M * N * K)
     return out
