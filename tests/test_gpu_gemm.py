@@ -57,6 +57,23 @@ def test_gemm_cta_pair_and_single_cta_paths(M, N, K):
     assert torch.equal(out[0][0], out[1][0])
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 384, 200), (1024, 2048, 1024), (2048, 4096, 8192)])
+def test_gemm_reads_second_operand_as_k_by_n(M, N, K):
+    """``matmul_nn(a, b)`` with ``b [K, N]`` (MN-major shared-memory descriptor) equals the K-major
+    kernel on a transposed copy bit for bit, and the fp32 product within rounding."""
+    from torchmpi_b200.ops import gemm
+    torch.manual_seed(M + 3 * N + 5 * K)
+    a = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    b = (torch.randn(K, N, device="cuda") * 0.2).to(torch.bfloat16)
+    y = gemm.matmul_nn(a, b)
+    y_t = gemm.matmul_nt(a, b.t().contiguous())
+    torch.cuda.synchronize()
+    gemm.check_status()
+    ref = a.float() @ b.float()
+    assert torch.allclose(y.float(), ref, rtol=1e-2, atol=0.02 * (K ** 0.5))
+    assert torch.equal(y, y_t)
+
+
 def test_gemm_epilogues_and_identity():
     from torchmpi_b200.ops import gemm
     torch.manual_seed(0)
@@ -120,6 +137,11 @@ def test_fused_gemms_single_rank():
             y = tp.gemm_rs(z, w2)
             ref2 = z.float() @ w2.float().t()
             assert torch.allclose(y.float(), ref2, rtol=2e-2, atol=5e-2), rep
+        # the weight handed over as [K, N] (what backward does) gives the same bits as its transpose
+        z_kn = tp.ag_gemm(x, full_off, full_buf, w1.t().contiguous(), None, w_is_kn=True)
+        assert torch.equal(z_kn, tp.ag_gemm(x, full_off, full_buf, w1, None))
+        y_kn = tp.gemm_rs(z, w2.t().contiguous(), w_is_kn=True)
+        assert torch.equal(y_kn, tp.gemm_rs(z, w2))
         torch.cuda.synchronize()
         tp.check()
     finally:

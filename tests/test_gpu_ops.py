@@ -154,3 +154,25 @@ def test_maxpool_nhwc_matches_torch(shape, k, s, p):
     yr.backward(dy)
     # many ties (zeros after ReLU): the first maximum of a window must receive the gradient
     assert torch.allclose(xa.grad.float(), xb.grad.float(), atol=2e-2, rtol=2e-2)
+
+
+def test_stem_conv_matches_conv2d():
+    """im2col + tcgen05 GEMM stem against an fp32 conv2d of the same bf16 operands, forward and dW."""
+    from torchmpi_b200.ops import stem_conv, gemm
+    torch.manual_seed(5)
+    for N, H, W in ((4, 224, 224), (3, 64, 96), (2, 40, 56)):
+        conv = stem_conv.StemConv7x7(64).cuda().to(torch.bfloat16).to(memory_format=torch.channels_last)
+        x = torch.randn(N, 3, H, W, device="cuda").to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+        assert stem_conv.supported(x, conv.weight)
+        y = conv(x)
+        assert y.is_contiguous(memory_format=torch.channels_last)
+        dy = torch.randn_like(y)
+        y.backward(dy)
+        wr = conv.weight.detach().float().requires_grad_(True)
+        yr = torch.nn.functional.conv2d(x.float(), wr, None, 2, 3)
+        yr.backward(dy.float())
+        assert y.shape == yr.shape
+        assert torch.allclose(y.float(), yr, rtol=2e-2, atol=5e-2), (N, H, W, (y.float() - yr).abs().max().item())
+        rel = (conv.weight.grad.float() - wr.grad).norm() / wr.grad.norm()
+        assert rel < 1e-2, (N, H, W, rel.item())
+        gemm.check_status()

@@ -245,6 +245,11 @@ int tmpi_maxpool_fwd(const void* x, void* y, void* idx, int N, int H, int W, int
 int tmpi_maxpool_bwd(const void* dy, const void* idx, void* dx, int N, int H, int W, int C, int OH, int OW,
                      int k, int s, int p, int dtype, void* stream);
 
+// Patch matrix of a 7x7 / stride 2 / pad 3 convolution over a channels-last input with 3 channels:
+// col[N*OH*OW, tmpi_stem_patch_width()] in (kh, kw, c) order, zero padded (the stem as a GEMM).
+int tmpi_stem_im2col(const void* x, void* col, int N, int H, int W, int dtype, void* stream);
+int tmpi_stem_patch_width(void);
+
 // ---------------------------------------------------------------- tcgen05 GEMM family
 // C[M,N] = act(A[M,K] * B[N,K]^T (+ bias)), bf16 in, fp32 accumulate in TMEM.
 int tmpi_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,

@@ -32,8 +32,11 @@ static int bn_grid(size_t nvec) {
 }
 
 // partial[(block * 2 + which) * C + c]
-template <typename T, int V, bool BWD>
-__global__ void __launch_bounds__(kBnThreads) bn_reduce_kernel(
+// MASKX (backward only): the ReLU mask comes from x, gamma and beta instead of y.  A template
+// parameter, not a run-time flag: the extra scale / shift registers would otherwise cost the other
+// path one resident block per SM.
+template <typename T, int V, bool BWD, bool MASKX>
+__global__ void __launch_bounds__(kBnThreads, 4) bn_reduce_kernel(
     const T* __restrict__ x, const T* __restrict__ y, const T* __restrict__ dy,
     const float* __restrict__ mean, const float* __restrict__ invstd,
     const float* __restrict__ gamma, const float* __restrict__ beta,
@@ -42,7 +45,7 @@ __global__ void __launch_bounds__(kBnThreads) bn_reduce_kernel(
   const size_t T0 = (size_t)blockIdx.x * kBnThreads + threadIdx.x;
   const size_t stride = (size_t)gridDim.x * kBnThreads;
   const int cv = (int)(T0 % cvn);                 // fixed: stride is a multiple of cvn
-  const bool mask_from_x = BWD && relu && y == nullptr;
+  constexpr bool mask_from_x = BWD && MASKX;
   float a[V], b[V], mu[V], is[V], sc[V], sh[V];
 #pragma unroll
   for (int k = 0; k < V; ++k) { a[k] = 0.f; b[k] = 0.f; }
@@ -89,16 +92,24 @@ __global__ void __launch_bounds__(kBnThreads) bn_reduce_kernel(
 
 // Sums the per-block partials of 32 channels with a 32 x 32 thread block: thread (cx, ry) adds the
 // blocks ry, ry + 32, ... of channel cx (coalesced over cx), then row 0 adds the 32 slices in order.
-// A serial loop over ~600 partials per channel made this step as slow as the bandwidth-bound passes.
+// All of a thread's loads are issued before the first add (the trip count is bounded by the largest
+// grid): a loop of dependent load-add pairs cost one L2 latency per partial, which made this tiny
+// kernel as slow as a bandwidth-bound pass.
+constexpr int kBnPartialsPerThread = (kBnMaxGrid + 31) / 32;
 __device__ __forceinline__ bool bn_partial_sums(const float* __restrict__ partial, int nblocks, int C, float* s1, float* s2) {
   __shared__ float sh1[32][33], sh2[32][33];
   const int c = blockIdx.x * 32 + threadIdx.x;
+  float va[kBnPartialsPerThread], vb[kBnPartialsPerThread];
+#pragma unroll
+  for (int j = 0; j < kBnPartialsPerThread; ++j) {
+    const int blk = threadIdx.y + 32 * j;
+    const bool ok = c < C && blk < nblocks;
+    va[j] = ok ? partial[((size_t)blk * 2) * C + c] : 0.f;
+    vb[j] = ok ? partial[((size_t)blk * 2 + 1) * C + c] : 0.f;
+  }
   float a = 0.f, b = 0.f;
-  if (c < C)
-    for (int blk = threadIdx.y; blk < nblocks; blk += 32) {
-      a += partial[((size_t)blk * 2) * C + c];
-      b += partial[((size_t)blk * 2 + 1) * C + c];
-    }
+#pragma unroll
+  for (int j = 0; j < kBnPartialsPerThread; ++j) { a += va[j]; b += vb[j]; }
   sh1[threadIdx.y][threadIdx.x] = a;
   sh2[threadIdx.y][threadIdx.x] = b;
   __syncthreads();
@@ -164,8 +175,8 @@ __global__ void __launch_bounds__(kBnThreads) bn_apply_fwd_kernel(
   }
 }
 
-template <typename T, int V>
-__global__ void __launch_bounds__(kBnThreads) bn_apply_bwd_kernel(
+template <typename T, int V, bool MASKX>
+__global__ void __launch_bounds__(kBnThreads, 4) bn_apply_bwd_kernel(
     const T* __restrict__ x, const T* __restrict__ y, const T* __restrict__ dy, T* __restrict__ dx,
     T* __restrict__ dres, const float* __restrict__ gamma, const float* __restrict__ beta, const float* __restrict__ mean,
     const float* __restrict__ invstd, const float* __restrict__ dgamma, const float* __restrict__ dbeta,
@@ -174,7 +185,7 @@ __global__ void __launch_bounds__(kBnThreads) bn_apply_bwd_kernel(
   const size_t T0 = (size_t)blockIdx.x * kBnThreads + threadIdx.x;
   const size_t stride = (size_t)gridDim.x * kBnThreads;
   const int cv = (int)(T0 % cvn);
-  const bool mask_from_x = relu && y == nullptr;
+  constexpr bool mask_from_x = MASKX;
   float mu[V], is[V], k1[V], k2[V], k3[V], sh[V];
 #pragma unroll
   for (int k = 0; k < V; ++k) {
@@ -220,7 +231,7 @@ static int bn_fwd_t(const void* x, const void* res, void* y, const float* gamma,
   size_t nvec = (size_t)rows * (C / V);
   int grid = bn_grid(nvec);
   if (training) {
-    bn_reduce_kernel<T, V, false><<<grid, kBnThreads, 0, s>>>((const T*)x, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nvec, C, 0,
+    bn_reduce_kernel<T, V, false, false><<<grid, kBnThreads, 0, s>>>((const T*)x, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nvec, C, 0,
                                                               (float*)scratch);
     float m = (float)rows;
     bn_finalize_fwd_kernel<<<(C + 31) / 32, dim3(32, 32), 0, s>>>((const float*)scratch, grid, C, 1.f / m,
@@ -242,11 +253,20 @@ static int bn_bwd_t(const void* x, const void* y, const void* dy, void* dx, void
   if (relu && !y && (!beta || dres)) return fail(TMPI_ERR_INVALID, "bn backward: without y the layer needs beta and no residual");
   size_t nvec = (size_t)rows * (C / V);
   int grid = bn_grid(nvec);
-  bn_reduce_kernel<T, V, true><<<grid, kBnThreads, 0, s>>>((const T*)x, (const T*)y, (const T*)dy, smean, sinv, gamma, beta, nvec, C, relu,
-                                                           (float*)scratch);
+  const bool maskx = relu && !y;
+  if (maskx)
+    bn_reduce_kernel<T, V, true, true><<<grid, kBnThreads, 0, s>>>((const T*)x, nullptr, (const T*)dy, smean, sinv, gamma, beta, nvec,
+                                                                   C, relu, (float*)scratch);
+  else
+    bn_reduce_kernel<T, V, true, false><<<grid, kBnThreads, 0, s>>>((const T*)x, (const T*)y, (const T*)dy, smean, sinv, gamma, beta,
+                                                                    nvec, C, relu, (float*)scratch);
   bn_finalize_bwd_kernel<<<(C + 31) / 32, dim3(32, 32), 0, s>>>((const float*)scratch, grid, C, dgamma, dbeta);
-  bn_apply_bwd_kernel<T, V><<<grid, kBnThreads, 0, s>>>((const T*)x, (const T*)y, (const T*)dy, (T*)dx, (T*)dres, gamma, beta, smean,
-                                                        sinv, dgamma, dbeta, nvec, C, relu, 1.f / (float)rows);
+  if (maskx)
+    bn_apply_bwd_kernel<T, V, true><<<grid, kBnThreads, 0, s>>>((const T*)x, nullptr, (const T*)dy, (T*)dx, (T*)dres, gamma, beta,
+                                                                smean, sinv, dgamma, dbeta, nvec, C, relu, 1.f / (float)rows);
+  else
+    bn_apply_bwd_kernel<T, V, false><<<grid, kBnThreads, 0, s>>>((const T*)x, (const T*)y, (const T*)dy, (T*)dx, (T*)dres, gamma, beta,
+                                                                 smean, sinv, dgamma, dbeta, nvec, C, relu, 1.f / (float)rows);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? TMPI_OK : fail(TMPI_ERR_CUDA, "bn backward launch: %s", cudaGetErrorString(e));
 }

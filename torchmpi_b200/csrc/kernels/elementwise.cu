@@ -98,6 +98,139 @@ __global__ void __launch_bounds__(256) xent_kernel(const T* __restrict__ logits,
   }
 }
 
+// One block per row with the row staged in shared memory: the logits are read from HBM once
+// (16-byte loads; the row keeps its global misalignment in shared memory so that the aligned body
+// maps onto aligned shared addresses) and the gradient is written once.  Rows of 50257 bf16 start on
+// 2-byte boundaries only, so a few head and tail elements move as scalars.
+template <typename T, int THREADS>
+__global__ void __launch_bounds__(THREADS) xent_row_smem_kernel(
+    const T* __restrict__ logits, const long long* __restrict__ labels, int rows, int cols,
+    float* __restrict__ loss_out, T* __restrict__ dlogits, float gscale, float* __restrict__ row_loss,
+    unsigned* __restrict__ counter) {
+  extern __shared__ __align__(16) unsigned char s_row_raw[];
+  __shared__ float s_red[32];
+  __shared__ float s_bcast;
+  __shared__ bool s_last;
+  constexpr int V = 16 / sizeof(T);
+  const int r = blockIdx.x, tid = threadIdx.x;
+  const int lane = tid & 31, warp = tid >> 5, nwarp = THREADS >> 5;
+  const T* x = logits + (size_t)r * cols;
+  const unsigned mis = (unsigned)((uintptr_t)x & 15);
+  T* srow = reinterpret_cast<T*>(s_row_raw + mis);
+  int head = mis ? (int)((16 - mis) / sizeof(T)) : 0;
+  if (head > cols) head = cols;
+  const int nvec = (cols - head) / V, tail0 = head + nvec * V;
+  const uint4* gx = reinterpret_cast<const uint4*>(x + head);
+  uint4* sx = reinterpret_cast<uint4*>(srow + head);
+
+  // pass 1: global -> shared, running maximum
+  float m = -INFINITY;
+  for (int c = tid; c < head; c += THREADS) { T v = x[c]; srow[c] = v; m = fmaxf(m, (float)to_acc<T>(v)); }
+  for (int c = tail0 + tid; c < cols; c += THREADS) { T v = x[c]; srow[c] = v; m = fmaxf(m, (float)to_acc<T>(v)); }
+  {
+    constexpr int U = 4;
+    int i = tid;
+    for (; i + (U - 1) * THREADS < nvec; i += U * THREADS) {
+      uint4 u[U];
+#pragma unroll
+      for (int k = 0; k < U; ++k) u[k] = __ldg(gx + i + k * THREADS);
+#pragma unroll
+      for (int k = 0; k < U; ++k) {
+        sx[i + k * THREADS] = u[k];
+        const T* e = reinterpret_cast<const T*>(&u[k]);
+#pragma unroll
+        for (int j = 0; j < V; ++j) m = fmaxf(m, (float)to_acc<T>(e[j]));
+      }
+    }
+    for (; i < nvec; i += THREADS) {
+      uint4 u = __ldg(gx + i);
+      sx[i] = u;
+      const T* e = reinterpret_cast<const T*>(&u);
+#pragma unroll
+      for (int j = 0; j < V; ++j) m = fmaxf(m, (float)to_acc<T>(e[j]));
+    }
+  }
+  for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(~0u, m, o));
+  if (lane == 0) s_red[warp] = m;
+  __syncthreads();                                    // also: the whole row is in shared memory
+  if (tid == 0) {
+    float v = s_red[0];
+    for (int w = 1; w < nwarp; ++w) v = fmaxf(v, s_red[w]);
+    s_bcast = v;
+  }
+  __syncthreads();
+  m = s_bcast;
+
+  // pass 2: sum of exponentials from shared memory
+  float sum = 0.f;
+  for (int c = tid; c < head; c += THREADS) sum += __expf((float)to_acc<T>(srow[c]) - m);
+  for (int c = tail0 + tid; c < cols; c += THREADS) sum += __expf((float)to_acc<T>(srow[c]) - m);
+  for (int i = tid; i < nvec; i += THREADS) {
+    uint4 u = sx[i];
+    const T* e = reinterpret_cast<const T*>(&u);
+#pragma unroll
+    for (int j = 0; j < V; ++j) sum += __expf((float)to_acc<T>(e[j]) - m);
+  }
+  for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(~0u, sum, o);
+  __syncthreads();
+  if (lane == 0) s_red[warp] = sum;
+  __syncthreads();
+  if (tid == 0) {
+    float v = 0.f;
+    for (int w = 0; w < nwarp; ++w) v += s_red[w];
+    s_bcast = v;
+  }
+  __syncthreads();
+  sum = s_bcast;
+  const float inv = 1.f / sum;
+  const int label = (int)labels[r];
+
+  // pass 3: gradient, written once
+  if (dlogits) {
+    T* d = dlogits + (size_t)r * cols;
+    auto grad = [&](T v, int c) {
+      float p = __expf((float)to_acc<T>(v) - m) * inv;
+      return from_acc<T>((typename AccOf<T>::type)((p - (c == label ? 1.f : 0.f)) * gscale));
+    };
+    for (int c = tid; c < head; c += THREADS) d[c] = grad(srow[c], c);
+    for (int c = tail0 + tid; c < cols; c += THREADS) d[c] = grad(srow[c], c);
+    if ((((uintptr_t)d) & 15) == mis) {
+      uint4* gd = reinterpret_cast<uint4*>(d + head);
+      for (int i = tid; i < nvec; i += THREADS) {
+        uint4 u = sx[i], o;
+        const T* e = reinterpret_cast<const T*>(&u);
+        T* q = reinterpret_cast<T*>(&o);
+#pragma unroll
+        for (int j = 0; j < V; ++j) q[j] = grad(e[j], head + i * V + j);
+        gd[i] = o;
+      }
+    } else {
+      for (int c = head + tid; c < tail0; c += THREADS) d[c] = grad(srow[c], c);
+    }
+  }
+  if (tid == 0) {
+    float xl = (label >= 0 && label < cols) ? (float)to_acc<T>(srow[label]) : m;
+    row_loss[r] = __logf(sum) + m - xl;
+    __threadfence();
+    s_last = atomicAdd(counter, 1u) == (unsigned)rows - 1;
+  }
+  __syncthreads();
+  if (s_last) {
+    __threadfence();
+    float v = 0.f;
+    for (int i = tid; i < rows; i += THREADS) v += row_loss[i];   // fixed per-thread order
+    for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(~0u, v, o);
+    if (lane == 0) s_red[warp] = v;
+    __syncthreads();
+    if (tid == 0) {
+      float t = 0.f;
+      for (int w = 0; w < nwarp; ++w) t += s_red[w];
+      loss_out[0] = t;
+      *counter = 0;
+    }
+  }
+}
+
 // ------------------------------------------------------------------ abs-mean / variance
 constexpr int kStatBlocks = 1024;
 constexpr int kStatThreads = 256;
@@ -187,6 +320,27 @@ using namespace tmpi;
     default: return fail(TMPI_ERR_UNSUPPORTED, "dtype %d not supported here", dtype); \
   }
 
+template <typename T>
+static cudaError_t launch_xent(const void* logits, const int64_t* labels, int rows, int cols, float* loss_sum, void* dlogits,
+                               float gscale, float* row_loss, unsigned* counter, cudaStream_t s) {
+  constexpr int kThreads = 512;
+  constexpr size_t kMaxRowBytes = 112 * 1024;          // two such blocks per SM
+  const size_t row_bytes = (size_t)cols * sizeof(T) + 16;
+  if (row_bytes <= kMaxRowBytes && ((uintptr_t)logits % sizeof(T)) == 0) {
+    static bool attr_set = false;                        // per instantiation
+    if (!attr_set) {
+      cudaFuncSetAttribute(xent_row_smem_kernel<T, kThreads>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxRowBytes);
+      attr_set = true;
+    }
+    xent_row_smem_kernel<T, kThreads><<<rows, kThreads, row_bytes, s>>>((const T*)logits, (const long long*)labels, rows, cols,
+                                                                        loss_sum, (T*)dlogits, gscale, row_loss, counter);
+  } else {
+    xent_kernel<T><<<rows, 256, 0, s>>>((const T*)logits, (const long long*)labels, rows, cols, loss_sum, (T*)dlogits, gscale,
+                                        row_loss, counter);
+  }
+  return cudaGetLastError();
+}
+
 extern "C" {
 
 int tmpi_sgd_momentum(void* weight, int wdt, const void* grad, int gdt, void* master, void* momentum, size_t n,
@@ -218,17 +372,13 @@ int tmpi_xent_fwd_bwd(const void* logits, int dtype, const int64_t* labels, int 
   unsigned* counter = (unsigned*)scratch;
   float* row_loss = (float*)((char*)scratch + 256);
   cudaStream_t s = (cudaStream_t)stream;
+  cudaError_t e;
   switch (dtype) {
-    case TMPI_F32: xent_kernel<float><<<rows, 256, 0, s>>>((const float*)logits, (const long long*)labels, rows, cols,
-                                                           loss_sum, (float*)dlogits, gscale, row_loss, counter); break;
-    case TMPI_BF16: xent_kernel<__nv_bfloat16><<<rows, 256, 0, s>>>((const __nv_bfloat16*)logits, (const long long*)labels,
-                                                                    rows, cols, loss_sum, (__nv_bfloat16*)dlogits, gscale,
-                                                                    row_loss, counter); break;
-    case TMPI_F16: xent_kernel<__half><<<rows, 256, 0, s>>>((const __half*)logits, (const long long*)labels, rows, cols,
-                                                            loss_sum, (__half*)dlogits, gscale, row_loss, counter); break;
+    case TMPI_F32: e = launch_xent<float>(logits, labels, rows, cols, loss_sum, dlogits, gscale, row_loss, counter, s); break;
+    case TMPI_BF16: e = launch_xent<__nv_bfloat16>(logits, labels, rows, cols, loss_sum, dlogits, gscale, row_loss, counter, s); break;
+    case TMPI_F16: e = launch_xent<__half>(logits, labels, rows, cols, loss_sum, dlogits, gscale, row_loss, counter, s); break;
     default: return fail(TMPI_ERR_UNSUPPORTED, "xent: dtype %d", dtype);
   }
-  cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? TMPI_OK : cuda_fail(e, "xent launch");
 }
 

@@ -29,7 +29,7 @@ constexpr int EPI_STAGING_BYTES = 2 * BM * 64 * 2;           // two 128 x 64 bf1
 constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + EPI_STAGING_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 constexpr unsigned long long kWaitBudgetNs = 4000000000ull;   // 4 s: far beyond any legitimate wait
 
-enum { EPI_NONE = 0, EPI_BIAS = 1, EPI_GELU = 2, EPI_BIAS_GELU = 3 };
+enum { EPI_NONE = 0, EPI_BIAS = 1, EPI_GELU = 2, EPI_BIAS_GELU = 3, B_IS_KN = 4 /* flag in the same word */ };
 
 struct Shared {
   uint64_t full[STAGES], empty[STAGES], acc_full[2], acc_empty[2];
@@ -43,6 +43,7 @@ struct Problem {
   int epilogue;
   const __nv_bfloat16* bias;   // [N] or nullptr
   int tma_store;               // epilogue writes through TMA (needs 16-byte aligned rows of C)
+  int b_mn;                    // B is given as [K, N] with N contiguous (CTA-pair kernels only)
   int* status;                 // global error word (nullptr: none)
 };
 
@@ -220,6 +221,7 @@ __device__ __forceinline__ void epilogue_tma_impl(Sh* sh, unsigned char* staging
 #pragma unroll 1
     for (int c0 = 0; c0 < BN; c0 += SLICE, ++slice_no) {
       const int col0 = n_blk * BN + c0;
+      if (col0 >= p.N) break;            // uniform over the 128 threads: the rest of the tile lies outside C
       unsigned char* stg = staging + (size_t)(slice_no & 1) * SLICE_BYTES;
       uint32_t r[2][32];
       sm100::tmem_ld_32x32(t_base + c0, r[0]);
@@ -257,7 +259,7 @@ __device__ __forceinline__ void epilogue_tma_impl(Sh* sh, unsigned char* staging
       }
       sm100::fence_proxy_async();        // generic-proxy writes to shared memory -> visible to the TMA unit
       epi_bar_sync();
-      if (leader && col0 < p.N && cmap) {
+      if (leader && cmap) {
         tma_store_2d(cmap, stg, col0, row0);
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
       }

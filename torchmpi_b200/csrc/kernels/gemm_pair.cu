@@ -93,14 +93,18 @@ int launch_gemm_pair(const void* A, const void* B, void* C, const void* bias, in
   CUtensorMap ma, mb, mc;
   int st;
   if ((st = make_tmap_bf16(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)K, gemm2::BM))) return st;
-  if ((st = make_tmap_bf16(&mb, B, (uint64_t)N, (uint64_t)K, (uint64_t)K, gemm2::BN / 2))) return st;
+  const bool b_kn = (epilogue & gemm::B_IS_KN) != 0;       // B given as [K, N], N contiguous
+  if (b_kn) st = make_tmap_bf16(&mb, B, (uint64_t)K, (uint64_t)N, (uint64_t)N, gemm2::BK);
+  else st = make_tmap_bf16(&mb, B, (uint64_t)N, (uint64_t)K, (uint64_t)K, gemm2::BN / 2);
+  if (st) return st;
   if ((st = make_tmap_bf16(&mc, C, (uint64_t)M, (uint64_t)N, (uint64_t)N, gemm2::BM))) return st;
   gemm::Problem p{};
   p.M = M; p.N = N; p.K = K;
   p.tiles_m = (M + 2 * gemm2::BM - 1) / (2 * gemm2::BM);
   p.tiles_n = (N + gemm2::BN - 1) / gemm2::BN;
   p.k_blocks = (K + gemm2::BK - 1) / gemm2::BK;
-  p.epilogue = epilogue;
+  p.epilogue = epilogue & 3;
+  p.b_mn = b_kn ? 1 : 0;
   p.bias = (const __nv_bfloat16*)bias;
   p.tma_store = 1;
   p.status = status_word;

@@ -137,6 +137,7 @@ int tmpi_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int 
   if ((epilogue & gemm::EPI_BIAS) && !bias) return fail(TMPI_ERR_INVALID, "gemm: bias epilogue without bias");
   if (tunable("gemm_pair") && gemm_pair_applicable(C, M, N, K))
     return launch_gemm_pair(A, B, C, bias, M, N, K, epilogue, gemm_status_word(), (cudaStream_t)stream);
+  if (epilogue & gemm::B_IS_KN) return fail(TMPI_ERR_UNSUPPORTED, "gemm: B as [K, N] needs the CTA-pair kernel (M, N >= 256, N %% 8 == 0)");
   CUtensorMap ma, mb;
   int st = make_tmap_bf16(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)K, gemm::BM);
   if (st) return st;

@@ -118,11 +118,27 @@ __device__ __forceinline__ uint64_t make_desc_sw128(uint32_t smem_addr) {
   return d;
 }
 
-// Instruction descriptor: fp32 accumulate, bf16 x bf16 (or f16 x f16), both operands K-major.
-__host__ __device__ constexpr uint32_t make_idesc_f16(int M, int N, bool bf16) {
+// The same for an operand stored MN-major (the M or N index contiguous, e.g. B given as [K, N]):
+// 64 contiguous elements (128 bytes) per k, eight k per 1024-byte swizzle atom; atoms follow one
+// another along K every `k_atom_stride` bytes (stride offset) and along M/N every `mn_stride` bytes
+// (leading offset).  One MMA of K = 16 spans two atoms along K.
+__device__ __forceinline__ uint64_t make_desc_sw128_mn(uint32_t smem_addr, uint32_t mn_stride, uint32_t k_atom_stride) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)(mn_stride >> 4) << 16;
+  d |= (uint64_t)(k_atom_stride >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+// Instruction descriptor: fp32 accumulate, bf16 x bf16 (or f16 x f16); operands K-major unless
+// b_mn_major says that B is MN-major.
+__host__ __device__ constexpr uint32_t make_idesc_f16(int M, int N, bool bf16, bool b_mn_major = false) {
   return (1u << 4)                                       // D format: f32
          | ((bf16 ? 1u : 0u) << 7)                       // A format
          | ((bf16 ? 1u : 0u) << 10)                      // B format
+         | ((b_mn_major ? 1u : 0u) << 16)                // B major
          | ((uint32_t)(N >> 3) << 17)                    // N / 8
          | ((uint32_t)(M >> 4) << 24);                   // M / 16
 }

@@ -3,8 +3,9 @@
 The reference ships no model beyond a logistic regressor
 (examples/mnist/mnist_allreduce.lua:31); this is the standard architecture
 (He et al. 2015, stride on the 3x3 convolution) written for channels_last bf16
-training.  Convolutions run in cuDNN; batch-norm + ReLU (+ residual add) can run
-as the fused kernels of ``ops.bn_relu`` (``fused_bn=True``).
+training.  With ``fused_bn=True`` batch-norm + ReLU (+ residual add) run as the fused kernels of
+``ops.bn_relu``, the max-pool as ``ops.pool`` and the stem convolution as im2col + tcgen05 GEMM
+(``ops.stem_conv``); the other convolutions run in cuDNN.
 """
 from __future__ import annotations
 
@@ -57,7 +58,11 @@ class ResNet(nn.Module):
         super().__init__()
         self.fused = fused_bn
         self.inplanes = width
-        self.conv1 = nn.Conv2d(3, width, 7, stride=2, padding=3, bias=False)
+        if fused_bn:
+            from ..ops.stem_conv import StemConv7x7
+            self.conv1 = StemConv7x7(width)           # im2col + tensor-core GEMM; same parameter as the Conv2d
+        else:
+            self.conv1 = nn.Conv2d(3, width, 7, stride=2, padding=3, bias=False)
         self.bn1 = _bn(width, fused_bn, relu=True)
         if fused_bn:
             from ..ops.pool import MaxPool2d

@@ -2,8 +2,8 @@
 
 ``matmul_nt(a, b)`` computes ``a @ b.T`` for row-major ``a [M, K]`` and ``b [N, K]`` (K contiguous,
 bf16), optionally with bias and GELU in the epilogue.  ``linear(x, w, bias, gelu)`` is the autograd
-version: backward runs the same kernel on transposed copies (``dX = dY @ W`` as
-``matmul_nt(dY, W.T)``, ``dW = dY.T @ X`` as ``matmul_nt(dY.T, X.T)``).
+version: ``dX = dY @ W`` reads W as it lies (``matmul_nn``); ``dW = dY.T @ X`` runs the same kernel
+on transposed copies.
 """
 from __future__ import annotations
 
@@ -14,6 +14,7 @@ import torch
 from .._lib import lib, check, has_symbol, stream_ptr, TorchMPIError
 
 EPI_NONE, EPI_BIAS, EPI_GELU = 0, 1, 2
+B_IS_KN = 4          # flag in the same word: the second operand is [K, N] with N contiguous
 launch_count = 0
 
 
@@ -39,6 +40,29 @@ def matmul_nt(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor] = N
     epi = (EPI_BIAS if bias is not None else 0) | (EPI_GELU if gelu else 0)
     check(lib.tmpi_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(),
                              bias.contiguous().data_ptr() if bias is not None else None, M, N, K, epi, stream_ptr()))
+    launch_count += 1
+    return out
+
+
+def pair_kernel_takes(M: int, N: int, K: int) -> bool:
+    """Shapes for which the CTA-pair kernel (and with it the ``[K, N]`` operand form) is available."""
+    from .. import config
+    return bool(config.get("gemm_pair")) and M >= 256 and N >= 256 and N % 8 == 0 and K % 8 == 0
+
+
+def matmul_nn(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``a @ b`` for row-major ``a [M, K]`` and ``b [K, N]`` (N contiguous): the kernel reads ``b`` as it
+    lies, through an MN-major shared-memory descriptor, where ``matmul_nt`` would need a transposed
+    copy.  Shapes the CTA-pair kernel does not take fall back to that copy."""
+    global launch_count
+    a, b = a.contiguous(), b.contiguous()
+    M, K = a.shape
+    N = b.shape[1]
+    if not (pair_kernel_takes(M, N, K) and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.is_cuda):
+        return matmul_nt(a, b.t().contiguous(), out=out)
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+    check(lib.tmpi_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), None, M, N, K, B_IS_KN, stream_ptr()))
     launch_count += 1
     return out
 
@@ -70,7 +94,7 @@ class _LinearFn(torch.autograd.Function):
         dy2 = dy.reshape(-1, dy.shape[-1]).contiguous()
         if ctx.gelu:
             dy2 = torch.ops.aten.gelu_backward(dy2, z)
-        dx = matmul_nt(dy2, w.t().contiguous()) if ctx.needs_input_grad[0] else None
+        dx = matmul_nn(dy2, w) if ctx.needs_input_grad[0] else None
         dw = matmul_nt(dy2.t().contiguous(), x2.t().contiguous()) if ctx.needs_input_grad[1] else None
         db = dy2.sum(0) if ctx.has_bias and ctx.needs_input_grad[2] else None
         return (dx.reshape(ctx.shape) if dx is not None else None), dw, db, None

@@ -101,6 +101,8 @@ def main():
               for _ in range(args.layers // 2)]
         w2 = [(torch.randn(D, f, device=dev) / math.sqrt(F)).to(torch.bfloat16).requires_grad_(True)
               for _ in range(args.layers // 2)]
+        b1 = [torch.zeros(f, device=dev, dtype=torch.bfloat16, requires_grad=True) for _ in w1]
+        b2 = [torch.zeros(D, device=dev, dtype=torch.bfloat16, requires_grad=True) for _ in w1]
 
         class AG(torch.autograd.Function):
             @staticmethod
@@ -130,8 +132,9 @@ def main():
 
         def step():
             h = x
-            for a, b in zip(w1, w2):
-                h = RS.apply(torch.nn.functional.gelu(AG.apply(h) @ a.t()) @ b.t())
+            lin = torch.nn.functional.linear
+            for a, ba, b, bb in zip(w1, b1, w2, b2):          # the same block: biases on both layers
+                h = RS.apply(lin(torch.nn.functional.gelu(lin(AG.apply(h), a, ba)), b)) + bb
             h.backward(dy)
         ms = timed(step, args.warmup, args.iters)
         flops = (args.layers // 2) * 6 * 2.0 * M * D * f

@@ -40,7 +40,7 @@ _i, _sz, _vp = C.c_int, C.c_size_t, C.c_void_p
 _gp = C.POINTER(_lib.Group)
 _ag_gemm = _fn("tmpi_cuda_ag_gemm", _i, [_sz, _sz, _vp, _vp, _vp, _i, _i, _i, _i, _i, _gp, _vp]) \
     if _lib.has_symbol("tmpi_cuda_ag_gemm") else None
-_gemm_rs = _fn("tmpi_cuda_gemm_rs", _i, [_vp, _vp, _sz, _vp, _i, _i, _i, _gp, _vp]) \
+_gemm_rs = _fn("tmpi_cuda_gemm_rs", _i, [_vp, _vp, _sz, _vp, _i, _i, _i, _i, _gp, _vp]) \
     if _lib.has_symbol("tmpi_cuda_gemm_rs") else None
 _fused_status = _fn("tmpi_cuda_fused_gemm_status", _i, []) if _lib.has_symbol("tmpi_cuda_fused_gemm_status") else None
 
@@ -75,28 +75,39 @@ class TPGroup:
         """A gathered-activation buffer [M, D] that a block keeps for its backward pass."""
         return self._alloc(self.M * self.d)
 
+    def takes_kn(self) -> bool:
+        """Whether the fused kernels accept the weight as ``[K, N]`` (the CTA-pair kernels do)."""
+        from .. import config
+        return bool(config.get("gemm_pair")) and self.rows % 256 == 0
+
     def ag_gemm(self, shard: torch.Tensor, full_off: int, full_buf: torch.Tensor, w: torch.Tensor,
-                bias: Optional[torch.Tensor], gelu: bool = False) -> torch.Tensor:
-        """``act(all_gather(shard) @ w.T + bias)``; the gathered operand is left in ``full_buf``."""
+                bias: Optional[torch.Tensor], gelu: bool = False, w_is_kn: bool = False) -> torch.Tensor:
+        """``act(all_gather(shard) @ w.T + bias)``; the gathered operand is left in ``full_buf``.
+        ``w_is_kn``: ``w`` is ``[K, N]`` and the product is ``all_gather(shard) @ w``."""
         global launch_count
         self.shard_buf[:shard.numel()].copy_(shard.reshape(-1))
-        N, K = w.shape
+        if w_is_kn and not self.takes_kn():
+            w, w_is_kn = w.t().contiguous(), False
+        K, N = w.shape if w_is_kn else (w.shape[1], w.shape[0])
         out = torch.empty((self.M, N), dtype=torch.bfloat16, device=shard.device)
-        epi = (1 if bias is not None else 0) | (2 if gelu else 0)
+        epi = (1 if bias is not None else 0) | (2 if gelu else 0) | (4 if w_is_kn else 0)
         check(_ag_gemm(self.shard_off, full_off, w.data_ptr(), out.data_ptr(),
                        bias.data_ptr() if bias is not None else None, self.M, N, K, epi, self.n_comm,
                        C.byref(self._group), stream_ptr()))
         launch_count += 1
         return out
 
-    def gemm_rs(self, a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-        """``reduce_scatter_rows(a @ w.T)``: this rank's [rows, N] slice of the sum over ranks."""
+    def gemm_rs(self, a: torch.Tensor, w: torch.Tensor, w_is_kn: bool = False) -> torch.Tensor:
+        """``reduce_scatter_rows(a @ w.T)``: this rank's [rows, N] slice of the sum over ranks
+        (``a @ w`` for a ``[K, N]`` weight with ``w_is_kn``)."""
         global launch_count
-        N, K = w.shape
+        if w_is_kn and not self.takes_kn():
+            w, w_is_kn = w.t().contiguous(), False
+        K, N = w.shape if w_is_kn else (w.shape[1], w.shape[0])
         assert N == self.d, "gemm_rs output width must be the model width the slot buffer was sized for"
         out = torch.empty((self.rows, N), dtype=torch.bfloat16, device=a.device)
         check(_gemm_rs(a.data_ptr(), w.data_ptr(), self.slots_off, out.data_ptr(), self.M, N, K,
-                       C.byref(self._group), stream_ptr()))
+                       4 if w_is_kn else 0, C.byref(self._group), stream_ptr()))
         launch_count += 1
         return out
 
@@ -126,14 +137,14 @@ class _TPMLPFn(torch.autograd.Function):
         tp: TPGroup = ctx.tp
         x_full = ctx.full_buf[:tp.M * tp.d].view(tp.M, tp.d)
         dy_shard = dy_shard.contiguous()
-        dh = tp.ag_gemm(dy_shard, tp.dfull_off, tp.dfull_buf, w2.t().contiguous(), None)     # [M, F/R]
+        dh = tp.ag_gemm(dy_shard, tp.dfull_off, tp.dfull_buf, w2, None, w_is_kn=True)        # [M, F/R] = dy @ w2
         dy_full = tp.dfull_buf[:tp.M * tp.d].view(tp.M, tp.d)
         # the two weight gradients are plain local GEMMs on operands whose contraction dimension is the
         # slow one: the library GEMM takes them as they lie, without materialising transposes
         dw2 = torch.matmul(dy_full.t(), h)                                                    # [D, F/R]
         db2 = dy_full.sum(0, dtype=torch.float32).to(dy_full.dtype) if ctx.has_b2 else None
         dz = torch.ops.aten.gelu_backward(dh, z)
-        dx = tp.gemm_rs(dz, w1.t().contiguous())                                              # [rows, D]
+        dx = tp.gemm_rs(dz, w1, w_is_kn=True)                                                 # [rows, D] = dz @ w1
         dw1 = torch.matmul(dz.t(), x_full)                                                    # [F/R, D]
         db1 = dz.sum(0, dtype=torch.float32).to(dz.dtype) if ctx.has_b1 else None
         return dx, dw1, db1, dw2, db2, None, None, None
