@@ -57,14 +57,14 @@ __global__ void __launch_bounds__(kBnThreads, 4) bn_reduce_kernel(
       for (int k = 0; k < V; ++k) { sc[k] = is[k] * gamma[cv * V + k]; sh[k] = beta[cv * V + k] - mu[k] * sc[k]; }
     }
   }
-  for (size_t v = T0; v < nvec; v += stride) {
-    Pack<T, V> xv = ld_pack<T, V>(x + v * V);
+  // U independent vectors per thread and iteration: the loads of all of them are issued before
+  // the first use, so a thread keeps U (forward) or up to 3U (backward) 16-byte loads in flight
+  constexpr int U = BWD ? 1 : 4;       // backward already has 2-3 loads per vector and no registers to spare
+  auto accumulate = [&](const Pack<T, V>& xv, const Pack<T, V>& gv, const Pack<T, V>& yv) {
     if (!BWD) {
 #pragma unroll
       for (int k = 0; k < V; ++k) { float f = (float)to_acc<T>(xv.v[k]); a[k] += f; b[k] += f * f; }
     } else {
-      Pack<T, V> gv = ld_pack<T, V>(dy + v * V), yv;
-      if (relu && !mask_from_x) yv = ld_pack<T, V>(y + v * V);
 #pragma unroll
       for (int k = 0; k < V; ++k) {
         float g = (float)to_acc<T>(gv.v[k]);
@@ -75,6 +75,28 @@ __global__ void __launch_bounds__(kBnThreads, 4) bn_reduce_kernel(
         b[k] += g * ((float)to_acc<T>(xv.v[k]) - mu[k]) * is[k];
       }
     }
+  };
+  size_t v = T0;
+  for (; v + (U - 1) * stride < nvec; v += U * stride) {
+    Pack<T, V> xv[U], gv[U], yv[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      xv[u] = ld_pack<T, V>(x + (v + u * stride) * V);
+      if (BWD) {
+        gv[u] = ld_pack<T, V>(dy + (v + u * stride) * V);
+        if (relu && !mask_from_x) yv[u] = ld_pack<T, V>(y + (v + u * stride) * V);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) accumulate(xv[u], gv[u], yv[u]);
+  }
+  for (; v < nvec; v += stride) {
+    Pack<T, V> xv = ld_pack<T, V>(x + v * V), gv, yv;
+    if (BWD) {
+      gv = ld_pack<T, V>(dy + v * V);
+      if (relu && !mask_from_x) yv = ld_pack<T, V>(y + v * V);
+    }
+    accumulate(xv, gv, yv);
   }
   __shared__ float s[kBnThreads][2 * V + 1];
 #pragma unroll

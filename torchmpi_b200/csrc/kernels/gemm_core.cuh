@@ -44,6 +44,8 @@ struct Problem {
   const __nv_bfloat16* bias;   // [N] or nullptr
   int tma_store;               // epilogue writes through TMA (needs 16-byte aligned rows of C)
   int b_mn;                    // B is given as [K, N] with N contiguous (CTA-pair kernels only)
+  int mma_n;                   // single-CTA kernel, narrow outputs: rows of B staged per tile and N of the MMA
+                               // (a multiple of 16 below BN); 0 = BN
   int* status;                 // global error word (nullptr: none)
 };
 
@@ -89,7 +91,7 @@ __device__ __forceinline__ void producer(Shared* sh, unsigned char* tiles, const
     for (int kb = 0; kb < p.k_blocks; ++kb) {
       if (!sm100::mbar_wait(&sh->empty[stage], phase ^ 1, kWaitBudgetNs) || sh->error) { fail(sh, p, 2); return; }
       unsigned char* a_dst = tiles + (size_t)stage * STAGE_BYTES;
-      sm100::mbar_expect_tx(&sh->full[stage], STAGE_BYTES);
+      sm100::mbar_expect_tx(&sh->full[stage], A_BYTES + (p.mma_n ? p.mma_n : BN) * BK * 2);
       sm100::tma_load_2d(a_dst, a_map, kb * BK, a_row0, &sh->full[stage]);
       sm100::tma_load_2d(a_dst + A_BYTES, mb, kb * BK, n_blk * BN, &sh->full[stage]);
       if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -99,7 +101,7 @@ __device__ __forceinline__ void producer(Shared* sh, unsigned char* tiles, const
 
 template <typename TileOrder>
 __device__ __forceinline__ void mma_issuer(Shared* sh, unsigned char* tiles, const Problem& p, TileOrder order) {
-  constexpr uint32_t idesc = sm100::make_idesc_f16(BM, BN, true);
+  const uint32_t idesc = sm100::make_idesc_f16(BM, p.mma_n ? p.mma_n : BN, true);
   int stage = 0;
   uint32_t phase = 0;
   int m_blk, n_blk;

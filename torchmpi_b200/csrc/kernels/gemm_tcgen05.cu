@@ -141,9 +141,12 @@ int tmpi_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int 
   CUtensorMap ma, mb;
   int st = make_tmap_bf16(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)K, gemm::BM);
   if (st) return st;
-  st = make_tmap_bf16(&mb, B, (uint64_t)N, (uint64_t)K, (uint64_t)K, gemm::BN);
+  // a narrow output (one column tile, N <= 128) stages and multiplies only the rows of B that exist
+  const int mma_n = N <= gemm::BN / 2 ? (N + 15) / 16 * 16 : 0;
+  st = make_tmap_bf16(&mb, B, (uint64_t)N, (uint64_t)K, (uint64_t)K, mma_n ? mma_n : gemm::BN);
   if (st) return st;
   gemm::Problem p{};
+  p.mma_n = mma_n;
   p.M = M; p.N = N; p.K = K;
   p.tiles_m = (M + gemm::BM - 1) / gemm::BM;
   p.tiles_n = (N + gemm::BN - 1) / gemm::BN;

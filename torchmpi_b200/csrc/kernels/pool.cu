@@ -16,27 +16,30 @@ namespace tmpi {
 
 struct PoolDims { int N, H, W, C, OH, OW, k, s, p; };
 
+// One block per (image, output row) forward and per (image, input row) backward: the row index comes
+// from blockIdx and the position inside the row from 32-bit arithmetic (a flat 64-bit index with
+// three run-time divisions per element cost more than the memory traffic).
 template <typename T, int V>
 __global__ void __launch_bounds__(256) maxpool_fwd_kernel(const T* __restrict__ x, T* __restrict__ y,
                                                           unsigned char* __restrict__ idx, PoolDims d) {
   const int cvn = d.C / V;
-  const size_t total = (size_t)d.N * d.OH * d.OW * cvn;
-  for (size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (size_t)gridDim.x * blockDim.x) {
-    const int cv = (int)(t % cvn);
-    size_t r = t / cvn;
-    const int ow = (int)(r % d.OW); r /= d.OW;
-    const int oh = (int)(r % d.OH);
-    const int n = (int)(r / d.OH);
+  const int n = blockIdx.x / d.OH, oh = blockIdx.x % d.OH;
+  const int ih0 = oh * d.s - d.p;
+  const T* xin = x + (size_t)n * d.H * d.W * d.C;
+  const size_t orow = ((size_t)n * d.OH + oh) * d.OW * d.C;
+  for (int t = threadIdx.x; t < d.OW * cvn; t += blockDim.x) {
+    const int ow = t / cvn, cv = t - ow * cvn;
+    const int iw0 = ow * d.s - d.p;
     float best[V];
     unsigned char bi[V];
     bool first = true;
     for (int kh = 0; kh < d.k; ++kh) {
-      const int ih = oh * d.s - d.p + kh;
+      const int ih = ih0 + kh;
       if (ih < 0 || ih >= d.H) continue;
       for (int kw = 0; kw < d.k; ++kw) {
-        const int iw = ow * d.s - d.p + kw;
+        const int iw = iw0 + kw;
         if (iw < 0 || iw >= d.W) continue;
-        Pack<T, V> v = ld_pack<T, V>(x + (((size_t)n * d.H + ih) * d.W + iw) * d.C + (size_t)cv * V);
+        Pack<T, V> v = ld_pack<T, V>(xin + ((size_t)ih * d.W + iw) * d.C + cv * V);
 #pragma unroll
         for (int c = 0; c < V; ++c) {
           const float f = (float)to_acc<T>(v.v[c]);
@@ -49,8 +52,8 @@ __global__ void __launch_bounds__(256) maxpool_fwd_kernel(const T* __restrict__ 
     Pack<unsigned char, V> oi;
 #pragma unroll
     for (int c = 0; c < V; ++c) { out.v[c] = from_acc<T>((typename AccOf<T>::type)best[c]); oi.v[c] = bi[c]; }
-    st_pack<T, V>(y + t * V, out);
-    st_pack<unsigned char, V>(idx + t * V, oi);
+    st_pack<T, V>(y + orow + (size_t)t * V, out);
+    st_pack<unsigned char, V>(idx + orow + (size_t)t * V, oi);
   }
 }
 
@@ -58,24 +61,23 @@ template <typename T, int V>
 __global__ void __launch_bounds__(256) maxpool_bwd_kernel(const T* __restrict__ dy, const unsigned char* __restrict__ idx,
                                                           T* __restrict__ dx, PoolDims d) {
   const int cvn = d.C / V;
-  const size_t total = (size_t)d.N * d.H * d.W * cvn;
-  for (size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (size_t)gridDim.x * blockDim.x) {
-    const int cv = (int)(t % cvn);
-    size_t r = t / cvn;
-    const int iw = (int)(r % d.W); r /= d.W;
-    const int ih = (int)(r % d.H);
-    const int n = (int)(r / d.H);
+  const int n = blockIdx.x / d.H, ih = blockIdx.x % d.H;
+  // outputs whose window [o*s - p, o*s - p + k) contains the input coordinate
+  int oh_lo = ih + d.p - d.k + 1; oh_lo = oh_lo <= 0 ? 0 : (oh_lo + d.s - 1) / d.s;
+  const int oh_hi = min((ih + d.p) / d.s, d.OH - 1);
+  const size_t obase = (size_t)n * d.OH * d.OW * d.C;
+  const size_t irow = ((size_t)n * d.H + ih) * d.W * d.C;
+  for (int t = threadIdx.x; t < d.W * cvn; t += blockDim.x) {
+    const int iw = t / cvn, cv = t - iw * cvn;
+    int ow_lo = iw + d.p - d.k + 1; ow_lo = ow_lo <= 0 ? 0 : (ow_lo + d.s - 1) / d.s;
+    const int ow_hi = min((iw + d.p) / d.s, d.OW - 1);
     float acc[V];
 #pragma unroll
     for (int c = 0; c < V; ++c) acc[c] = 0.f;
-    // outputs whose window [o*s - p, o*s - p + k) contains the input coordinate
-    int oh_lo = ih + d.p - d.k + 1; oh_lo = oh_lo <= 0 ? 0 : (oh_lo + d.s - 1) / d.s;
-    int ow_lo = iw + d.p - d.k + 1; ow_lo = ow_lo <= 0 ? 0 : (ow_lo + d.s - 1) / d.s;
-    const int oh_hi = min((ih + d.p) / d.s, d.OH - 1), ow_hi = min((iw + d.p) / d.s, d.OW - 1);
     for (int oh = oh_lo; oh <= oh_hi; ++oh)
       for (int ow = ow_lo; ow <= ow_hi; ++ow) {
         const unsigned char w = (unsigned char)((ih - (oh * d.s - d.p)) * d.k + (iw - (ow * d.s - d.p)));
-        const size_t o = ((((size_t)n * d.OH + oh) * d.OW + ow) * cvn + cv) * V;
+        const size_t o = obase + ((size_t)(oh * d.OW + ow) * cvn + cv) * V;
         Pack<unsigned char, V> iv = ld_pack<unsigned char, V>(idx + o);
         Pack<T, V> gv = ld_pack<T, V>(dy + o);
 #pragma unroll
@@ -85,7 +87,7 @@ __global__ void __launch_bounds__(256) maxpool_bwd_kernel(const T* __restrict__ 
     Pack<T, V> out;
 #pragma unroll
     for (int c = 0; c < V; ++c) out.v[c] = from_acc<T>((typename AccOf<T>::type)acc[c]);
-    st_pack<T, V>(dx + t * V, out);
+    st_pack<T, V>(dx + irow + (size_t)t * V, out);
   }
 }
 
@@ -94,8 +96,9 @@ static int pool_launch(bool fwd, const void* a, void* b, void* idx, PoolDims d, 
   constexpr int V = 16 / sizeof(T);
   if (d.C % V) return fail(TMPI_ERR_INVALID, "maxpool: C=%d must be a multiple of %d", d.C, V);
   if (d.k * d.k > 255) return fail(TMPI_ERR_INVALID, "maxpool: window too large");
-  size_t total = (size_t)d.N * (fwd ? d.OH * d.OW : d.H * d.W) * (d.C / V);
-  int grid = (int)std::max<size_t>(1, std::min<size_t>((total + 255) / 256, 148 * 16));
+  const long long rows = (long long)d.N * (fwd ? d.OH : d.H);
+  if (rows < 1 || rows > 0x7fffffffLL) return fail(TMPI_ERR_INVALID, "maxpool: %lld rows", rows);
+  int grid = (int)rows;
   if (fwd) maxpool_fwd_kernel<T, V><<<grid, 256, 0, s>>>((const T*)a, (T*)b, (unsigned char*)idx, d);
   else maxpool_bwd_kernel<T, V><<<grid, 256, 0, s>>>((const T*)a, (const unsigned char*)idx, (T*)b, d);
   cudaError_t e = cudaGetLastError();
