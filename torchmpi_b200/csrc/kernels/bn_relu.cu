@@ -77,6 +77,7 @@ __global__ void __launch_bounds__(kBnThreads, 4) bn_reduce_kernel(
     }
   };
   size_t v = T0;
+  if constexpr (U > 1)
   for (; v + (U - 1) * stride < nvec; v += U * stride) {
     Pack<T, V> xv[U], gv[U], yv[U];
 #pragma unroll

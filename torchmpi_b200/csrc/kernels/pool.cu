@@ -19,7 +19,8 @@ struct PoolDims { int N, H, W, C, OH, OW, k, s, p; };
 // One block per (image, output row) forward and per (image, input row) backward: the row index comes
 // from blockIdx and the position inside the row from 32-bit arithmetic (a flat 64-bit index with
 // three run-time divisions per element cost more than the memory traffic).
-template <typename T, int V>
+// K3: the window is 3 x 3 (all nine loads are issued before the first comparison).
+template <typename T, int V, bool K3>
 __global__ void __launch_bounds__(256) maxpool_fwd_kernel(const T* __restrict__ x, T* __restrict__ y,
                                                           unsigned char* __restrict__ idx, PoolDims d) {
   const int cvn = d.C / V;
@@ -33,6 +34,26 @@ __global__ void __launch_bounds__(256) maxpool_fwd_kernel(const T* __restrict__ 
     float best[V];
     unsigned char bi[V];
     bool first = true;
+    if constexpr (K3) {
+      Pack<T, V> win[9];
+      bool ok[9];
+#pragma unroll
+      for (int q = 0; q < 9; ++q) {
+        const int ih = ih0 + q / 3, iw = iw0 + q % 3;
+        ok[q] = ih >= 0 && ih < d.H && iw >= 0 && iw < d.W;
+        if (ok[q]) win[q] = ld_pack<T, V>(xin + ((size_t)ih * d.W + iw) * d.C + cv * V);
+      }
+#pragma unroll
+      for (int q = 0; q < 9; ++q) {
+        if (!ok[q]) continue;
+#pragma unroll
+        for (int c = 0; c < V; ++c) {
+          const float f = (float)to_acc<T>(win[q].v[c]);
+          if (first || f > best[c] || f != f) { best[c] = f; bi[c] = (unsigned char)q; }
+        }
+        first = false;
+      }
+    } else
     for (int kh = 0; kh < d.k; ++kh) {
       const int ih = ih0 + kh;
       if (ih < 0 || ih >= d.H) continue;
@@ -57,7 +78,8 @@ __global__ void __launch_bounds__(256) maxpool_fwd_kernel(const T* __restrict__ 
   }
 }
 
-template <typename T, int V>
+// C2: at most two outputs per axis cover an input (k <= 2 s): their loads are issued together.
+template <typename T, int V, bool C2>
 __global__ void __launch_bounds__(256) maxpool_bwd_kernel(const T* __restrict__ dy, const unsigned char* __restrict__ idx,
                                                           T* __restrict__ dx, PoolDims d) {
   const int cvn = d.C / V;
@@ -74,6 +96,30 @@ __global__ void __launch_bounds__(256) maxpool_bwd_kernel(const T* __restrict__ 
     float acc[V];
 #pragma unroll
     for (int c = 0; c < V; ++c) acc[c] = 0.f;
+    if constexpr (C2) {
+      Pack<unsigned char, V> iv[4];
+      Pack<T, V> gv[4];
+      bool ok[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int oh = oh_lo + (q >> 1), ow = ow_lo + (q & 1);
+        ok[q] = oh <= oh_hi && ow <= ow_hi;
+        if (ok[q]) {
+          const size_t o = obase + ((size_t)(oh * d.OW + ow) * cvn + cv) * V;
+          iv[q] = ld_pack<unsigned char, V>(idx + o);
+          gv[q] = ld_pack<T, V>(dy + o);
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        if (!ok[q]) continue;
+        const int oh = oh_lo + (q >> 1), ow = ow_lo + (q & 1);
+        const unsigned char w = (unsigned char)((ih - (oh * d.s - d.p)) * d.k + (iw - (ow * d.s - d.p)));
+#pragma unroll
+        for (int c = 0; c < V; ++c)
+          if (iv[q].v[c] == w) acc[c] += (float)to_acc<T>(gv[q].v[c]);
+      }
+    } else
     for (int oh = oh_lo; oh <= oh_hi; ++oh)
       for (int ow = ow_lo; ow <= ow_hi; ++ow) {
         const unsigned char w = (unsigned char)((ih - (oh * d.s - d.p)) * d.k + (iw - (ow * d.s - d.p)));
@@ -99,8 +145,10 @@ static int pool_launch(bool fwd, const void* a, void* b, void* idx, PoolDims d, 
   const long long rows = (long long)d.N * (fwd ? d.OH : d.H);
   if (rows < 1 || rows > 0x7fffffffLL) return fail(TMPI_ERR_INVALID, "maxpool: %lld rows", rows);
   int grid = (int)rows;
-  if (fwd) maxpool_fwd_kernel<T, V><<<grid, 256, 0, s>>>((const T*)a, (T*)b, (unsigned char*)idx, d);
-  else maxpool_bwd_kernel<T, V><<<grid, 256, 0, s>>>((const T*)a, (const unsigned char*)idx, (T*)b, d);
+  if (fwd && d.k == 3) maxpool_fwd_kernel<T, V, true><<<grid, 256, 0, s>>>((const T*)a, (T*)b, (unsigned char*)idx, d);
+  else if (fwd) maxpool_fwd_kernel<T, V, false><<<grid, 256, 0, s>>>((const T*)a, (T*)b, (unsigned char*)idx, d);
+  else if (d.k <= 2 * d.s) maxpool_bwd_kernel<T, V, true><<<grid, 256, 0, s>>>((const T*)a, (const unsigned char*)idx, (T*)b, d);
+  else maxpool_bwd_kernel<T, V, false><<<grid, 256, 0, s>>>((const T*)a, (const unsigned char*)idx, (T*)b, d);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? TMPI_OK : fail(TMPI_ERR_CUDA, "maxpool launch: %s", cudaGetErrorString(e));
 }
