@@ -39,6 +39,7 @@ def parse():
     ap.add_argument("--fused-bn", type=int, default=int(os.environ.get("TORCHMPI_FUSED_BN", "1")))
     ap.add_argument("--bucket-mb", type=int, default=0)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--set", action="append", default=[], metavar="NAME=VALUE", help="set a runtime tunable")
     ap.add_argument("--profile-one-step", action="store_true",
                     help="after the warm-up run one step between cudaProfilerStart/Stop and exit (no timing)")
     return ap.parse_args()
@@ -113,6 +114,9 @@ def main():
         print(f"bench.py: --gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run", file=sys.stderr)
         return 2
     config.set("heap_bytes", 1 << 30)
+    for kv in args.set:
+        name, _, value = kv.partition("=")
+        config.set(name, int(value))
     if args.bucket_mb:
         config.set("bucket_bytes", args.bucket_mb << 20)
     mpi.start(with_cuda=True)

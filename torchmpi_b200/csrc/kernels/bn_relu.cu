@@ -12,8 +12,6 @@
 // writes of the activation; the reference has no such ops at all (its only kernel is `out += in`,
 // lib/detail/reduce_kernel.cu).  Every thread owns a fixed group of V channels, so partial sums
 // stay in registers; block partials go to scratch and are reduced in block order (deterministic).
-// (Walking the statistics pass from the end of the tensor towards its start, to begin on lines the
-// producer left in L2, was measured: the descending walk itself ran a third slower from HBM.)
 // A ReLU layer without a residual does not read y in backward: y > 0 exactly when the affine
 // transform of x is positive, and x is read anyway.
 #include "vec.cuh"
@@ -40,11 +38,17 @@ __global__ void __launch_bounds__(kBnThreads, 4) bn_reduce_kernel(
     const T* __restrict__ x, const T* __restrict__ y, const T* __restrict__ dy,
     const float* __restrict__ mean, const float* __restrict__ invstd,
     const float* __restrict__ gamma, const float* __restrict__ beta,
-    size_t nvec, int C, int relu, float* __restrict__ partial) {
+    size_t nvec, int C, int relu, int reverse, float* __restrict__ partial) {
   const int cvn = C / V;
   const size_t T0 = (size_t)blockIdx.x * kBnThreads + threadIdx.x;
   const size_t stride = (size_t)gridDim.x * kBnThreads;
-  const int cv = (int)(T0 % cvn);                 // fixed: stride is a multiple of cvn
+  // reverse: the walk starts at the end of the tensor (vector nvec-1-T0, then down by the stride), where
+  // the lines the producer wrote last are still in L2; the apply pass that follows walks up from the
+  // start, which this pass read last.  nvec and the stride are multiples of cvn: the group stays fixed.
+  const int cv = reverse ? cvn - 1 - (int)(T0 % cvn) : (int)(T0 % cvn);
+  const T* xe = x + (nvec - 1) * V;
+  const T* ge = BWD ? dy + (nvec - 1) * V : nullptr;
+  const T* ye = (BWD && y) ? y + (nvec - 1) * V : nullptr;
   constexpr bool mask_from_x = BWD && MASKX;
   float a[V], b[V], mu[V], is[V], sc[V], sh[V];
 #pragma unroll
@@ -82,20 +86,20 @@ __global__ void __launch_bounds__(kBnThreads, 4) bn_reduce_kernel(
     Pack<T, V> xv[U], gv[U], yv[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      xv[u] = ld_pack<T, V>(x + (v + u * stride) * V);
+      xv[u] = ld_pack<T, V>(reverse ? xe - (v + u * stride) * V : x + (v + u * stride) * V);
       if (BWD) {
-        gv[u] = ld_pack<T, V>(dy + (v + u * stride) * V);
-        if (relu && !mask_from_x) yv[u] = ld_pack<T, V>(y + (v + u * stride) * V);
+        gv[u] = ld_pack<T, V>(reverse ? ge - (v + u * stride) * V : dy + (v + u * stride) * V);
+        if (relu && !mask_from_x) yv[u] = ld_pack<T, V>(reverse ? ye - (v + u * stride) * V : y + (v + u * stride) * V);
       }
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) accumulate(xv[u], gv[u], yv[u]);
   }
   for (; v < nvec; v += stride) {
-    Pack<T, V> xv = ld_pack<T, V>(x + v * V), gv, yv;
+    Pack<T, V> xv = ld_pack<T, V>(reverse ? xe - v * V : x + v * V), gv, yv;
     if (BWD) {
-      gv = ld_pack<T, V>(dy + v * V);
-      if (relu && !mask_from_x) yv = ld_pack<T, V>(y + v * V);
+      gv = ld_pack<T, V>(reverse ? ge - v * V : dy + v * V);
+      if (relu && !mask_from_x) yv = ld_pack<T, V>(reverse ? ye - v * V : y + v * V);
     }
     accumulate(xv, gv, yv);
   }
@@ -107,7 +111,7 @@ __global__ void __launch_bounds__(kBnThreads, 4) bn_reduce_kernel(
   for (int o = threadIdx.x; o < cvn * 2 * V; o += kBnThreads) {
     const int c = o / (2 * V), k = o % (2 * V);   // c: channel group, k: slot
     float t = 0.f;
-    for (int g = c; g < kBnThreads; g += cvn) t += s[g][k];
+    for (int g = reverse ? cvn - 1 - c : c; g < kBnThreads; g += cvn) t += s[g][k];   // the threads whose group is c
     const int which = k / V, ch = c * V + (k % V);
     partial[((size_t)blockIdx.x * 2 + which) * C + ch] = t;
   }
@@ -253,15 +257,18 @@ static int bn_fwd_t(const void* x, const void* res, void* y, const float* gamma,
   if (st) return st;
   size_t nvec = (size_t)rows * (C / V);
   int grid = bn_grid(nvec);
+  const int reverse = tunable("bn_reverse_stats") != 0;
   if (training) {
-    bn_reduce_kernel<T, V, false, false><<<grid, kBnThreads, 0, s>>>((const T*)x, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nvec, C, 0,
+    bn_reduce_kernel<T, V, false, false><<<grid, kBnThreads, 0, s>>>((const T*)x, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nvec, C, 0, reverse,
                                                               (float*)scratch);
     float m = (float)rows;
     bn_finalize_fwd_kernel<<<(C + 31) / 32, dim3(32, 32), 0, s>>>((const float*)scratch, grid, C, 1.f / m,
                                                            rows > 1 ? m / (m - 1.f) : 1.f, eps, momentum, smean, sinv,
                                                            rmean, rvar);
   }
-  bn_apply_fwd_kernel<T, V><<<grid, kBnThreads, 0, s>>>((const T*)x, (const T*)res, (T*)y, gamma, beta, smean, sinv, nvec, C, relu);
+  // the apply pass keeps no partials and needs 32 registers: eight blocks per SM
+  const int apply_grid = (int)std::max<size_t>(1, std::min<size_t>((nvec + kBnThreads - 1) / kBnThreads, 2 * kBnMaxGrid));
+  bn_apply_fwd_kernel<T, V><<<apply_grid, kBnThreads, 0, s>>>((const T*)x, (const T*)res, (T*)y, gamma, beta, smean, sinv, nvec, C, relu);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? TMPI_OK : fail(TMPI_ERR_CUDA, "bn forward launch: %s", cudaGetErrorString(e));
 }
@@ -276,13 +283,14 @@ static int bn_bwd_t(const void* x, const void* y, const void* dy, void* dx, void
   if (relu && !y && (!beta || dres)) return fail(TMPI_ERR_INVALID, "bn backward: without y the layer needs beta and no residual");
   size_t nvec = (size_t)rows * (C / V);
   int grid = bn_grid(nvec);
+  const int reverse = tunable("bn_reverse_stats") != 0;
   const bool maskx = relu && !y;
   if (maskx)
     bn_reduce_kernel<T, V, true, true><<<grid, kBnThreads, 0, s>>>((const T*)x, nullptr, (const T*)dy, smean, sinv, gamma, beta, nvec,
-                                                                   C, relu, (float*)scratch);
+                                                                   C, relu, reverse, (float*)scratch);
   else
     bn_reduce_kernel<T, V, true, false><<<grid, kBnThreads, 0, s>>>((const T*)x, (const T*)y, (const T*)dy, smean, sinv, gamma, beta,
-                                                                    nvec, C, relu, (float*)scratch);
+                                                                    nvec, C, relu, reverse, (float*)scratch);
   bn_finalize_bwd_kernel<<<(C + 31) / 32, dim3(32, 32), 0, s>>>((const float*)scratch, grid, C, dgamma, dbeta);
   if (maskx)
     bn_apply_bwd_kernel<T, V, true><<<grid, kBnThreads, 0, s>>>((const T*)x, nullptr, (const T*)dy, (T*)dx, (T*)dres, gamma, beta,
