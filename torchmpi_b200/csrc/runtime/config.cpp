@@ -44,6 +44,7 @@ Tunable g_tunables[] = {
   {"oneshot_max_bytes", {512 << 10}},      // <= : one-shot push allreduce
   {"nvls_min_bytes", {1 << 20}},           // >= : multimem allreduce when multicast is bound
   {"comm_max_ctas", {64}},                 // CTAs of a stand-alone collective kernel
+  {"ps_max_ctas", {148}},                  // CTAs of a parameter-server push / pull kernel (one per SM: +30 % push bandwidth over 64)
   {"opt_max_ctas", {32}},                  // CTAs of the fused allreduce+SGD kernel (runs beside backward)
   {"comm_threads", {512}},
   {"num_comm_lanes", {2}},                 // ordered launch lanes (stream + flag set each)

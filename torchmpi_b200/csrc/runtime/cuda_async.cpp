@@ -134,7 +134,7 @@ static int ps_launch(size_t shard_off, void* data, size_t n, int dtype, int rule
     if (st) return st;
   }
   a.shard_off = shard_off; a.data = data; a.n = n; a.rule = rule;
-  int grid = grid_for(n / g->nmembers + 1, 512);
+  int grid = grid_for(n / g->nmembers + 1, 512, "ps_max_ctas");
   cudaError_t e = launch_ps(dtype, &a, grid, 512, (cudaStream_t)stream);
   return e == cudaSuccess ? TMPI_OK : cuda_fail(e, "parameter-server kernel launch");
 }

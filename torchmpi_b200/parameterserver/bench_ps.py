@@ -24,7 +24,7 @@ def main():
     ap.add_argument("--max-bytes", type=int, default=1 << 30)
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp32"])
     ap.add_argument("--iters", type=int, default=10)
-    ap.add_argument("--ctas", type=int, default=0, help="CTAs per kernel (default: the comm_max_ctas tunable)")
+    ap.add_argument("--ctas", type=int, default=0, help="CTAs per kernel (default: the ps_max_ctas tunable)")
     ap.add_argument("--link-gbs", type=float, default=770.0)
     args = ap.parse_args()
 
@@ -32,7 +32,7 @@ def main():
     from torchmpi_b200 import config, parameterserver as ps
     config.set("heap_bytes", 2 * args.max_bytes + (512 << 20))
     if args.ctas:
-        config.set("comm_max_ctas", args.ctas)
+        config.set("ps_max_ctas", args.ctas)
     mpi.start(with_cuda=True)
     rank, world, dev = mpi.rank(), mpi.size(), mpi.device
     dt = torch.bfloat16 if args.dtype == "bf16" else torch.float32
@@ -63,7 +63,7 @@ def main():
                 print(json.dumps({"op": name, "dtype": args.dtype, "bytes": size, "world": world,
                                   "us": round(ms.item() * 1e3, 2), "gbs": round(moved / ms.item() / 1e6, 1),
                                   "roofline_frac": round(moved / ms.item() / 1e6 / args.link_gbs, 3),
-                                  "ctas": config.get("comm_max_ctas")}), flush=True)
+                                  "ctas": config.get("ps_max_ctas")}), flush=True)
         ps.free(server)
         del t
         size *= 4
