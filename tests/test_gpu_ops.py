@@ -176,3 +176,39 @@ def test_stem_conv_matches_conv2d():
         rel = (conv.weight.grad.float() - wr.grad).norm() / wr.grad.norm()
         assert rel < 1e-2, (N, H, W, rel.item())
         gemm.check_status()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_bn_relu_maxpool_stage_matches_separate_ops(dtype):
+    """Batch-norm + ReLU + max-pool in one stage against the three PyTorch ops in fp32 on the same input."""
+    from torchmpi_b200.ops.bn_relu import FusedBatchNormReLUMaxPool
+    torch.manual_seed(7)
+    for N, C, H, W in ((4, 64, 112, 112), (2, 16, 33, 47), (3, 32, 16, 16)):
+        x = torch.randn(N, C, H, W, device="cuda").to(dtype).contiguous(memory_format=torch.channels_last).requires_grad_(True)
+        m = FusedBatchNormReLUMaxPool(C).cuda()
+        with torch.no_grad():
+            m.weight.copy_(torch.randn(C).abs() + 0.5)
+            m.weight[::3] *= -1                      # negative scales reverse the order inside a window
+            m.bias.copy_(torch.randn(C) * 0.3)
+        y = m(x)
+        dy = torch.randn_like(y)
+        y.backward(dy)
+        xr = x.detach().float().requires_grad_(True)
+        ref_bn = torch.nn.BatchNorm2d(C).cuda()
+        with torch.no_grad():
+            ref_bn.weight.copy_(m.weight)
+            ref_bn.bias.copy_(m.bias)
+        z = torch.relu(ref_bn(xr))
+        if dtype == torch.bfloat16:
+            z = z + (z.to(dtype).float() - z).detach()      # the stage pools the bf16-rounded activation
+        yr = torch.nn.functional.max_pool2d(z, 3, 2, 1)
+        yr.backward(dy.float())
+        tol = 2e-2 if dtype == torch.bfloat16 else 1e-4
+        assert y.shape == yr.shape
+        assert torch.allclose(y.float(), yr, rtol=tol, atol=tol), (N, C, H, W)
+        assert torch.allclose(m.running_mean, ref_bn.running_mean, atol=1e-4)
+        assert torch.allclose(m.running_var, ref_bn.running_var, atol=1e-3, rtol=1e-3)
+        rel = (x.grad.float() - xr.grad).norm() / xr.grad.norm()
+        assert rel < (2e-2 if dtype == torch.bfloat16 else 1e-4), (N, C, H, W, rel.item())
+        assert torch.allclose(m.weight.grad, ref_bn.weight.grad, rtol=2e-2, atol=2e-2 * ref_bn.weight.grad.abs().max().item())
+        assert torch.allclose(m.bias.grad, ref_bn.bias.grad, rtol=2e-2, atol=2e-2 * ref_bn.bias.grad.abs().max().item())

@@ -177,6 +177,8 @@ _CUDA_PROTOS = {
     "tmpi_bn_relu_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _f, _f, _i, _i, _i, _vp, _vp]),
     "tmpi_bn_relu_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _vp, _vp]),
     "tmpi_bn_scratch_bytes": (_sz, [_i]),
+    "tmpi_bn_relu_pool_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _f, _i, _i, _vp, _vp]),
+    "tmpi_bn_relu_pool_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp]),
     "tmpi_stem_im2col": (_i, [_vp, _vp, _i, _i, _i, _i, _vp]),
     "tmpi_stem_patch_width": (_i, []),
     "tmpi_maxpool_fwd": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp]),

@@ -302,6 +302,237 @@ static int bn_bwd_t(const void* x, const void* y, const void* dy, void* dx, void
   return e == cudaSuccess ? TMPI_OK : fail(TMPI_ERR_CUDA, "bn backward launch: %s", cudaGetErrorString(e));
 }
 
+// ------------------------------------------------------------------ batch-norm + ReLU + max-pool
+// Batch-norm + ReLU + 3x3 / stride-2 / pad-1 max-pool as one stage (the ResNet stem after its
+// convolution), for channels-last activations.  The normalised full-resolution activation is never
+// written: forward reads the convolution output once and writes the pooled tensor and a one-byte
+// window index; backward rebuilds, per input position, the gradient that the pool routes to it
+// (from the pooled gradient and the index, which stay in L2) and the ReLU mask (from x), inside both
+// batch-norm backward passes.  Unfused, the same stage writes and re-reads the full-resolution
+// activation once forward and its gradient twice backward.
+//
+//   z = x * scale[c] + shift[c];  a = max(z, 0);  y[oh, ow] = max over the window of a
+//   idx = position of the first maximum in the window (kh * 3 + kw), as in pool.cu
+//   dz[ih, iw] = (z > 0) * sum over windows (oh, ow) covering (ih, iw) with idx == this position of dy[oh, ow]
+//   then the usual batch-norm backward on dz.
+constexpr int kBpThreads = kBnThreads;   // same partial layout as the kernels above: partial[(block * 2 + which) * C + c]
+
+struct BpDims { int N, H, W, C, OH, OW; };
+
+// forward: one block per (n, oh); thread -> (ow, channel group)
+template <typename T, int V>
+__global__ void __launch_bounds__(kBpThreads) bn_pool_fwd_kernel(
+    const T* __restrict__ x, T* __restrict__ y, unsigned char* __restrict__ idx, const float* __restrict__ gamma,
+    const float* __restrict__ beta, const float* __restrict__ mean, const float* __restrict__ invstd, BpDims d) {
+  const int cvn = d.C / V;
+  const int n = blockIdx.x / d.OH, oh = blockIdx.x % d.OH;
+  const int ih0 = oh * 2 - 1;
+  const T* xin = x + (size_t)n * d.H * d.W * d.C;
+  const size_t orow = ((size_t)n * d.OH + oh) * d.OW * d.C;
+  const int cv = threadIdx.x % cvn;                  // kBpThreads is a multiple of cvn: fixed channel group
+  float sc[V], sh[V];
+#pragma unroll
+  for (int k = 0; k < V; ++k) {
+    const int c = cv * V + k;
+    sc[k] = invstd[c] * gamma[c];
+    sh[k] = beta[c] - mean[c] * sc[k];
+  }
+  for (int t = threadIdx.x; t < d.OW * cvn; t += kBpThreads) {
+    const int ow = t / cvn;
+    const int iw0 = ow * 2 - 1;
+    Pack<T, V> win[9];
+    bool ok[9];
+#pragma unroll
+    for (int q = 0; q < 9; ++q) {
+      const int ih = ih0 + q / 3, iw = iw0 + q % 3;
+      ok[q] = ih >= 0 && ih < d.H && iw >= 0 && iw < d.W;
+      if (ok[q]) win[q] = ld_pack<T, V>(xin + ((size_t)ih * d.W + iw) * d.C + cv * V);
+    }
+    float best[V];
+    unsigned char bi[V];
+    bool first = true;
+#pragma unroll
+    for (int q = 0; q < 9; ++q) {
+      if (!ok[q]) continue;
+#pragma unroll
+      for (int k = 0; k < V; ++k) {
+        // the value the unfused path would have stored: bf16(relu(z))
+        const float a = (float)to_acc<T>(from_acc<T>((typename AccOf<T>::type)fmaxf((float)to_acc<T>(win[q].v[k]) * sc[k] + sh[k], 0.f)));
+        if (first || a > best[k] || a != a) { best[k] = a; bi[k] = (unsigned char)q; }
+      }
+      first = false;
+    }
+    Pack<T, V> out;
+    Pack<unsigned char, V> oi;
+#pragma unroll
+    for (int k = 0; k < V; ++k) { out.v[k] = from_acc<T>((typename AccOf<T>::type)best[k]); oi.v[k] = bi[k]; }
+    st_pack<T, V>(y + orow + (size_t)t * V, out);
+    st_pack<unsigned char, V>(idx + orow + (size_t)t * V, oi);
+  }
+}
+
+// gradient routed by the pool to input position (ih, iw), channel group cv
+template <typename T, int V>
+__device__ __forceinline__ void pooled_grad(const T* __restrict__ dy, const unsigned char* __restrict__ idx, const BpDims& d,
+                                            size_t obase, int ih, int iw, int cv, int cvn, float (&g)[V]) {
+#pragma unroll
+  for (int k = 0; k < V; ++k) g[k] = 0.f;
+  // windows [2o - 1, 2o + 1] containing the coordinate: o in {ceil((i - 1) / 2), floor((i + 1) / 2)}
+  const int oh_lo = ih >> 1, ow_lo = iw >> 1;                       // = ceil((i - 1) / 2) for i >= 0
+  const int oh_hi = min((ih + 1) >> 1, d.OH - 1), ow_hi = min((iw + 1) >> 1, d.OW - 1);
+  Pack<unsigned char, V> iv[4];
+  Pack<T, V> gv[4];
+  bool ok[4];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const int oh = oh_lo + (q >> 1), ow = ow_lo + (q & 1);
+    ok[q] = oh <= oh_hi && ow <= ow_hi;
+    if (ok[q]) {
+      const size_t o = obase + ((size_t)(oh * d.OW + ow) * cvn + cv) * V;
+      iv[q] = ld_pack<unsigned char, V>(idx + o);
+      gv[q] = ld_pack<T, V>(dy + o);
+    }
+  }
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    if (!ok[q]) continue;
+    const int oh = oh_lo + (q >> 1), ow = ow_lo + (q & 1);
+    const unsigned char w = (unsigned char)((ih - (oh * 2 - 1)) * 3 + (iw - (ow * 2 - 1)));
+#pragma unroll
+    for (int k = 0; k < V; ++k)
+      if (iv[q].v[k] == w) g[k] += (float)to_acc<T>(gv[q].v[k]);
+  }
+}
+
+// backward statistics: blocks take input rows (n, ih) round-robin; partial sums per block
+template <typename T, int V>
+__global__ void __launch_bounds__(kBpThreads, 2) bn_pool_bwd_reduce_kernel(
+    const T* __restrict__ x, const T* __restrict__ dy, const unsigned char* __restrict__ idx, const float* __restrict__ gamma,
+    const float* __restrict__ beta, const float* __restrict__ mean, const float* __restrict__ invstd, BpDims d,
+    float* __restrict__ partial) {
+  const int cvn = d.C / V;
+  const int cv = threadIdx.x % cvn;                  // kBpThreads is a multiple of cvn: fixed channel group
+  const int pos0 = threadIdx.x / cvn, pos_step = kBpThreads / cvn;
+  float a[V], b[V], mu[V], is[V], sc[V], sh[V];
+#pragma unroll
+  for (int k = 0; k < V; ++k) {
+    const int c = cv * V + k;
+    a[k] = 0.f; b[k] = 0.f;
+    mu[k] = mean[c]; is[k] = invstd[c];
+    sc[k] = is[k] * gamma[c]; sh[k] = beta[c] - mu[k] * sc[k];
+  }
+  const int rows = d.N * d.H;
+  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+    const int n = r / d.H, ih = r - n * d.H;
+    const size_t obase = (size_t)n * d.OH * d.OW * d.C;
+    const T* xrow = x + (size_t)r * d.W * d.C;
+    for (int iw = pos0; iw < d.W; iw += pos_step) {
+      Pack<T, V> xv = ld_pack<T, V>(xrow + ((size_t)iw * cvn + cv) * V);
+      float g[V];
+      pooled_grad<T, V>(dy, idx, d, obase, ih, iw, cv, cvn, g);
+#pragma unroll
+      for (int k = 0; k < V; ++k) {
+        const float xf = (float)to_acc<T>(xv.v[k]);
+        const float gz = (xf * sc[k] + sh[k] > 0.f) ? g[k] : 0.f;
+        a[k] += gz;
+        b[k] += gz * (xf - mu[k]) * is[k];
+      }
+    }
+  }
+  __shared__ float s[kBpThreads][2 * V + 1];
+#pragma unroll
+  for (int k = 0; k < V; ++k) { s[threadIdx.x][k] = a[k]; s[threadIdx.x][V + k] = b[k]; }
+  __syncthreads();
+  for (int o = threadIdx.x; o < cvn * 2 * V; o += kBpThreads) {
+    const int c = o / (2 * V), k = o % (2 * V);
+    float t = 0.f;
+    for (int g = c; g < kBpThreads; g += cvn) t += s[g][k];
+    const int which = k / V, ch = c * V + (k % V);
+    partial[((size_t)blockIdx.x * 2 + which) * d.C + ch] = t;
+  }
+}
+
+// backward apply: one block per input row
+template <typename T, int V>
+__global__ void __launch_bounds__(kBpThreads, 2) bn_pool_bwd_apply_kernel(
+    const T* __restrict__ x, const T* __restrict__ dy, const unsigned char* __restrict__ idx, T* __restrict__ dx,
+    const float* __restrict__ gamma, const float* __restrict__ beta, const float* __restrict__ mean,
+    const float* __restrict__ invstd, const float* __restrict__ dgamma, const float* __restrict__ dbeta, BpDims d, float inv_m) {
+  const int cvn = d.C / V;
+  const int r = blockIdx.x;
+  const int n = r / d.H, ih = r - n * d.H;
+  const size_t obase = (size_t)n * d.OH * d.OW * d.C;
+  const size_t irow = (size_t)r * d.W * d.C;
+  const int cv = threadIdx.x % cvn;                  // fixed channel group
+  float mu[V], is[V], k1[V], k2[V], k3[V], sh[V];
+#pragma unroll
+  for (int k = 0; k < V; ++k) {
+    const int c = cv * V + k;
+    mu[k] = mean[c]; is[k] = invstd[c];
+    k1[k] = gamma[c] * is[k];
+    k2[k] = dbeta[c] * inv_m;
+    k3[k] = dgamma[c] * inv_m;
+    sh[k] = beta[c] - mu[k] * k1[k];
+  }
+  for (int t = threadIdx.x; t < d.W * cvn; t += kBpThreads) {
+    const int iw = t / cvn;
+    Pack<T, V> xv = ld_pack<T, V>(x + irow + (size_t)t * V), ox;
+    float g[V];
+    pooled_grad<T, V>(dy, idx, d, obase, ih, iw, cv, cvn, g);
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+      const float xf = (float)to_acc<T>(xv.v[k]);
+      const float gz = (xf * k1[k] + sh[k] > 0.f) ? g[k] : 0.f;
+      const float xhat = (xf - mu[k]) * is[k];
+      ox.v[k] = from_acc<T>((typename AccOf<T>::type)(k1[k] * (gz - k2[k] - xhat * k3[k])));
+    }
+    st_pack<T, V>(dx + irow + (size_t)t * V, ox);
+  }
+}
+
+
+template <typename T>
+static int bn_pool_fwd_t(const void* x, void* y, void* idx, const float* gamma, const float* beta, float* rmean, float* rvar,
+                         float* smean, float* sinv, int N, int H, int W, int C, float eps, float momentum, int training,
+                         void* scratch, cudaStream_t s) {
+  constexpr int V = 16 / sizeof(T);
+  const int64_t rows = (int64_t)N * H * W;
+  int st = bn_check(rows, C, V);
+  if (st) return st;
+  BpDims d{N, H, W, C, (H - 1) / 2 + 1, (W - 1) / 2 + 1};
+  if (training) {
+    size_t nvec = (size_t)rows * (C / V);
+    int grid = bn_grid(nvec);
+    bn_reduce_kernel<T, V, false, false><<<grid, kBnThreads, 0, s>>>((const T*)x, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr,
+                                                                     nvec, C, 0, tunable("bn_reverse_stats") != 0, (float*)scratch);
+    float m = (float)rows;
+    bn_finalize_fwd_kernel<<<(C + 31) / 32, dim3(32, 32), 0, s>>>((const float*)scratch, grid, C, 1.f / m,
+                                                           rows > 1 ? m / (m - 1.f) : 1.f, eps, momentum, smean, sinv, rmean, rvar);
+  }
+  bn_pool_fwd_kernel<T, V><<<N * d.OH, kBpThreads, 0, s>>>((const T*)x, (T*)y, (unsigned char*)idx, gamma, beta, smean, sinv, d);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? TMPI_OK : fail(TMPI_ERR_CUDA, "bn+pool forward launch: %s", cudaGetErrorString(e));
+}
+
+template <typename T>
+static int bn_pool_bwd_t(const void* x, const void* dy, const void* idx, void* dx, const float* gamma, const float* beta,
+                         const float* smean, const float* sinv, float* dgamma, float* dbeta, int N, int H, int W, int C,
+                         void* scratch, cudaStream_t s) {
+  constexpr int V = 16 / sizeof(T);
+  const int64_t rows = (int64_t)N * H * W;
+  int st = bn_check(rows, C, V);
+  if (st) return st;
+  BpDims d{N, H, W, C, (H - 1) / 2 + 1, (W - 1) / 2 + 1};
+  const int grid = std::min(N * H, kBnMaxGrid);
+  bn_pool_bwd_reduce_kernel<T, V><<<grid, kBpThreads, 0, s>>>((const T*)x, (const T*)dy, (const unsigned char*)idx, gamma, beta,
+                                                              smean, sinv, d, (float*)scratch);
+  bn_finalize_bwd_kernel<<<(C + 31) / 32, dim3(32, 32), 0, s>>>((const float*)scratch, grid, C, dgamma, dbeta);
+  bn_pool_bwd_apply_kernel<T, V><<<N * H, kBpThreads, 0, s>>>((const T*)x, (const T*)dy, (const unsigned char*)idx, (T*)dx, gamma,
+                                                              beta, smean, sinv, dgamma, dbeta, d, 1.f / (float)rows);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? TMPI_OK : fail(TMPI_ERR_CUDA, "bn+pool backward launch: %s", cudaGetErrorString(e));
+}
+
 }  // namespace tmpi
 
 using namespace tmpi;
@@ -342,6 +573,38 @@ int tmpi_bn_relu_bwd(const void* x, const void* y, const void* dy, void* dx, voi
                                           channels, relu, scratch, s);
   }
   return fail(TMPI_ERR_UNSUPPORTED, "bn: dtype %d", dtype);
+}
+
+// Batch-norm + ReLU + max-pool (3x3, stride 2, pad 1) in one stage.  x: [N, H, W, C] channels-last;
+// y, idx: [N, OH, OW, C] with OH = (H - 1) / 2 + 1.  Other arguments as tmpi_bn_relu_fwd / _bwd.
+int tmpi_bn_relu_pool_fwd(const void* x, void* y, void* idx, const float* gamma, const float* beta, float* running_mean,
+                          float* running_var, float* save_mean, float* save_invstd, int N, int H, int W, int channels,
+                          float eps, float momentum, int training, int dtype, void* scratch, void* stream) {
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (dtype) {
+    case TMPI_BF16: return bn_pool_fwd_t<__nv_bfloat16>(x, y, idx, gamma, beta, running_mean, running_var, save_mean, save_invstd,
+                                                        N, H, W, channels, eps, momentum, training, scratch, s);
+    case TMPI_F16: return bn_pool_fwd_t<__half>(x, y, idx, gamma, beta, running_mean, running_var, save_mean, save_invstd, N, H, W,
+                                                channels, eps, momentum, training, scratch, s);
+    case TMPI_F32: return bn_pool_fwd_t<float>(x, y, idx, gamma, beta, running_mean, running_var, save_mean, save_invstd, N, H, W,
+                                               channels, eps, momentum, training, scratch, s);
+  }
+  return fail(TMPI_ERR_UNSUPPORTED, "bn+pool: dtype %d", dtype);
+}
+
+int tmpi_bn_relu_pool_bwd(const void* x, const void* dy, const void* idx, void* dx, const float* gamma, const float* beta,
+                          const float* save_mean, const float* save_invstd, float* dgamma, float* dbeta, int N, int H, int W,
+                          int channels, int dtype, void* scratch, void* stream) {
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (dtype) {
+    case TMPI_BF16: return bn_pool_bwd_t<__nv_bfloat16>(x, dy, idx, dx, gamma, beta, save_mean, save_invstd, dgamma, dbeta, N, H, W,
+                                                        channels, scratch, s);
+    case TMPI_F16: return bn_pool_bwd_t<__half>(x, dy, idx, dx, gamma, beta, save_mean, save_invstd, dgamma, dbeta, N, H, W, channels,
+                                                scratch, s);
+    case TMPI_F32: return bn_pool_bwd_t<float>(x, dy, idx, dx, gamma, beta, save_mean, save_invstd, dgamma, dbeta, N, H, W, channels,
+                                               scratch, s);
+  }
+  return fail(TMPI_ERR_UNSUPPORTED, "bn+pool: dtype %d", dtype);
 }
 
 }  // extern "C"

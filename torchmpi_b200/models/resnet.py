@@ -63,11 +63,12 @@ class ResNet(nn.Module):
             self.conv1 = StemConv7x7(width)           # im2col + tensor-core GEMM; same parameter as the Conv2d
         else:
             self.conv1 = nn.Conv2d(3, width, 7, stride=2, padding=3, bias=False)
-        self.bn1 = _bn(width, fused_bn, relu=True)
         if fused_bn:
-            from ..ops.pool import MaxPool2d
-            self.maxpool = MaxPool2d(3, stride=2, padding=1)
+            from ..ops.bn_relu import FusedBatchNormReLUMaxPool
+            self.bn1 = FusedBatchNormReLUMaxPool(width)     # batch-norm + ReLU + max-pool in one stage
+            self.maxpool = nn.Identity()
         else:
+            self.bn1 = _bn(width, fused_bn, relu=True)
             self.maxpool = nn.MaxPool2d(3, stride=2, padding=1)
         self.layer1 = self._make_layer(width, layers[0], 1)
         self.layer2 = self._make_layer(width * 2, layers[1], 2)

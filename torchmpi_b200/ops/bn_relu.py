@@ -87,6 +87,66 @@ class _BnReluFn(torch.autograd.Function):
         return dx, dres, dgamma, dbeta, None, None, None, None, None, None
 
 
+class _BnReluPoolFn(torch.autograd.Function):
+    """``max_pool2d(relu(batch_norm(x)), 3, 2, 1)`` without materialising the full-resolution activation."""
+
+    @staticmethod
+    def forward(ctx, x, gamma, beta, running_mean, running_var, eps, momentum, training):
+        global launch_count
+        x = x.contiguous(memory_format=torch.channels_last)
+        N, C, H, W = x.shape
+        OH, OW = (H - 1) // 2 + 1, (W - 1) // 2 + 1
+        y = torch.empty((N, C, OH, OW), dtype=x.dtype, device=x.device, memory_format=torch.channels_last)
+        idx = torch.empty((N, OH, OW, C), dtype=torch.uint8, device=x.device)
+        if training:
+            mean = torch.empty(C, dtype=torch.float32, device=x.device)
+            invstd = torch.empty(C, dtype=torch.float32, device=x.device)
+        else:
+            mean = running_mean.float()
+            invstd = torch.rsqrt(running_var.float() + eps)
+        check(lib.tmpi_bn_relu_pool_fwd(
+            x.data_ptr(), y.data_ptr(), idx.data_ptr(), gamma.data_ptr(), beta.data_ptr(),
+            running_mean.data_ptr() if (training and running_mean is not None) else None,
+            running_var.data_ptr() if (training and running_var is not None) else None,
+            mean.data_ptr(), invstd.data_ptr(), N, H, W, C, eps, momentum, int(training), dtype_code(x.dtype),
+            _scratch_for(x.device, C).data_ptr(), stream_ptr()))
+        launch_count += 3 if training else 1
+        ctx.save_for_backward(x, idx, gamma, beta, mean, invstd)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        global launch_count
+        x, idx, gamma, beta, mean, invstd = ctx.saved_tensors
+        dy = dy.contiguous(memory_format=torch.channels_last)
+        N, C, H, W = x.shape
+        dx = torch.empty_like(x, memory_format=torch.channels_last)
+        dgamma = torch.empty(C, dtype=torch.float32, device=x.device)
+        dbeta = torch.empty(C, dtype=torch.float32, device=x.device)
+        check(lib.tmpi_bn_relu_pool_bwd(
+            x.data_ptr(), dy.data_ptr(), idx.data_ptr(), dx.data_ptr(), gamma.data_ptr(), beta.data_ptr(),
+            mean.data_ptr(), invstd.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(), N, H, W, C, dtype_code(x.dtype),
+            _scratch_for(x.device, C).data_ptr(), stream_ptr()))
+        launch_count += 3
+        return dx, dgamma, dbeta, None, None, None, None, None
+
+
+class FusedBatchNormReLUMaxPool(nn.BatchNorm2d):
+    """``BatchNorm2d`` + ReLU + ``MaxPool2d(3, stride=2, padding=1)`` as one stage (the ResNet stem).  The
+    parameters and buffers are those of the ``BatchNorm2d``."""
+
+    def __init__(self, num_features: int, eps: float = 1e-5, momentum: float = 0.1):
+        super().__init__(num_features, eps=eps, momentum=momentum)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if supported(x) and self.weight.dtype == torch.float32 and has_symbol("tmpi_bn_relu_pool_fwd"):
+            return _BnReluPoolFn.apply(x, self.weight, self.bias, self.running_mean, self.running_var, self.eps,
+                                       self.momentum, self.training)
+        out = torch.relu(F.batch_norm(x, self.running_mean, self.running_var, self.weight, self.bias, self.training,
+                                      self.momentum, self.eps))
+        return F.max_pool2d(out, 3, 2, 1)
+
+
 class FusedBatchNormReLU(nn.BatchNorm2d):
     """``forward(x, residual=None)`` = ``relu(batch_norm(x) + residual)`` (ReLU optional)."""
 
