@@ -319,17 +319,24 @@ constexpr int kBpThreads = kBnThreads;   // same partial layout as the kernels a
 
 struct BpDims { int N, H, W, C, OH, OW; };
 
-// forward: one block per (n, oh); thread -> (ow, channel group)
+// Both directions stage the rows a block needs in shared memory first (coalesced 16-byte loads), then
+// gather from there: the 2.25 windows that cover an input position, and the 9 positions of a window,
+// would otherwise each be a separate L2 request, and the stage becomes bound by L2 bandwidth.
+//
+// forward: one block per (n, oh).  The three input rows of the window go to shared memory already
+// normalised, rectified and rounded to T, in a row of W + 2 positions whose first and last hold -1
+// (below every rectified value), as do rows outside the image: the window scan needs no bounds checks.
 template <typename T, int V>
 __global__ void __launch_bounds__(kBpThreads) bn_pool_fwd_kernel(
     const T* __restrict__ x, T* __restrict__ y, unsigned char* __restrict__ idx, const float* __restrict__ gamma,
     const float* __restrict__ beta, const float* __restrict__ mean, const float* __restrict__ invstd, BpDims d) {
+  extern __shared__ __align__(16) unsigned char s_raw[];
+  T* s_a = reinterpret_cast<T*>(s_raw);                         // [3][W + 2][C]
   const int cvn = d.C / V;
   const int n = blockIdx.x / d.OH, oh = blockIdx.x % d.OH;
   const int ih0 = oh * 2 - 1;
-  const T* xin = x + (size_t)n * d.H * d.W * d.C;
-  const size_t orow = ((size_t)n * d.OH + oh) * d.OW * d.C;
-  const int cv = threadIdx.x % cvn;                  // kBpThreads is a multiple of cvn: fixed channel group
+  const int cv = threadIdx.x % cvn;                             // kBpThreads is a multiple of cvn: fixed channel group
+  const int pw = d.W + 2;
   float sc[V], sh[V];
 #pragma unroll
   for (int k = 0; k < V; ++k) {
@@ -337,30 +344,40 @@ __global__ void __launch_bounds__(kBpThreads) bn_pool_fwd_kernel(
     sc[k] = invstd[c] * gamma[c];
     sh[k] = beta[c] - mean[c] * sc[k];
   }
+  Pack<T, V> neg;
+#pragma unroll
+  for (int k = 0; k < V; ++k) neg.v[k] = from_acc<T>((typename AccOf<T>::type)(-1.f));
+  const T* xin = x + (size_t)n * d.H * d.W * d.C;
+  for (int t = threadIdx.x; t < 3 * pw * cvn; t += kBpThreads) {
+    const int pos = t / cvn;                                    // (row, padded column)
+    const int row = pos / pw, col = pos - row * pw;
+    const int ih = ih0 + row, iw = col - 1;
+    Pack<T, V> o = neg;
+    if (ih >= 0 && ih < d.H && iw >= 0 && iw < d.W) {
+      Pack<T, V> v = ld_pack<T, V>(xin + ((size_t)ih * d.W + iw) * d.C + cv * V);
+#pragma unroll
+      for (int k = 0; k < V; ++k)
+        o.v[k] = from_acc<T>((typename AccOf<T>::type)fmaxf((float)to_acc<T>(v.v[k]) * sc[k] + sh[k], 0.f));
+    }
+    st_pack<T, V>(s_a + (size_t)t * V, o);
+  }
+  __syncthreads();
+  const size_t orow = ((size_t)n * d.OH + oh) * d.OW * d.C;
   for (int t = threadIdx.x; t < d.OW * cvn; t += kBpThreads) {
     const int ow = t / cvn;
-    const int iw0 = ow * 2 - 1;
-    Pack<T, V> win[9];
-    bool ok[9];
-#pragma unroll
-    for (int q = 0; q < 9; ++q) {
-      const int ih = ih0 + q / 3, iw = iw0 + q % 3;
-      ok[q] = ih >= 0 && ih < d.H && iw >= 0 && iw < d.W;
-      if (ok[q]) win[q] = ld_pack<T, V>(xin + ((size_t)ih * d.W + iw) * d.C + cv * V);
-    }
     float best[V];
     unsigned char bi[V];
-    bool first = true;
+#pragma unroll
+    for (int k = 0; k < V; ++k) { best[k] = -2.f; bi[k] = 0; }
 #pragma unroll
     for (int q = 0; q < 9; ++q) {
-      if (!ok[q]) continue;
+      // padded column of iw = 2 ow - 1 + kw is 2 ow + kw
+      Pack<T, V> v = ld_pack<T, V>(s_a + ((size_t)((q / 3) * pw + ow * 2 + q % 3) * cvn + cv) * V);
 #pragma unroll
       for (int k = 0; k < V; ++k) {
-        // the value the unfused path would have stored: bf16(relu(z))
-        const float a = (float)to_acc<T>(from_acc<T>((typename AccOf<T>::type)fmaxf((float)to_acc<T>(win[q].v[k]) * sc[k] + sh[k], 0.f)));
-        if (first || a > best[k] || a != a) { best[k] = a; bi[k] = (unsigned char)q; }
+        const float a = (float)to_acc<T>(v.v[k]);
+        if (a > best[k] || a != a) { best[k] = a; bi[k] = (unsigned char)q; }
       }
-      first = false;
     }
     Pack<T, V> out;
     Pack<unsigned char, V> oi;
@@ -371,48 +388,66 @@ __global__ void __launch_bounds__(kBpThreads) bn_pool_fwd_kernel(
   }
 }
 
-// gradient routed by the pool to input position (ih, iw), channel group cv
+// backward: a block works on the input rows 2k and 2k + 1 of one image; the windows that cover them
+// lie in the output rows k and k + 1, which go to shared memory (gradient and index) with one extra
+// zero column and a zero row where the image ends.
 template <typename T, int V>
-__device__ __forceinline__ void pooled_grad(const T* __restrict__ dy, const unsigned char* __restrict__ idx, const BpDims& d,
-                                            size_t obase, int ih, int iw, int cv, int cvn, float (&g)[V]) {
+__device__ __forceinline__ void stage_pool_rows(const T* __restrict__ dy, const unsigned char* __restrict__ idx, const BpDims& d,
+                                                int n, int k, T* s_dy, unsigned char* s_ix) {
+  const int cvn = d.C / V, pw = d.OW + 1;
+  for (int t = threadIdx.x; t < 2 * pw * cvn; t += kBpThreads) {
+    const int pos = t / cvn, cvv = t - pos * cvn;
+    const int row = pos / pw, ow = pos - row * pw;
+    const int oh = k + row;
+    Pack<T, V> g;
+    Pack<unsigned char, V> iv;
 #pragma unroll
-  for (int k = 0; k < V; ++k) g[k] = 0.f;
-  // windows [2o - 1, 2o + 1] containing the coordinate: o in {ceil((i - 1) / 2), floor((i + 1) / 2)}
-  const int oh_lo = ih >> 1, ow_lo = iw >> 1;                       // = ceil((i - 1) / 2) for i >= 0
-  const int oh_hi = min((ih + 1) >> 1, d.OH - 1), ow_hi = min((iw + 1) >> 1, d.OW - 1);
-  Pack<unsigned char, V> iv[4];
-  Pack<T, V> gv[4];
-  bool ok[4];
-#pragma unroll
-  for (int q = 0; q < 4; ++q) {
-    const int oh = oh_lo + (q >> 1), ow = ow_lo + (q & 1);
-    ok[q] = oh <= oh_hi && ow <= ow_hi;
-    if (ok[q]) {
-      const size_t o = obase + ((size_t)(oh * d.OW + ow) * cvn + cv) * V;
-      iv[q] = ld_pack<unsigned char, V>(idx + o);
-      gv[q] = ld_pack<T, V>(dy + o);
+    for (int c = 0; c < V; ++c) { g.v[c] = from_acc<T>((typename AccOf<T>::type)0.f); iv.v[c] = 255; }
+    if (oh < d.OH && ow < d.OW) {
+      const size_t o = ((((size_t)n * d.OH + oh) * d.OW + ow) * cvn + cvv) * V;
+      g = ld_pack<T, V>(dy + o);
+      iv = ld_pack<unsigned char, V>(idx + o);
     }
-  }
-#pragma unroll
-  for (int q = 0; q < 4; ++q) {
-    if (!ok[q]) continue;
-    const int oh = oh_lo + (q >> 1), ow = ow_lo + (q & 1);
-    const unsigned char w = (unsigned char)((ih - (oh * 2 - 1)) * 3 + (iw - (ow * 2 - 1)));
-#pragma unroll
-    for (int k = 0; k < V; ++k)
-      if (iv[q].v[k] == w) g[k] += (float)to_acc<T>(gv[q].v[k]);
+    st_pack<T, V>(s_dy + (size_t)t * V, g);
+    st_pack<unsigned char, V>(s_ix + (size_t)t * V, iv);
   }
 }
 
-// backward statistics: blocks take input rows (n, ih) round-robin; partial sums per block
+// gradient routed by the pool to input position (ih, iw), channel group cv, from the staged rows
 template <typename T, int V>
-__global__ void __launch_bounds__(kBpThreads, 2) bn_pool_bwd_reduce_kernel(
+__device__ __forceinline__ void pooled_grad(const T* s_dy, const unsigned char* s_ix, const BpDims& d, int k, int ih, int iw,
+                                            int cv, float (&g)[V]) {
+  const int cvn = d.C / V, pw = d.OW + 1;
+#pragma unroll
+  for (int c = 0; c < V; ++c) g[c] = 0.f;
+  // windows [2o - 1, 2o + 1] containing a coordinate i: o = i >> 1 and, for odd i, o + 1
+  const int ow_lo = iw >> 1;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const int dr = q >> 1, dc = q & 1;
+    if ((dr && !(ih & 1)) || (dc && !(iw & 1))) continue;
+    const int oh = (ih >> 1) + dr, ow = ow_lo + dc;             // ow <= OW (the zero column), oh - k in {0, 1}
+    const size_t o = ((size_t)((oh - k) * pw + ow) * cvn + cv) * V;
+    Pack<unsigned char, V> iv = ld_pack<unsigned char, V>(s_ix + o);
+    Pack<T, V> gv = ld_pack<T, V>(s_dy + o);
+    const unsigned char w = (unsigned char)((ih - (oh * 2 - 1)) * 3 + (iw - (ow * 2 - 1)));
+#pragma unroll
+    for (int c = 0; c < V; ++c)
+      if (iv.v[c] == w) g[c] += (float)to_acc<T>(gv.v[c]);
+  }
+}
+
+// backward statistics: blocks take row pairs (n, k) round-robin; partial sums per block
+template <typename T, int V>
+__global__ void __launch_bounds__(kBpThreads) bn_pool_bwd_reduce_kernel(
     const T* __restrict__ x, const T* __restrict__ dy, const unsigned char* __restrict__ idx, const float* __restrict__ gamma,
     const float* __restrict__ beta, const float* __restrict__ mean, const float* __restrict__ invstd, BpDims d,
     float* __restrict__ partial) {
+  extern __shared__ __align__(16) unsigned char s_raw[];
   const int cvn = d.C / V;
-  const int cv = threadIdx.x % cvn;                  // kBpThreads is a multiple of cvn: fixed channel group
-  const int pos0 = threadIdx.x / cvn, pos_step = kBpThreads / cvn;
+  T* s_dy = reinterpret_cast<T*>(s_raw);
+  unsigned char* s_ix = s_raw + (size_t)2 * (d.OW + 1) * d.C * sizeof(T);
+  const int cv = threadIdx.x % cvn;
   float a[V], b[V], mu[V], is[V], sc[V], sh[V];
 #pragma unroll
   for (int k = 0; k < V; ++k) {
@@ -421,24 +456,30 @@ __global__ void __launch_bounds__(kBpThreads, 2) bn_pool_bwd_reduce_kernel(
     mu[k] = mean[c]; is[k] = invstd[c];
     sc[k] = is[k] * gamma[c]; sh[k] = beta[c] - mu[k] * sc[k];
   }
-  const int rows = d.N * d.H;
-  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
-    const int n = r / d.H, ih = r - n * d.H;
-    const size_t obase = (size_t)n * d.OH * d.OW * d.C;
-    const T* xrow = x + (size_t)r * d.W * d.C;
-    for (int iw = pos0; iw < d.W; iw += pos_step) {
-      Pack<T, V> xv = ld_pack<T, V>(xrow + ((size_t)iw * cvn + cv) * V);
+  const int hp = (d.H + 1) / 2, pairs = d.N * hp;
+  for (int pr = blockIdx.x; pr < pairs; pr += gridDim.x) {
+    const int n = pr / hp, k = pr - n * hp;
+    __syncthreads();                                            // the previous pair's gathers are done
+    stage_pool_rows<T, V>(dy, idx, d, n, k, s_dy, s_ix);
+    __syncthreads();
+    const int rows_here = min(2, d.H - 2 * k);
+    const T* xrow = x + ((size_t)n * d.H + 2 * k) * d.W * d.C;
+    for (int t = threadIdx.x; t < rows_here * d.W * cvn; t += kBpThreads) {
+      const int pos = t / cvn;
+      const int r = pos / d.W, iw = pos - r * d.W;
+      Pack<T, V> xv = ld_pack<T, V>(xrow + (size_t)t * V);
       float g[V];
-      pooled_grad<T, V>(dy, idx, d, obase, ih, iw, cv, cvn, g);
+      pooled_grad<T, V>(s_dy, s_ix, d, k, 2 * k + r, iw, cv, g);
 #pragma unroll
-      for (int k = 0; k < V; ++k) {
-        const float xf = (float)to_acc<T>(xv.v[k]);
-        const float gz = (xf * sc[k] + sh[k] > 0.f) ? g[k] : 0.f;
-        a[k] += gz;
-        b[k] += gz * (xf - mu[k]) * is[k];
+      for (int c = 0; c < V; ++c) {
+        const float xf = (float)to_acc<T>(xv.v[c]);
+        const float gz = (xf * sc[c] + sh[c] > 0.f) ? g[c] : 0.f;
+        a[c] += gz;
+        b[c] += gz * (xf - mu[c]) * is[c];
       }
     }
   }
+  __syncthreads();
   __shared__ float s[kBpThreads][2 * V + 1];
 #pragma unroll
   for (int k = 0; k < V; ++k) { s[threadIdx.x][k] = a[k]; s[threadIdx.x][V + k] = b[k]; }
@@ -452,44 +493,54 @@ __global__ void __launch_bounds__(kBpThreads, 2) bn_pool_bwd_reduce_kernel(
   }
 }
 
-// backward apply: one block per input row
+// backward apply: one block per row pair
 template <typename T, int V>
-__global__ void __launch_bounds__(kBpThreads, 2) bn_pool_bwd_apply_kernel(
+__global__ void __launch_bounds__(kBpThreads) bn_pool_bwd_apply_kernel(
     const T* __restrict__ x, const T* __restrict__ dy, const unsigned char* __restrict__ idx, T* __restrict__ dx,
     const float* __restrict__ gamma, const float* __restrict__ beta, const float* __restrict__ mean,
     const float* __restrict__ invstd, const float* __restrict__ dgamma, const float* __restrict__ dbeta, BpDims d, float inv_m) {
+  extern __shared__ __align__(16) unsigned char s_raw[];
   const int cvn = d.C / V;
-  const int r = blockIdx.x;
-  const int n = r / d.H, ih = r - n * d.H;
-  const size_t obase = (size_t)n * d.OH * d.OW * d.C;
-  const size_t irow = (size_t)r * d.W * d.C;
+  T* s_dy = reinterpret_cast<T*>(s_raw);
+  unsigned char* s_ix = s_raw + (size_t)2 * (d.OW + 1) * d.C * sizeof(T);
+  const int hp = (d.H + 1) / 2;
+  const int n = blockIdx.x / hp, k = blockIdx.x - n * hp;
   const int cv = threadIdx.x % cvn;                  // fixed channel group
   float mu[V], is[V], k1[V], k2[V], k3[V], sh[V];
 #pragma unroll
-  for (int k = 0; k < V; ++k) {
-    const int c = cv * V + k;
-    mu[k] = mean[c]; is[k] = invstd[c];
-    k1[k] = gamma[c] * is[k];
-    k2[k] = dbeta[c] * inv_m;
-    k3[k] = dgamma[c] * inv_m;
-    sh[k] = beta[c] - mu[k] * k1[k];
+  for (int c = 0; c < V; ++c) {
+    const int ch = cv * V + c;
+    mu[c] = mean[ch]; is[c] = invstd[ch];
+    k1[c] = gamma[ch] * is[c];
+    k2[c] = dbeta[ch] * inv_m;
+    k3[c] = dgamma[ch] * inv_m;
+    sh[c] = beta[ch] - mu[c] * k1[c];
   }
-  for (int t = threadIdx.x; t < d.W * cvn; t += kBpThreads) {
-    const int iw = t / cvn;
+  stage_pool_rows<T, V>(dy, idx, d, n, k, s_dy, s_ix);
+  __syncthreads();
+  const int rows_here = min(2, d.H - 2 * k);
+  const size_t irow = ((size_t)n * d.H + 2 * k) * d.W * d.C;
+  for (int t = threadIdx.x; t < rows_here * d.W * cvn; t += kBpThreads) {
+    const int pos = t / cvn;
+    const int r = pos / d.W, iw = pos - r * d.W;
     Pack<T, V> xv = ld_pack<T, V>(x + irow + (size_t)t * V), ox;
     float g[V];
-    pooled_grad<T, V>(dy, idx, d, obase, ih, iw, cv, cvn, g);
+    pooled_grad<T, V>(s_dy, s_ix, d, k, 2 * k + r, iw, cv, g);
 #pragma unroll
-    for (int k = 0; k < V; ++k) {
-      const float xf = (float)to_acc<T>(xv.v[k]);
-      const float gz = (xf * k1[k] + sh[k] > 0.f) ? g[k] : 0.f;
-      const float xhat = (xf - mu[k]) * is[k];
-      ox.v[k] = from_acc<T>((typename AccOf<T>::type)(k1[k] * (gz - k2[k] - xhat * k3[k])));
+    for (int c = 0; c < V; ++c) {
+      const float xf = (float)to_acc<T>(xv.v[c]);
+      const float gz = (xf * k1[c] + sh[c] > 0.f) ? g[c] : 0.f;
+      const float xhat = (xf - mu[c]) * is[c];
+      ox.v[c] = from_acc<T>((typename AccOf<T>::type)(k1[c] * (gz - k2[c] - xhat * k3[c])));
     }
     st_pack<T, V>(dx + irow + (size_t)t * V, ox);
   }
 }
 
+// shared memory of the two stages, and the limit under which they are offered
+template <typename T> static size_t bn_pool_fwd_smem(const BpDims& d) { return (size_t)3 * (d.W + 2) * d.C * sizeof(T); }
+template <typename T> static size_t bn_pool_bwd_smem(const BpDims& d) { return (size_t)2 * (d.OW + 1) * d.C * (sizeof(T) + 1); }
+constexpr size_t kBpMaxSmem = 96 * 1024;
 
 template <typename T>
 static int bn_pool_fwd_t(const void* x, void* y, void* idx, const float* gamma, const float* beta, float* rmean, float* rvar,
@@ -509,7 +560,11 @@ static int bn_pool_fwd_t(const void* x, void* y, void* idx, const float* gamma, 
     bn_finalize_fwd_kernel<<<(C + 31) / 32, dim3(32, 32), 0, s>>>((const float*)scratch, grid, C, 1.f / m,
                                                            rows > 1 ? m / (m - 1.f) : 1.f, eps, momentum, smean, sinv, rmean, rvar);
   }
-  bn_pool_fwd_kernel<T, V><<<N * d.OH, kBpThreads, 0, s>>>((const T*)x, (T*)y, (unsigned char*)idx, gamma, beta, smean, sinv, d);
+  const size_t smem = bn_pool_fwd_smem<T>(d);
+  if (smem > kBpMaxSmem) return fail(TMPI_ERR_UNSUPPORTED, "bn+pool: rows of %d x %d do not fit in shared memory", W, C);
+  static bool attr = false;
+  if (!attr) { cudaFuncSetAttribute(bn_pool_fwd_kernel<T, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kBpMaxSmem); attr = true; }
+  bn_pool_fwd_kernel<T, V><<<N * d.OH, kBpThreads, smem, s>>>((const T*)x, (T*)y, (unsigned char*)idx, gamma, beta, smean, sinv, d);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? TMPI_OK : fail(TMPI_ERR_CUDA, "bn+pool forward launch: %s", cudaGetErrorString(e));
 }
@@ -523,11 +578,20 @@ static int bn_pool_bwd_t(const void* x, const void* dy, const void* idx, void* d
   int st = bn_check(rows, C, V);
   if (st) return st;
   BpDims d{N, H, W, C, (H - 1) / 2 + 1, (W - 1) / 2 + 1};
-  const int grid = std::min(N * H, kBnMaxGrid);
-  bn_pool_bwd_reduce_kernel<T, V><<<grid, kBpThreads, 0, s>>>((const T*)x, (const T*)dy, (const unsigned char*)idx, gamma, beta,
+  const int pairs = N * ((H + 1) / 2);
+  const int grid = std::min(pairs, kBnMaxGrid);
+  const size_t smem = bn_pool_bwd_smem<T>(d);
+  if (smem > kBpMaxSmem) return fail(TMPI_ERR_UNSUPPORTED, "bn+pool: rows of %d x %d do not fit in shared memory", W, C);
+  static bool attr = false;
+  if (!attr) {
+    cudaFuncSetAttribute(bn_pool_bwd_reduce_kernel<T, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kBpMaxSmem);
+    cudaFuncSetAttribute(bn_pool_bwd_apply_kernel<T, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kBpMaxSmem);
+    attr = true;
+  }
+  bn_pool_bwd_reduce_kernel<T, V><<<grid, kBpThreads, smem, s>>>((const T*)x, (const T*)dy, (const unsigned char*)idx, gamma, beta,
                                                               smean, sinv, d, (float*)scratch);
   bn_finalize_bwd_kernel<<<(C + 31) / 32, dim3(32, 32), 0, s>>>((const float*)scratch, grid, C, dgamma, dbeta);
-  bn_pool_bwd_apply_kernel<T, V><<<N * H, kBpThreads, 0, s>>>((const T*)x, (const T*)dy, (const unsigned char*)idx, (T*)dx, gamma,
+  bn_pool_bwd_apply_kernel<T, V><<<pairs, kBpThreads, smem, s>>>((const T*)x, (const T*)dy, (const unsigned char*)idx, (T*)dx, gamma,
                                                               beta, smean, sinv, dgamma, dbeta, d, 1.f / (float)rows);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? TMPI_OK : fail(TMPI_ERR_CUDA, "bn+pool backward launch: %s", cudaGetErrorString(e));

@@ -154,15 +154,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   if (peer_barrier(P, 1, 210, &s_abort) && !sh->error) {
     // every rank's partial rows for me are in my slots: sum them in rank order
     const __nv_bfloat16* slots = reinterpret_cast<const __nv_bfloat16*>(P.base[P.me] + g.sym_off);
-    const size_t nv = slot_elems / 8;
-    for (size_t i = (size_t)blockIdx.x * THREADS + threadIdx.x; i < nv; i += (size_t)gridDim.x * THREADS) {
-      Acc<__nv_bfloat16, 8> acc;
-      for (int r = 0; r < R; ++r) {
-        Pack<__nv_bfloat16, 8> x = ld_pack_peer<__nv_bfloat16, 8>(slots + (size_t)r * slot_elems + i * 8);
-        if (r == 0) acc.set(x); else acc.add(x);
-      }
-      st_pack<__nv_bfloat16, 8>(g.local + i * 8, acc.pack(1.0f));
-    }
+    gemm::slot_sum(slots, slot_elems, R, g.local, (size_t)blockIdx.x * THREADS + threadIdx.x, (size_t)gridDim.x * THREADS);
     peer_barrier(P, 2, 211, &s_abort);      // slots may be overwritten by the next call only after everyone has summed
   }
   teardown(sh, warp);
@@ -304,15 +296,7 @@ gemm_rs_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   if (peer_barrier(P, 1, 210, &s_abort) && !sh->error) {
     // every rank's partial rows for me are in my slots: sum them in rank order
     const __nv_bfloat16* slots = reinterpret_cast<const __nv_bfloat16*>(P.base[P.me] + g.sym_off);
-    const size_t nv = slot_elems / 8;
-    for (size_t i = (size_t)blockIdx.x * THREADS + threadIdx.x; i < nv; i += (size_t)gridDim.x * THREADS) {
-      Acc<__nv_bfloat16, 8> acc;
-      for (int r = 0; r < R; ++r) {
-        Pack<__nv_bfloat16, 8> x = ld_pack_peer<__nv_bfloat16, 8>(slots + (size_t)r * slot_elems + i * 8);
-        if (r == 0) acc.set(x); else acc.add(x);
-      }
-      st_pack<__nv_bfloat16, 8>(g.local + i * 8, acc.pack(1.0f));
-    }
+    gemm::slot_sum(slots, slot_elems, R, g.local, (size_t)blockIdx.x * THREADS + threadIdx.x, (size_t)gridDim.x * THREADS);
     peer_barrier(P, 2, 211, &s_abort);      // slots may be overwritten by the next call only after everyone has summed
   }
   __syncwarp();

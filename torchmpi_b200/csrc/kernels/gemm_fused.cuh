@@ -112,5 +112,63 @@ __device__ void ag_comm(const FusedArgs& g, const Problem& p, unsigned char* til
   peer_barrier(P, 2, 201, s_abort);                              // nobody still reads my shard
 }
 
+
+// out[i] = sum over r of slots[r][i], added in rank order (every rank computes the same bits), for the
+// reduce-scatter tail.  RC is the rank count when it is known at compile time (0: run-time loop); all
+// loads of an iteration are issued before the first add, RC x U 16-byte loads per thread in flight -
+// with one load in flight the pass ran at a seventh of the memory bandwidth.
+template <int RC>
+__device__ __forceinline__ void slot_sum_t(const __nv_bfloat16* __restrict__ slots, size_t slot_elems, int R,
+                                           __nv_bfloat16* __restrict__ out, size_t t0, size_t stride) {
+  using P8 = Pack<__nv_bfloat16, 8>;
+  constexpr int U = RC == 0 ? 4 : (RC >= 4 ? 2 : 4);
+  const size_t nv = slot_elems / 8;
+  size_t i = t0;
+  for (; i + (U - 1) * stride < nv; i += U * stride) {
+    Acc<__nv_bfloat16, 8> acc[U];
+    if constexpr (RC > 0) {
+      P8 x[RC][U];
+#pragma unroll
+      for (int r = 0; r < RC; ++r)
+#pragma unroll
+        for (int u = 0; u < U; ++u) x[r][u] = ld_pack_peer<__nv_bfloat16, 8>(slots + (size_t)r * slot_elems + (i + u * stride) * 8);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        acc[u].set(x[0][u]);
+#pragma unroll
+        for (int r = 1; r < RC; ++r) acc[u].add(x[r][u]);
+      }
+    } else {
+      for (int r = 0; r < R; ++r) {
+        P8 x[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) x[u] = ld_pack_peer<__nv_bfloat16, 8>(slots + (size_t)r * slot_elems + (i + u * stride) * 8);
+#pragma unroll
+        for (int u = 0; u < U; ++u) { if (r == 0) acc[u].set(x[u]); else acc[u].add(x[u]); }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) st_pack<__nv_bfloat16, 8>(out + (i + u * stride) * 8, acc[u].pack(1.0f));
+  }
+  for (; i < nv; i += stride) {
+    Acc<__nv_bfloat16, 8> acc;
+    for (int r = 0; r < R; ++r) {
+      P8 x = ld_pack_peer<__nv_bfloat16, 8>(slots + (size_t)r * slot_elems + i * 8);
+      if (r == 0) acc.set(x); else acc.add(x);
+    }
+    st_pack<__nv_bfloat16, 8>(out + i * 8, acc.pack(1.0f));
+  }
+}
+
+__device__ __forceinline__ void slot_sum(const __nv_bfloat16* slots, size_t slot_elems, int R, __nv_bfloat16* out,
+                                         size_t t0, size_t stride) {
+  switch (R) {
+    case 2: slot_sum_t<2>(slots, slot_elems, R, out, t0, stride); break;
+    case 4: slot_sum_t<4>(slots, slot_elems, R, out, t0, stride); break;
+    case 8: slot_sum_t<8>(slots, slot_elems, R, out, t0, stride); break;
+    default: slot_sum_t<0>(slots, slot_elems, R, out, t0, stride); break;
+  }
+}
+
 }  // namespace gemm
 }  // namespace tmpi
