@@ -348,18 +348,31 @@ __global__ void __launch_bounds__(kBpThreads) bn_pool_fwd_kernel(
 #pragma unroll
   for (int k = 0; k < V; ++k) neg.v[k] = from_acc<T>((typename AccOf<T>::type)(-1.f));
   const T* xin = x + (size_t)n * d.H * d.W * d.C;
-  for (int t = threadIdx.x; t < 3 * pw * cvn; t += kBpThreads) {
-    const int pos = t / cvn;                                    // (row, padded column)
-    const int row = pos / pw, col = pos - row * pw;
-    const int ih = ih0 + row, iw = col - 1;
-    Pack<T, V> o = neg;
-    if (ih >= 0 && ih < d.H && iw >= 0 && iw < d.W) {
-      Pack<T, V> v = ld_pack<T, V>(xin + ((size_t)ih * d.W + iw) * d.C + cv * V);
+  constexpr int U = 4;                                          // global loads in flight per thread
+  for (int t0 = threadIdx.x; t0 < 3 * pw * cvn; t0 += U * kBpThreads) {
+    Pack<T, V> v[U];
+    bool in[U];
 #pragma unroll
-      for (int k = 0; k < V; ++k)
-        o.v[k] = from_acc<T>((typename AccOf<T>::type)fmaxf((float)to_acc<T>(v.v[k]) * sc[k] + sh[k], 0.f));
+    for (int u = 0; u < U; ++u) {
+      const int t = t0 + u * kBpThreads;
+      const int pos = t / cvn;                                  // (row, padded column)
+      const int row = pos / pw, col = pos - row * pw;
+      const int ih = ih0 + row, iw = col - 1;
+      in[u] = t < 3 * pw * cvn && ih >= 0 && ih < d.H && iw >= 0 && iw < d.W;
+      if (in[u]) v[u] = ld_pack<T, V>(xin + ((size_t)ih * d.W + iw) * d.C + cv * V);
     }
-    st_pack<T, V>(s_a + (size_t)t * V, o);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int t = t0 + u * kBpThreads;
+      if (t >= 3 * pw * cvn) break;
+      Pack<T, V> o = neg;
+      if (in[u]) {
+#pragma unroll
+        for (int k = 0; k < V; ++k)
+          o.v[k] = from_acc<T>((typename AccOf<T>::type)fmaxf((float)to_acc<T>(v[u].v[k]) * sc[k] + sh[k], 0.f));
+      }
+      st_pack<T, V>(s_a + (size_t)t * V, o);
+    }
   }
   __syncthreads();
   const size_t orow = ((size_t)n * d.OH + oh) * d.OW * d.C;
@@ -395,21 +408,49 @@ template <typename T, int V>
 __device__ __forceinline__ void stage_pool_rows(const T* __restrict__ dy, const unsigned char* __restrict__ idx, const BpDims& d,
                                                 int n, int k, T* s_dy, unsigned char* s_ix) {
   const int cvn = d.C / V, pw = d.OW + 1;
-  for (int t = threadIdx.x; t < 2 * pw * cvn; t += kBpThreads) {
-    const int pos = t / cvn, cvv = t - pos * cvn;
-    const int row = pos / pw, ow = pos - row * pw;
-    const int oh = k + row;
-    Pack<T, V> g;
-    Pack<unsigned char, V> iv;
+  constexpr int U = 4;
+  const int items = 2 * pw * cvn;
+  for (int t0 = threadIdx.x; t0 < items; t0 += U * kBpThreads) {
+    Pack<T, V> g[U];
+    Pack<unsigned char, V> iv[U];
 #pragma unroll
-    for (int c = 0; c < V; ++c) { g.v[c] = from_acc<T>((typename AccOf<T>::type)0.f); iv.v[c] = 255; }
-    if (oh < d.OH && ow < d.OW) {
-      const size_t o = ((((size_t)n * d.OH + oh) * d.OW + ow) * cvn + cvv) * V;
-      g = ld_pack<T, V>(dy + o);
-      iv = ld_pack<unsigned char, V>(idx + o);
+    for (int u = 0; u < U; ++u) {
+      const int t = t0 + u * kBpThreads;
+      const int pos = t / cvn, cvv = t - pos * cvn;
+      const int row = pos / pw, ow = pos - row * pw;
+      const int oh = k + row;
+#pragma unroll
+      for (int c = 0; c < V; ++c) { g[u].v[c] = from_acc<T>((typename AccOf<T>::type)0.f); iv[u].v[c] = 255; }
+      if (t < items && oh < d.OH && ow < d.OW) {
+        const size_t o = ((((size_t)n * d.OH + oh) * d.OW + ow) * cvn + cvv) * V;
+        g[u] = ld_pack<T, V>(dy + o);
+        iv[u] = ld_pack<unsigned char, V>(idx + o);
+      }
     }
-    st_pack<T, V>(s_dy + (size_t)t * V, g);
-    st_pack<unsigned char, V>(s_ix + (size_t)t * V, iv);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int t = t0 + u * kBpThreads;
+      if (t >= items) break;
+      st_pack<T, V>(s_dy + (size_t)t * V, g[u]);
+      st_pack<unsigned char, V>(s_ix + (size_t)t * V, iv[u]);
+    }
+  }
+}
+
+// copies `items` packs (the block's two input rows of x, contiguous in memory) to shared memory with
+// four loads in flight per thread; the statistics and apply loops then run out of shared memory with
+// few registers, so that three blocks fit on an SM
+template <typename T, int V>
+__device__ __forceinline__ void stage_x_rows(const T* __restrict__ src, T* s_x, int items) {
+  constexpr int U = 4;
+  for (int t0 = threadIdx.x; t0 < items; t0 += U * kBpThreads) {
+    Pack<T, V> v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (t0 + u * kBpThreads < items) v[u] = ld_pack<T, V>(src + (size_t)(t0 + u * kBpThreads) * V);
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (t0 + u * kBpThreads < items) st_pack<T, V>(s_x + (size_t)(t0 + u * kBpThreads) * V, v[u]);
   }
 }
 
@@ -439,7 +480,7 @@ __device__ __forceinline__ void pooled_grad(const T* s_dy, const unsigned char* 
 
 // backward statistics: blocks take row pairs (n, k) round-robin; partial sums per block
 template <typename T, int V>
-__global__ void __launch_bounds__(kBpThreads) bn_pool_bwd_reduce_kernel(
+__global__ void __launch_bounds__(kBpThreads, 3) bn_pool_bwd_reduce_kernel(
     const T* __restrict__ x, const T* __restrict__ dy, const unsigned char* __restrict__ idx, const float* __restrict__ gamma,
     const float* __restrict__ beta, const float* __restrict__ mean, const float* __restrict__ invstd, BpDims d,
     float* __restrict__ partial) {
@@ -447,27 +488,31 @@ __global__ void __launch_bounds__(kBpThreads) bn_pool_bwd_reduce_kernel(
   const int cvn = d.C / V;
   T* s_dy = reinterpret_cast<T*>(s_raw);
   unsigned char* s_ix = s_raw + (size_t)2 * (d.OW + 1) * d.C * sizeof(T);
+  T* s_x = reinterpret_cast<T*>(s_raw + (size_t)2 * (d.OW + 1) * d.C * (sizeof(T) + 1));
   const int cv = threadIdx.x % cvn;
-  float a[V], b[V], mu[V], is[V], sc[V], sh[V];
+  // b accumulates sum(dz * x); the centred form sum(dz * (x - mean)) / std is recovered at the end,
+  // which keeps the loop at two constants per channel
+  float a[V], b[V], sc[V], sh[V];
 #pragma unroll
   for (int k = 0; k < V; ++k) {
     const int c = cv * V + k;
     a[k] = 0.f; b[k] = 0.f;
-    mu[k] = mean[c]; is[k] = invstd[c];
-    sc[k] = is[k] * gamma[c]; sh[k] = beta[c] - mu[k] * sc[k];
+    sc[k] = invstd[c] * gamma[c]; sh[k] = beta[c] - mean[c] * sc[k];
   }
   const int hp = (d.H + 1) / 2, pairs = d.N * hp;
   for (int pr = blockIdx.x; pr < pairs; pr += gridDim.x) {
     const int n = pr / hp, k = pr - n * hp;
     __syncthreads();                                            // the previous pair's gathers are done
-    stage_pool_rows<T, V>(dy, idx, d, n, k, s_dy, s_ix);
-    __syncthreads();
     const int rows_here = min(2, d.H - 2 * k);
-    const T* xrow = x + ((size_t)n * d.H + 2 * k) * d.W * d.C;
-    for (int t = threadIdx.x; t < rows_here * d.W * cvn; t += kBpThreads) {
+    const int items = rows_here * d.W * cvn;
+    stage_pool_rows<T, V>(dy, idx, d, n, k, s_dy, s_ix);
+    stage_x_rows<T, V>(x + ((size_t)n * d.H + 2 * k) * d.W * d.C, s_x, items);
+    __syncthreads();
+#pragma unroll 1
+    for (int t = threadIdx.x; t < items; t += kBpThreads) {
       const int pos = t / cvn;
       const int r = pos / d.W, iw = pos - r * d.W;
-      Pack<T, V> xv = ld_pack<T, V>(xrow + (size_t)t * V);
+      Pack<T, V> xv = ld_pack<T, V>(s_x + (size_t)t * V);
       float g[V];
       pooled_grad<T, V>(s_dy, s_ix, d, k, 2 * k + r, iw, cv, g);
 #pragma unroll
@@ -475,14 +520,18 @@ __global__ void __launch_bounds__(kBpThreads) bn_pool_bwd_reduce_kernel(
         const float xf = (float)to_acc<T>(xv.v[c]);
         const float gz = (xf * sc[c] + sh[c] > 0.f) ? g[c] : 0.f;
         a[c] += gz;
-        b[c] += gz * (xf - mu[c]) * is[c];
+        b[c] += gz * xf;
       }
     }
   }
   __syncthreads();
   __shared__ float s[kBpThreads][2 * V + 1];
 #pragma unroll
-  for (int k = 0; k < V; ++k) { s[threadIdx.x][k] = a[k]; s[threadIdx.x][V + k] = b[k]; }
+  for (int k = 0; k < V; ++k) {
+    const int c = cv * V + k;
+    s[threadIdx.x][k] = a[k];
+    s[threadIdx.x][V + k] = (b[k] - mean[c] * a[k]) * invstd[c];
+  }
   __syncthreads();
   for (int o = threadIdx.x; o < cvn * 2 * V; o += kBpThreads) {
     const int c = o / (2 * V), k = o % (2 * V);
@@ -495,7 +544,7 @@ __global__ void __launch_bounds__(kBpThreads) bn_pool_bwd_reduce_kernel(
 
 // backward apply: one block per row pair
 template <typename T, int V>
-__global__ void __launch_bounds__(kBpThreads) bn_pool_bwd_apply_kernel(
+__global__ void __launch_bounds__(kBpThreads, 3) bn_pool_bwd_apply_kernel(
     const T* __restrict__ x, const T* __restrict__ dy, const unsigned char* __restrict__ idx, T* __restrict__ dx,
     const float* __restrict__ gamma, const float* __restrict__ beta, const float* __restrict__ mean,
     const float* __restrict__ invstd, const float* __restrict__ dgamma, const float* __restrict__ dbeta, BpDims d, float inv_m) {
@@ -503,35 +552,39 @@ __global__ void __launch_bounds__(kBpThreads) bn_pool_bwd_apply_kernel(
   const int cvn = d.C / V;
   T* s_dy = reinterpret_cast<T*>(s_raw);
   unsigned char* s_ix = s_raw + (size_t)2 * (d.OW + 1) * d.C * sizeof(T);
+  T* s_x = reinterpret_cast<T*>(s_raw + (size_t)2 * (d.OW + 1) * d.C * (sizeof(T) + 1));
   const int hp = (d.H + 1) / 2;
   const int n = blockIdx.x / hp, k = blockIdx.x - n * hp;
   const int cv = threadIdx.x % cvn;                  // fixed channel group
-  float mu[V], is[V], k1[V], k2[V], k3[V], sh[V];
+  // dx = k1 * (dz - dbeta/M - xhat * dgamma/M) with xhat = (x - mean) * invstd, folded to k1 * dz + ca * x + cb
+  float k1[V], sh[V], ca[V], cb[V];
 #pragma unroll
   for (int c = 0; c < V; ++c) {
     const int ch = cv * V + c;
-    mu[c] = mean[ch]; is[c] = invstd[ch];
-    k1[c] = gamma[ch] * is[c];
-    k2[c] = dbeta[ch] * inv_m;
-    k3[c] = dgamma[ch] * inv_m;
-    sh[c] = beta[ch] - mu[c] * k1[c];
+    const float mu = mean[ch], is = invstd[ch];
+    k1[c] = gamma[ch] * is;
+    sh[c] = beta[ch] - mu * k1[c];
+    ca[c] = -k1[c] * dgamma[ch] * inv_m * is;
+    cb[c] = -k1[c] * dbeta[ch] * inv_m - ca[c] * mu;
   }
-  stage_pool_rows<T, V>(dy, idx, d, n, k, s_dy, s_ix);
-  __syncthreads();
   const int rows_here = min(2, d.H - 2 * k);
   const size_t irow = ((size_t)n * d.H + 2 * k) * d.W * d.C;
-  for (int t = threadIdx.x; t < rows_here * d.W * cvn; t += kBpThreads) {
+  const int items = rows_here * d.W * cvn;
+  stage_pool_rows<T, V>(dy, idx, d, n, k, s_dy, s_ix);
+  stage_x_rows<T, V>(x + irow, s_x, items);
+  __syncthreads();
+#pragma unroll 1
+  for (int t = threadIdx.x; t < items; t += kBpThreads) {
     const int pos = t / cvn;
     const int r = pos / d.W, iw = pos - r * d.W;
-    Pack<T, V> xv = ld_pack<T, V>(x + irow + (size_t)t * V), ox;
+    Pack<T, V> xv = ld_pack<T, V>(s_x + (size_t)t * V), ox;
     float g[V];
     pooled_grad<T, V>(s_dy, s_ix, d, k, 2 * k + r, iw, cv, g);
 #pragma unroll
     for (int c = 0; c < V; ++c) {
       const float xf = (float)to_acc<T>(xv.v[c]);
       const float gz = (xf * k1[c] + sh[c] > 0.f) ? g[c] : 0.f;
-      const float xhat = (xf - mu[c]) * is[c];
-      ox.v[c] = from_acc<T>((typename AccOf<T>::type)(k1[c] * (gz - k2[c] - xhat * k3[c])));
+      ox.v[c] = from_acc<T>((typename AccOf<T>::type)(k1[c] * gz + ca[c] * xf + cb[c]));
     }
     st_pack<T, V>(dx + irow + (size_t)t * V, ox);
   }
@@ -539,7 +592,9 @@ __global__ void __launch_bounds__(kBpThreads) bn_pool_bwd_apply_kernel(
 
 // shared memory of the two stages, and the limit under which they are offered
 template <typename T> static size_t bn_pool_fwd_smem(const BpDims& d) { return (size_t)3 * (d.W + 2) * d.C * sizeof(T); }
-template <typename T> static size_t bn_pool_bwd_smem(const BpDims& d) { return (size_t)2 * (d.OW + 1) * d.C * (sizeof(T) + 1); }
+template <typename T> static size_t bn_pool_bwd_smem(const BpDims& d) {
+  return (size_t)2 * (d.OW + 1) * d.C * (sizeof(T) + 1) + (size_t)2 * d.W * d.C * sizeof(T);
+}
 constexpr size_t kBpMaxSmem = 96 * 1024;
 
 template <typename T>
