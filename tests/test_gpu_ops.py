@@ -178,10 +178,13 @@ def test_stem_conv_matches_conv2d():
         gemm.check_status()
 
 
+@pytest.mark.parametrize("fused_bwd", [0, 1])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
-def test_bn_relu_maxpool_stage_matches_separate_ops(dtype):
+def test_bn_relu_maxpool_stage_matches_separate_ops(dtype, fused_bwd):
     """Batch-norm + ReLU + max-pool in one stage against the three PyTorch ops in fp32 on the same input."""
+    from torchmpi_b200 import config
     from torchmpi_b200.ops.bn_relu import FusedBatchNormReLUMaxPool
+    config.set("bn_pool_fused_bwd", fused_bwd)
     torch.manual_seed(7)
     for N, C, H, W in ((4, 64, 112, 112), (2, 16, 33, 47), (3, 32, 16, 16)):
         x = torch.randn(N, C, H, W, device="cuda").to(dtype).contiguous(memory_format=torch.channels_last).requires_grad_(True)

@@ -8,6 +8,7 @@
 // Traffic is one read of the input and one write of output + index forward, and a read of
 // dy + index and one write of dx backward.
 #include "vec.cuh"
+#include "pool_rows.cuh"
 #include "../include/tmpi_c_api.h"
 #include "../runtime/common.h"
 #include <algorithm>
@@ -137,6 +138,35 @@ __global__ void __launch_bounds__(256) maxpool_bwd_kernel(const T* __restrict__ 
   }
 }
 
+// 3x3 / stride 2 / pad 1: one block per pair of input rows, gathering from the two output rows that
+// cover them after staging those in shared memory (each pooled gradient is otherwise fetched from L2
+// by every input position of its window, and the kernel is bound by L2 bandwidth).
+template <typename T, int V>
+__global__ void __launch_bounds__(kBpThreads) maxpool_bwd_rows_kernel(const T* __restrict__ dy, const unsigned char* __restrict__ idx,
+                                                                      T* __restrict__ dx, BpDims d) {
+  extern __shared__ __align__(16) unsigned char s_raw[];
+  const int cvn = d.C / V;
+  T* s_dy = reinterpret_cast<T*>(s_raw);
+  unsigned char* s_ix = s_raw + (size_t)2 * (d.OW + 1) * d.C * sizeof(T);
+  const int hp = (d.H + 1) / 2;
+  const int n = blockIdx.x / hp, k = blockIdx.x - n * hp;
+  const int cv = threadIdx.x % cvn;                  // kBpThreads is a multiple of cvn
+  stage_pool_rows<T, V>(dy, idx, d, n, k, s_dy, s_ix);
+  __syncthreads();
+  const int rows_here = min(2, d.H - 2 * k);
+  const size_t irow = ((size_t)n * d.H + 2 * k) * d.W * d.C;
+  for (int t = threadIdx.x; t < rows_here * d.W * cvn; t += kBpThreads) {
+    const int pos = t / cvn;
+    const int r = pos / d.W, iw = pos - r * d.W;
+    float g[V];
+    pooled_grad<T, V>(s_dy, s_ix, d, k, 2 * k + r, iw, cv, g);
+    Pack<T, V> out;
+#pragma unroll
+    for (int c = 0; c < V; ++c) out.v[c] = from_acc<T>((typename AccOf<T>::type)g[c]);
+    st_pack<T, V>(dx + irow + (size_t)t * V, out);
+  }
+}
+
 template <typename T>
 static int pool_launch(bool fwd, const void* a, void* b, void* idx, PoolDims d, cudaStream_t s) {
   constexpr int V = 16 / sizeof(T);
@@ -145,7 +175,14 @@ static int pool_launch(bool fwd, const void* a, void* b, void* idx, PoolDims d, 
   const long long rows = (long long)d.N * (fwd ? d.OH : d.H);
   if (rows < 1 || rows > 0x7fffffffLL) return fail(TMPI_ERR_INVALID, "maxpool: %lld rows", rows);
   int grid = (int)rows;
-  if (fwd && d.k == 3) maxpool_fwd_kernel<T, V, true><<<grid, 256, 0, s>>>((const T*)a, (T*)b, (unsigned char*)idx, d);
+  const size_t rows_smem = (size_t)2 * (d.OW + 1) * d.C * (sizeof(T) + 1);
+  if (!fwd && d.k == 3 && d.s == 2 && d.p == 1 && kBpThreads % (d.C / V) == 0 && rows_smem <= 96 * 1024 &&
+      d.OH == (d.H - 1) / 2 + 1 && d.OW == (d.W - 1) / 2 + 1) {
+    static bool attr = false;
+    if (!attr) { cudaFuncSetAttribute(maxpool_bwd_rows_kernel<T, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); attr = true; }
+    BpDims bd{d.N, d.H, d.W, d.C, d.OH, d.OW};
+    maxpool_bwd_rows_kernel<T, V><<<d.N * ((d.H + 1) / 2), kBpThreads, rows_smem, s>>>((const T*)a, (const unsigned char*)idx, (T*)b, bd);
+  } else if (fwd && d.k == 3) maxpool_fwd_kernel<T, V, true><<<grid, 256, 0, s>>>((const T*)a, (T*)b, (unsigned char*)idx, d);
   else if (fwd) maxpool_fwd_kernel<T, V, false><<<grid, 256, 0, s>>>((const T*)a, (T*)b, (unsigned char*)idx, d);
   else if (d.k <= 2 * d.s) maxpool_bwd_kernel<T, V, true><<<grid, 256, 0, s>>>((const T*)a, (const unsigned char*)idx, (T*)b, d);
   else maxpool_bwd_kernel<T, V, false><<<grid, 256, 0, s>>>((const T*)a, (const unsigned char*)idx, (T*)b, d);

@@ -54,6 +54,7 @@ Tunable g_tunables[] = {
   {"heap_bytes", {int64_t(1) << 30}},      // symmetric heap per rank
   {"staging_bytes", {64 << 20}},           // bounce buffer inside the heap for foreign tensors
   {"use_nvls", {1}},
+  {"bn_pool_fused_bwd", {0}},              // stem batch-norm + pool backward as one stage (slower than pool, then batch-norm)
   {"bn_reverse_stats", {1}},               // batch-norm statistics passes walk the tensor from its end (L2 reuse)
   {"gemm_pair", {1}},                      // 256 x 256 tiles on CTA pairs (cta_group::2) where the shape allows
   {"ps_poll_us", {100}},

@@ -14,6 +14,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from .. import config
 from .._lib import lib, check, dtype_code, has_symbol, stream_ptr
 
 launch_count = 0
@@ -123,11 +124,25 @@ class _BnReluPoolFn(torch.autograd.Function):
         dx = torch.empty_like(x, memory_format=torch.channels_last)
         dgamma = torch.empty(C, dtype=torch.float32, device=x.device)
         dbeta = torch.empty(C, dtype=torch.float32, device=x.device)
-        check(lib.tmpi_bn_relu_pool_bwd(
-            x.data_ptr(), dy.data_ptr(), idx.data_ptr(), dx.data_ptr(), gamma.data_ptr(), beta.data_ptr(),
-            mean.data_ptr(), invstd.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(), N, H, W, C, dtype_code(x.dtype),
-            _scratch_for(x.device, C).data_ptr(), stream_ptr()))
-        launch_count += 3
+        if config.get("bn_pool_fused_bwd"):
+            # one stage: both batch-norm passes rebuild the pool's gradient routing from dy and the index
+            check(lib.tmpi_bn_relu_pool_bwd(
+                x.data_ptr(), dy.data_ptr(), idx.data_ptr(), dx.data_ptr(), gamma.data_ptr(), beta.data_ptr(),
+                mean.data_ptr(), invstd.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(), N, H, W, C, dtype_code(x.dtype),
+                _scratch_for(x.device, C).data_ptr(), stream_ptr()))
+            launch_count += 3
+        else:
+            # measured faster: route the gradient through the pool once, then the batch-norm backward with the
+            # ReLU mask rebuilt from x (the rectified activation itself was never stored)
+            OH, OW = dy.shape[2], dy.shape[3]
+            da = torch.empty_like(x, memory_format=torch.channels_last)
+            check(lib.tmpi_maxpool_bwd(dy.data_ptr(), idx.data_ptr(), da.data_ptr(), N, H, W, C, OH, OW, 3, 2, 1,
+                                       dtype_code(x.dtype), stream_ptr()))
+            check(lib.tmpi_bn_relu_bwd(
+                x.data_ptr(), None, da.data_ptr(), dx.data_ptr(), None, gamma.data_ptr(), beta.data_ptr(),
+                mean.data_ptr(), invstd.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(), N * H * W, C, 1,
+                dtype_code(x.dtype), _scratch_for(x.device, C).data_ptr(), stream_ptr()))
+            launch_count += 4
         return dx, dgamma, dbeta, None, None, None, None, None
 
 
