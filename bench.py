@@ -163,8 +163,8 @@ def main():
         n = engine._opt.launches if engine._opt is not None else 0
         n += getattr(xent, "launch_count", 0)
         try:
-            from torchmpi_b200.ops import bn_relu, pool
-            n += bn_relu.launch_count + pool.launch_count
+            from torchmpi_b200.ops import bn_relu, pool, stem_conv
+            n += bn_relu.launch_count + pool.launch_count + stem_conv.launch_count
         except ImportError:
             pass
         return n

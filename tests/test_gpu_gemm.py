@@ -74,6 +74,23 @@ def test_gemm_reads_second_operand_as_k_by_n(M, N, K):
     assert torch.equal(y, y_t)
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (384, 512, 200), (1024, 2048, 1000), (4096, 1024, 8192)])
+def test_gemm_transposed_first_operand(M, N, K):
+    """``matmul_tn(a, b) = a.T @ b`` with ``a [K, M]`` and ``b [K, N]`` as stored (the weight-gradient layout):
+    same bits as the K-major kernel on transposed copies, and the fp32 product within rounding."""
+    from torchmpi_b200.ops import gemm
+    torch.manual_seed(2 * M + 3 * N + K)
+    a = torch.randn(K, M, device="cuda").to(torch.bfloat16)
+    b = (torch.randn(K, N, device="cuda") * 0.2).to(torch.bfloat16)
+    y = gemm.matmul_tn(a, b)
+    y_t = gemm.matmul_nt(a.t().contiguous(), b.t().contiguous())
+    torch.cuda.synchronize()
+    gemm.check_status()
+    ref = a.float().t() @ b.float()
+    assert torch.allclose(y.float(), ref, rtol=1e-2, atol=0.02 * (K ** 0.5))
+    assert torch.equal(y, y_t)
+
+
 def test_gemm_epilogues_and_identity():
     from torchmpi_b200.ops import gemm
     torch.manual_seed(0)

@@ -29,7 +29,8 @@ constexpr int EPI_STAGING_BYTES = 2 * BM * 64 * 2;           // two 128 x 64 bf1
 constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + EPI_STAGING_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 constexpr unsigned long long kWaitBudgetNs = 4000000000ull;   // 4 s: far beyond any legitimate wait
 
-enum { EPI_NONE = 0, EPI_BIAS = 1, EPI_GELU = 2, EPI_BIAS_GELU = 3, B_IS_KN = 4 /* flag in the same word */ };
+enum { EPI_NONE = 0, EPI_BIAS = 1, EPI_GELU = 2, EPI_BIAS_GELU = 3,
+       B_IS_KN = 4, A_IS_KM = 8 /* operand layout flags in the same word */ };
 
 struct Shared {
   uint64_t full[STAGES], empty[STAGES], acc_full[2], acc_empty[2];
@@ -44,6 +45,7 @@ struct Problem {
   const __nv_bfloat16* bias;   // [N] or nullptr
   int tma_store;               // epilogue writes through TMA (needs 16-byte aligned rows of C)
   int b_mn;                    // B is given as [K, N] with N contiguous (CTA-pair kernels only)
+  int a_mn;                    // A is given as [K, M] with M contiguous (plain CTA-pair GEMM only)
   int mma_n;                   // single-CTA kernel, narrow outputs: rows of B staged per tile and N of the MMA
                                // (a multiple of 16 below BN); 0 = BN
   int* status;                 // global error word (nullptr: none)

@@ -84,15 +84,22 @@ static int max_clusters() {
 }  // namespace gemm2
 
 // Shapes the pair kernel takes: TMA-storable C and at least one full pair tile each way.
-bool gemm_pair_applicable(const void* C, int M, int N, int K) {
-  return M >= 2 * gemm2::BM && N >= gemm2::BN && N % 8 == 0 && K % 8 == 0 && ((uintptr_t)C & 15) == 0;
+bool gemm_pair_applicable(const void* C, int M, int N, int K, int flags) {
+  const bool a_km = (flags & gemm::A_IS_KM) != 0, b_kn = (flags & gemm::B_IS_KN) != 0;
+  if (M < 2 * gemm2::BM || N < gemm2::BN || N % 8 || ((uintptr_t)C & 15)) return false;
+  if ((a_km ? M : K) % 8) return false;          // 16-byte rows of A as stored
+  if (!b_kn && K % 8) return false;              // 16-byte rows of B as stored ([K, N] rows are covered by N % 8)
+  return true;
 }
 
 int launch_gemm_pair(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int epilogue,
                      int* status_word, cudaStream_t stream) {
   CUtensorMap ma, mb, mc;
   int st;
-  if ((st = make_tmap_bf16(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)K, gemm2::BM))) return st;
+  const bool a_km = (epilogue & gemm::A_IS_KM) != 0;       // A given as [K, M], M contiguous
+  if (a_km) st = make_tmap_bf16(&ma, A, (uint64_t)K, (uint64_t)M, (uint64_t)M, gemm2::BK);
+  else st = make_tmap_bf16(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)K, gemm2::BM);
+  if (st) return st;
   const bool b_kn = (epilogue & gemm::B_IS_KN) != 0;       // B given as [K, N], N contiguous
   if (b_kn) st = make_tmap_bf16(&mb, B, (uint64_t)K, (uint64_t)N, (uint64_t)N, gemm2::BK);
   else st = make_tmap_bf16(&mb, B, (uint64_t)N, (uint64_t)K, (uint64_t)K, gemm2::BN / 2);
@@ -105,6 +112,7 @@ int launch_gemm_pair(const void* A, const void* B, void* C, const void* bias, in
   p.k_blocks = (K + gemm2::BK - 1) / gemm2::BK;
   p.epilogue = epilogue & 3;
   p.b_mn = b_kn ? 1 : 0;
+  p.a_mn = a_km ? 1 : 0;
   p.bias = (const __nv_bfloat16*)bias;
   p.tma_store = 1;
   p.status = status_word;

@@ -84,7 +84,12 @@ __device__ __forceinline__ void producer(Shared* sh, unsigned char* tiles, const
       unsigned char* a_dst = tiles + (size_t)stage * STAGE_BYTES;
       const uint32_t full0 = sm100::map_to_cta(&sh->full[stage], 0);
       if (rank == 0) sm100::mbar_expect_tx(&sh->full[stage], 2 * STAGE_BYTES);   // both CTAs' bytes
-      sm100::tma_load_2d_pair(a_dst, a_map, kb * BK, a_row0, full0);
+      if (!p.a_mn) {
+        sm100::tma_load_2d_pair(a_dst, a_map, kb * BK, a_row0, full0);
+      } else {   // A is [K, M]: two boxes of 64 rows of the product x 64 k-rows
+        sm100::tma_load_2d_pair(a_dst, a_map, a_row0, kb * BK, full0);
+        sm100::tma_load_2d_pair(a_dst + A_BYTES / 2, a_map, a_row0 + 64, kb * BK, full0);
+      }
       if (!p.b_mn) {
         sm100::tma_load_2d_pair(a_dst + A_BYTES, mb, kb * BK, b_row0, full0);
       } else {   // B is [K, N]: two boxes of 64 columns x 64 k-rows, each a column of eight swizzle atoms
@@ -99,7 +104,7 @@ __device__ __forceinline__ void producer(Shared* sh, unsigned char* tiles, const
 // One thread of the EVEN CTA only.
 template <typename TileOrder>
 __device__ __forceinline__ void mma_issuer(Shared* sh, unsigned char* tiles, const Problem& p, TileOrder order) {
-  const uint32_t idesc = sm100::make_idesc_f16(2 * BM, BN, true, p.b_mn != 0);
+  const uint32_t idesc = sm100::make_idesc_f16(2 * BM, BN, true, p.b_mn != 0, p.a_mn != 0);
   int stage = 0;
   uint32_t phase = 0;
   int m_blk, n_blk;
@@ -116,7 +121,8 @@ __device__ __forceinline__ void mma_issuer(Shared* sh, unsigned char* tiles, con
       const uint32_t b_addr = a_addr + A_BYTES;
 #pragma unroll
       for (int k = 0; k < BK / UMMA_K; ++k) {
-        const uint64_t da = sm100::make_desc_sw128(a_addr + k * UMMA_K * 2);
+        const uint64_t da = p.a_mn ? sm100::make_desc_sw128_mn(a_addr + k * UMMA_K * 128, A_BYTES / 2, 1024)
+                                   : sm100::make_desc_sw128(a_addr + k * UMMA_K * 2);
         const uint64_t db = p.b_mn ? sm100::make_desc_sw128_mn(b_addr + k * UMMA_K * 128, B_BYTES / 2, 1024)
                                    : sm100::make_desc_sw128(b_addr + k * UMMA_K * 2);
         sm100::umma_f16_pair(d_tmem, da, db, idesc, (kb | k) != 0);

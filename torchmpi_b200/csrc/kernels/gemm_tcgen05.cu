@@ -107,7 +107,7 @@ int gemm_sm_count() {
   return n;
 }
 
-bool gemm_pair_applicable(const void* C, int M, int N, int K);
+bool gemm_pair_applicable(const void* C, int M, int N, int K, int flags);
 int launch_gemm_pair(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int epilogue,
                      int* status_word, cudaStream_t stream);
 
@@ -133,11 +133,13 @@ extern "C" {
 int tmpi_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int epilogue,
                    void* stream) {
   if (M < 1 || N < 1 || K < 1) return fail(TMPI_ERR_INVALID, "gemm: empty problem");
-  if (K % 8) return fail(TMPI_ERR_INVALID, "gemm: K must be a multiple of 8 (16-byte rows for TMA)");
+  const bool k_rows = !(epilogue & gemm::A_IS_KM) || !(epilogue & gemm::B_IS_KN);   // some operand has K contiguous
+  if (k_rows && K % 8) return fail(TMPI_ERR_INVALID, "gemm: K must be a multiple of 8 (16-byte rows for TMA)");
   if ((epilogue & gemm::EPI_BIAS) && !bias) return fail(TMPI_ERR_INVALID, "gemm: bias epilogue without bias");
-  if (tunable("gemm_pair") && gemm_pair_applicable(C, M, N, K))
+  if (tunable("gemm_pair") && gemm_pair_applicable(C, M, N, K, epilogue))
     return launch_gemm_pair(A, B, C, bias, M, N, K, epilogue, gemm_status_word(), (cudaStream_t)stream);
-  if (epilogue & gemm::B_IS_KN) return fail(TMPI_ERR_UNSUPPORTED, "gemm: B as [K, N] needs the CTA-pair kernel (M, N >= 256, N %% 8 == 0)");
+  if (epilogue & (gemm::B_IS_KN | gemm::A_IS_KM))
+    return fail(TMPI_ERR_UNSUPPORTED, "gemm: operands given as [K, M] / [K, N] need the CTA-pair kernel (M, N >= 256, M, N %% 8 == 0)");
   CUtensorMap ma, mb;
   int st = make_tmap_bf16(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)K, gemm::BM);
   if (st) return st;

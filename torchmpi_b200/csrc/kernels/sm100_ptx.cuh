@@ -134,10 +134,12 @@ __device__ __forceinline__ uint64_t make_desc_sw128_mn(uint32_t smem_addr, uint3
 
 // Instruction descriptor: fp32 accumulate, bf16 x bf16 (or f16 x f16); operands K-major unless
 // b_mn_major says that B is MN-major.
-__host__ __device__ constexpr uint32_t make_idesc_f16(int M, int N, bool bf16, bool b_mn_major = false) {
+__host__ __device__ constexpr uint32_t make_idesc_f16(int M, int N, bool bf16, bool b_mn_major = false,
+                                                      bool a_mn_major = false) {
   return (1u << 4)                                       // D format: f32
          | ((bf16 ? 1u : 0u) << 7)                       // A format
          | ((bf16 ? 1u : 0u) << 10)                      // B format
+         | ((a_mn_major ? 1u : 0u) << 15)                // A major
          | ((b_mn_major ? 1u : 0u) << 16)                // B major
          | ((uint32_t)(N >> 3) << 17)                    // N / 8
          | ((uint32_t)(M >> 4) << 24);                   // M / 16

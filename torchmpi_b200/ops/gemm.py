@@ -2,8 +2,8 @@
 
 ``matmul_nt(a, b)`` computes ``a @ b.T`` for row-major ``a [M, K]`` and ``b [N, K]`` (K contiguous,
 bf16), optionally with bias and GELU in the epilogue.  ``linear(x, w, bias, gelu)`` is the autograd
-version: ``dX = dY @ W`` reads W as it lies (``matmul_nn``); ``dW = dY.T @ X`` runs the same kernel
-on transposed copies.
+version: ``dX = dY @ W`` (``matmul_nn``) and ``dW = dY.T @ X`` (``matmul_tn``) read their operands as they
+lie, through MN-major shared-memory descriptors, so backward makes no transposed copies.
 """
 from __future__ import annotations
 
@@ -15,6 +15,12 @@ from .._lib import lib, check, has_symbol, stream_ptr, TorchMPIError
 
 EPI_NONE, EPI_BIAS, EPI_GELU = 0, 1, 2
 B_IS_KN = 4          # flag in the same word: the second operand is [K, N] with N contiguous
+A_IS_KM = 8          # the first operand is [K, M] with M contiguous
+
+
+def config_get(name: str) -> int:
+    from .. import config
+    return config.get(name)
 launch_count = 0
 
 
@@ -67,6 +73,25 @@ def matmul_nn(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = No
     return out
 
 
+def matmul_tn(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``a.T @ b`` for row-major ``a [K, M]`` and ``b [K, N]``: both operands are read as they lie
+    (MN-major descriptors), which is the layout of a weight gradient ``dY.T @ X``.  Shapes the CTA-pair
+    kernel does not take fall back to transposed copies."""
+    global launch_count
+    a, b = a.contiguous(), b.contiguous()
+    K, M = a.shape
+    N = b.shape[1]
+    ok = (bool(config_get("gemm_pair")) and M >= 256 and N >= 256 and M % 8 == 0 and N % 8 == 0 and a.is_cuda
+          and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16)
+    if not ok:
+        return matmul_nt(a.t().contiguous(), b.t().contiguous(), out=out)
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+    check(lib.tmpi_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), None, M, N, K, A_IS_KM | B_IS_KN, stream_ptr()))
+    launch_count += 1
+    return out
+
+
 def check_status() -> None:
     """Raises if a GEMM CTA gave up on one of its bounded waits since the last call."""
     st = lib.tmpi_gemm_status()
@@ -95,7 +120,7 @@ class _LinearFn(torch.autograd.Function):
         if ctx.gelu:
             dy2 = torch.ops.aten.gelu_backward(dy2, z)
         dx = matmul_nn(dy2, w) if ctx.needs_input_grad[0] else None
-        dw = matmul_nt(dy2.t().contiguous(), x2.t().contiguous()) if ctx.needs_input_grad[1] else None
+        dw = matmul_tn(dy2, x2) if ctx.needs_input_grad[1] else None
         db = dy2.sum(0) if ctx.has_bias and ctx.needs_input_grad[2] else None
         return (dx.reshape(ctx.shape) if dx is not None else None), dw, db, None
 

@@ -139,13 +139,13 @@ class _TPMLPFn(torch.autograd.Function):
         dy_shard = dy_shard.contiguous()
         dh = tp.ag_gemm(dy_shard, tp.dfull_off, tp.dfull_buf, w2, None, w_is_kn=True)        # [M, F/R] = dy @ w2
         dy_full = tp.dfull_buf[:tp.M * tp.d].view(tp.M, tp.d)
-        # the two weight gradients are plain local GEMMs on operands whose contraction dimension is the
-        # slow one: the library GEMM takes them as they lie, without materialising transposes
-        dw2 = torch.matmul(dy_full.t(), h)                                                    # [D, F/R]
+        # the two weight gradients are local GEMMs whose contraction dimension is the slow one of both
+        # operands: the CTA-pair kernel reads them as they lie (MN-major descriptors)
+        dw2 = gemm.matmul_tn(dy_full, h)                                                      # [D, F/R]
         db2 = dy_full.sum(0, dtype=torch.float32).to(dy_full.dtype) if ctx.has_b2 else None
         dz = torch.ops.aten.gelu_backward(dh, z)
         dx = tp.gemm_rs(dz, w1, w_is_kn=True)                                                 # [rows, D] = dz @ w1
-        dw1 = torch.matmul(dz.t(), x_full)                                                    # [F/R, D]
+        dw1 = gemm.matmul_tn(dz, x_full)                                                      # [F/R, D]
         db1 = dz.sum(0, dtype=torch.float32).to(dz.dtype) if ctx.has_b1 else None
         return dx, dw1, db1, dw2, db2, None, None, None
 
