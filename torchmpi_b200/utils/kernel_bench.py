@@ -103,6 +103,12 @@ def cases(small: bool):
             finally:
                 config.set("gemm_pair", 1)
         out[name + "_1cta"] = (single, (M * K + N * K + M * N) * 2, 2.0 * M * N * K)
+        if name == "gemm_bf16_tp_col":      # operands read as stored for dX = dY W and dW = dY^T X
+            b_kn, a_km = b.t().contiguous(), a.t().contiguous()
+            out[name + "_b_as_kn"] = (lambda a=a, b_kn=b_kn, c=c: gemm.matmul_nn(a, b_kn, out=c),
+                                      (M * K + N * K + M * N) * 2, 2.0 * M * N * K)
+            out[name + "_a_as_km_b_as_kn"] = (lambda a_km=a_km, b_kn=b_kn, c=c: gemm.matmul_tn(a_km, b_kn, out=c),
+                                              (M * K + N * K + M * N) * 2, 2.0 * M * N * K)
         out[name + "_cublas"] = (lambda a=a, b=b, c=c: torch.matmul(a, b.t(), out=c), (M * K + N * K + M * N) * 2,
                                  2.0 * M * N * K)
     return out
