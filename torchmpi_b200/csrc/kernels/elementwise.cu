@@ -241,9 +241,27 @@ __device__ __forceinline__ void absstat_body(const T* __restrict__ x, size_t n, 
   __shared__ double s1[kStatThreads / 32], s2[kStatThreads / 32];
   __shared__ bool s_last;
   double a = 0.0, b = 0.0;
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
-    double v = fabs((double)to_acc<T>(x[i]));
-    a += v; b += v * v;
+  const size_t t0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x, stride = (size_t)gridDim.x * blockDim.x;
+  // 16-byte packs over the aligned body (two loads in flight per thread), single elements before and after it
+  constexpr int V = 16 / sizeof(T);
+  const size_t mis = ((uintptr_t)x & 15) / sizeof(T);
+  const size_t head = mis ? (V - mis < n ? V - mis : n) : 0;
+  const size_t nv = (n - head) / V, tail0 = head + nv * V;
+  for (size_t i = t0; i < head; i += stride) { double v = fabs((double)to_acc<T>(x[i])); a += v; b += v * v; }
+  for (size_t i = tail0 + t0; i < n; i += stride) { double v = fabs((double)to_acc<T>(x[i])); a += v; b += v * v; }
+  const T* xb = x + head;
+  size_t i = t0;
+  for (; i + stride < nv; i += 2 * stride) {
+    Pack<T, V> p0 = ld_pack<T, V>(xb + i * V), p1 = ld_pack<T, V>(xb + (i + stride) * V);
+#pragma unroll
+    for (int k = 0; k < V; ++k) { double v = fabs((double)to_acc<T>(p0.v[k])); a += v; b += v * v; }
+#pragma unroll
+    for (int k = 0; k < V; ++k) { double v = fabs((double)to_acc<T>(p1.v[k])); a += v; b += v * v; }
+  }
+  for (; i < nv; i += stride) {
+    Pack<T, V> p0 = ld_pack<T, V>(xb + i * V);
+#pragma unroll
+    for (int k = 0; k < V; ++k) { double v = fabs((double)to_acc<T>(p0.v[k])); a += v; b += v * v; }
   }
   for (int o = 16; o; o >>= 1) { a += __shfl_xor_sync(~0u, a, o); b += __shfl_xor_sync(~0u, b, o); }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
