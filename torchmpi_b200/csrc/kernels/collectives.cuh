@@ -139,6 +139,36 @@ __device__ __forceinline__ void copy_packs(T* dst, const T* src, size_t len, siz
   for (; i < len; i += stride) st_pack_peer<T, V>(dst + i * V, ld_pack_peer<T, V>(src + i * V));
 }
 
+// out[i] = scale * sum over members (in member order) of the pack at element offset `first` + i * V of
+// the symmetric buffer at in_off; U vectors per thread and iteration, so U loads per peer are in flight
+template <typename T, int V>
+__device__ __forceinline__ void sum_from_peers(const Peers& P, size_t in_off, size_t first, T* out, size_t nv, float scale,
+                                               size_t t0, size_t stride) {
+  constexpr int U = V * sizeof(T) == 16 ? 4 : 2;
+  size_t i = t0;
+  for (; i + (U - 1) * stride < nv; i += U * stride) {
+    Acc<T, V> acc[U];
+    for (int m = 0; m < P.n; ++m) {
+      const T* src = at<T>(P.base[m], in_off) + first;
+      Pack<T, V> x[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) x[u] = ld_pack_peer<T, V>(src + (i + u * stride) * V);
+#pragma unroll
+      for (int u = 0; u < U; ++u) { if (m == 0) acc[u].set(x[u]); else acc[u].add(x[u]); }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) st_pack<T, V>(out + (i + u * stride) * V, acc[u].pack(scale));
+  }
+  for (; i < nv; i += stride) {
+    Acc<T, V> acc;
+    for (int m = 0; m < P.n; ++m) {
+      Pack<T, V> x = ld_pack_peer<T, V>(at<T>(P.base[m], in_off) + first + i * V);
+      if (m == 0) acc.set(x); else acc.add(x);
+    }
+    st_pack<T, V>(out + i * V, acc.pack(scale));
+  }
+}
+
 template <typename T, int V>
 __device__ void body_ar_twoshot_any(const CollArgs& a, int* s_abort) {
   const Peers& P = a.P;
@@ -322,8 +352,7 @@ __device__ void body_bcast_pull(const CollArgs& a, int* s_abort) {
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     T* dst = at<T>(P.base[P.me], a.out_off);
     const T* src = at<T>(P.base[a.root], a.out_off);
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nv; i += stride)
-      st_pack<T, V>(dst + i * V, ld_pack_peer<T, V>(src + i * V));
+    copy_packs<T, V, 8>(dst, src, nv, (size_t)blockIdx.x * blockDim.x + threadIdx.x, stride);
   }
   peer_barrier(P, 2, 51, s_abort);
 }
@@ -426,14 +455,7 @@ __device__ void body_reduce(const CollArgs& a, int* s_abort) {
   if (P.me == a.root) {
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     T* out = reinterpret_cast<T*>(a.out);
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nv; i += stride) {
-      Acc<T, V> acc;
-      for (int m = 0; m < P.n; ++m) {
-        Pack<T, V> x = ld_pack_peer<T, V>(at<T>(P.base[m], a.in_off) + i * V);
-        if (m == 0) acc.set(x); else acc.add(x);
-      }
-      st_pack<T, V>(out + i * V, acc.pack(a.scale));
-    }
+    sum_from_peers<T, V>(P, a.in_off, 0, out, nv, a.scale, (size_t)blockIdx.x * blockDim.x + threadIdx.x, stride);
   }
   peer_barrier(P, 2, 61, s_abort);
 }
@@ -453,7 +475,7 @@ __device__ void body_allgather(const CollArgs& a, int* s_abort) {
     for (int q = 0; q < m; ++q) o += a.cnt[q];
     const T* src = at<T>(P.base[m], a.in_off);
     const size_t nv = a.cnt[m] / V;
-    for (size_t i = t0; i < nv; i += stride) st_pack<T, V>(out + o + i * V, ld_pack_peer<T, V>(src + i * V));
+    copy_packs<T, V, 8>(out + o, src, nv, t0, stride);
   }
   (void)off;
   peer_barrier(P, 2, 71, s_abort);
@@ -467,14 +489,7 @@ __device__ void body_reduce_scatter(const CollArgs& a, int* s_abort) {
   if (!peer_barrier(P, 1, 80, s_abort)) return;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   T* out = reinterpret_cast<T*>(a.out);
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nv; i += stride) {
-    Acc<T, V> acc;
-    for (int m = 0; m < P.n; ++m) {
-      Pack<T, V> x = ld_pack_peer<T, V>(at<T>(P.base[m], a.in_off) + (size_t)P.me * a.n + i * V);
-      if (m == 0) acc.set(x); else acc.add(x);
-    }
-    st_pack<T, V>(out + i * V, acc.pack(a.scale));
-  }
+  sum_from_peers<T, V>(P, a.in_off, (size_t)P.me * a.n, out, nv, a.scale, (size_t)blockIdx.x * blockDim.x + threadIdx.x, stride);
   peer_barrier(P, 2, 81, s_abort);
 }
 
