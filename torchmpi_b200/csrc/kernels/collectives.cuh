@@ -395,7 +395,17 @@ __device__ void body_bcast_mc(const CollArgs& a, int* s_abort) {
     if (P.me == a.root) {
       const size_t stride = (size_t)gridDim.x * blockDim.x;
       const T* src = at<T>(P.base[P.me], a.out_off);
-      for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nv; i += stride) {
+      constexpr int U = 4;
+      size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+      for (; i + (U - 1) * stride < nv; i += U * stride) {
+        Pack<T, V> x[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) x[u] = ld_pack<T, V>(src + (i + u * stride) * V);
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          multimem_st(at<T>(P.mc_base, a.out_off) + (i + u * stride) * V, *reinterpret_cast<uint4*>(&x[u]));
+      }
+      for (; i < nv; i += stride) {
         Pack<T, V> x = ld_pack<T, V>(src + i * V);
         multimem_st(at<T>(P.mc_base, a.out_off) + i * V, *reinterpret_cast<uint4*>(&x));
       }

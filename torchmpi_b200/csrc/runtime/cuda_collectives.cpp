@@ -174,11 +174,13 @@ static int broadcast_heap(size_t off, size_t n, int dtype, int root, const tmpi_
   bool vec = al16(off) && bytes % 16 == 0;
   size_t items = vec ? bytes / 16 : bytes;
   int op = OP_BCAST_PULL;
+  // with two ranks a multicast store also sends the data back to the root: the pull is faster there
   bool mc_ok = h.mc_base && whole_heap(g) && vec && tunable("use_nvls");
+  const bool mc_auto = mc_ok && g->nmembers > 2;
   if (algo == 3 && mc_ok) op = OP_BCAST_MC;
   else if (algo == 2) op = OP_BCAST_CHUNKED;
   else if (algo == 0) {
-    if (mc_ok && bytes >= (size_t)tunable("nvls_min_bytes")) op = OP_BCAST_MC;
+    if (mc_auto && bytes >= (size_t)tunable("nvls_min_bytes")) op = OP_BCAST_MC;
     else if (bytes > (size_t)tunable("broadcast_size_gpu_tree_based") && g->nmembers > 2) op = OP_BCAST_CHUNKED;
   }
   return run_op(op, TMPI_U8, g, vec, items, s, [&](int, CollArgs* a) {
