@@ -122,7 +122,7 @@ def run(args) -> list:
                         elif op == "reduce":
                             mpi.reduce_tensor(0, t, out, backend=backend)
                         elif op == "allgather":
-                            mpi.allgather_tensor(t, out, backend=backend)
+                            mpi.allgather_tensor(t, out, backend=backend, equal_counts=args.benchmark)
                         elif op == "reduce_scatter":
                             mpi.reduce_scatter_tensor(t, out, backend=backend)
                     # correctness on the first run
