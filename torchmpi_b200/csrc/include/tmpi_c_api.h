@@ -233,11 +233,11 @@ int tmpi_bn_relu_fwd(const void* x, const void* residual, void* y, const float* 
                      const float* beta, float* running_mean, float* running_var,
                      float* save_mean, float* save_invstd, int64_t rows, int channels,
                      float eps, float momentum, int relu, int training, int dtype,
-                     void* scratch, void* stream);
+                     void* mask_bits, void* scratch, void* stream);
 int tmpi_bn_relu_bwd(const void* x, const void* y, const void* dy, void* dx, void* dresidual,
                      const float* gamma, const float* beta, const float* save_mean, const float* save_invstd,
                      float* dgamma, float* dbeta, int64_t rows, int channels, int relu, int dtype,
-                     void* scratch, void* stream);
+                     const void* mask_bits, void* scratch, void* stream);
 size_t tmpi_bn_scratch_bytes(int channels);
 // batch-norm + ReLU + max-pool (3x3, stride 2, pad 1) as one stage; y, idx: [N, (H-1)/2+1, (W-1)/2+1, C]
 int tmpi_bn_relu_pool_fwd(const void* x, void* y, void* idx, const float* gamma, const float* beta,

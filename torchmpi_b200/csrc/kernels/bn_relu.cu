@@ -38,7 +38,7 @@ template <typename T, int V, bool BWD, bool MASKX>
 __global__ void __launch_bounds__(kBnThreads, 4) bn_reduce_kernel(
     const T* __restrict__ x, const T* __restrict__ y, const T* __restrict__ dy,
     const float* __restrict__ mean, const float* __restrict__ invstd,
-    const float* __restrict__ gamma, const float* __restrict__ beta,
+    const float* __restrict__ gamma, const float* __restrict__ beta, const unsigned char* __restrict__ bits,
     size_t nvec, int C, int relu, int reverse, float* __restrict__ partial) {
   const int cvn = C / V;
   const size_t T0 = (size_t)blockIdx.x * kBnThreads + threadIdx.x;
@@ -65,7 +65,9 @@ __global__ void __launch_bounds__(kBnThreads, 4) bn_reduce_kernel(
   // U independent vectors per thread and iteration: the loads of all of them are issued before
   // the first use, so a thread keeps U (forward) or up to 3U (backward) 16-byte loads in flight
   constexpr int U = BWD ? 1 : 4;       // backward already has 2-3 loads per vector and no registers to spare
-  auto accumulate = [&](const Pack<T, V>& xv, const Pack<T, V>& gv, const Pack<T, V>& yv) {
+  // bits (backward, ReLU layers with a residual): one byte per vector written by the forward apply
+  // pass, bit k set where the output was positive; replaces the read of y
+  auto accumulate = [&](const Pack<T, V>& xv, const Pack<T, V>& gv, const Pack<T, V>& yv, unsigned mb = 0) {
     if (!BWD) {
 #pragma unroll
       for (int k = 0; k < V; ++k) { float f = (float)to_acc<T>(xv.v[k]); a[k] += f; b[k] += f * f; }
@@ -75,7 +77,9 @@ __global__ void __launch_bounds__(kBnThreads, 4) bn_reduce_kernel(
         float g = (float)to_acc<T>(gv.v[k]);
         if (mask_from_x) {
           if (!((float)to_acc<T>(xv.v[k]) * sc[k] + sh[k] > 0.f)) g = 0.f;
-        } else if (relu && !((float)to_acc<T>(yv.v[k]) > 0.f)) g = 0.f;
+        } else if (relu) {
+          if (bits ? !((mb >> k) & 1u) : !((float)to_acc<T>(yv.v[k]) > 0.f)) g = 0.f;
+        }
         a[k] += g;
         b[k] += g * ((float)to_acc<T>(xv.v[k]) - mu[k]) * is[k];
       }
@@ -98,11 +102,15 @@ __global__ void __launch_bounds__(kBnThreads, 4) bn_reduce_kernel(
   }
   for (; v < nvec; v += stride) {
     Pack<T, V> xv = ld_pack<T, V>(reverse ? xe - v * V : x + v * V), gv, yv;
+    unsigned mb = 0;
     if (BWD) {
       gv = ld_pack<T, V>(reverse ? ge - v * V : dy + v * V);
-      if (relu && !mask_from_x) yv = ld_pack<T, V>(reverse ? ye - v * V : y + v * V);
+      if (relu && !mask_from_x) {
+        if (bits) mb = bits[reverse ? nvec - 1 - v : v];
+        else yv = ld_pack<T, V>(reverse ? ye - v * V : y + v * V);
+      }
     }
-    accumulate(xv, gv, yv);
+    accumulate(xv, gv, yv, mb);
   }
   __shared__ float s[kBnThreads][2 * V + 1];
 #pragma unroll
@@ -177,7 +185,7 @@ template <typename T, int V>
 __global__ void __launch_bounds__(kBnThreads) bn_apply_fwd_kernel(
     const T* __restrict__ x, const T* __restrict__ res, T* __restrict__ y, const float* __restrict__ gamma,
     const float* __restrict__ beta, const float* __restrict__ mean, const float* __restrict__ invstd,
-    size_t nvec, int C, int relu) {
+    unsigned char* __restrict__ bits, size_t nvec, int C, int relu) {
   const int cvn = C / V;
   const size_t T0 = (size_t)blockIdx.x * kBnThreads + threadIdx.x;
   const size_t stride = (size_t)gridDim.x * kBnThreads;
@@ -191,6 +199,7 @@ __global__ void __launch_bounds__(kBnThreads) bn_apply_fwd_kernel(
   }
   for (size_t v = T0; v < nvec; v += stride) {
     Pack<T, V> xv = ld_pack<T, V>(x + v * V), rv, out;
+    unsigned mb = 0;
     if (res) rv = ld_pack<T, V>(res + v * V);
 #pragma unroll
     for (int k = 0; k < V; ++k) {
@@ -198,8 +207,10 @@ __global__ void __launch_bounds__(kBnThreads) bn_apply_fwd_kernel(
       if (res) z += (float)to_acc<T>(rv.v[k]);
       if (relu) z = fmaxf(z, 0.f);
       out.v[k] = from_acc<T>((typename AccOf<T>::type)z);
+      if ((float)to_acc<T>(out.v[k]) > 0.f) mb |= 1u << k;     // what `y > 0` would read back
     }
     st_pack<T, V>(y + v * V, out);
+    if (bits) bits[v] = (unsigned char)mb;
   }
 }
 
@@ -208,7 +219,7 @@ __global__ void __launch_bounds__(kBnThreads, 4) bn_apply_bwd_kernel(
     const T* __restrict__ x, const T* __restrict__ y, const T* __restrict__ dy, T* __restrict__ dx,
     T* __restrict__ dres, const float* __restrict__ gamma, const float* __restrict__ beta, const float* __restrict__ mean,
     const float* __restrict__ invstd, const float* __restrict__ dgamma, const float* __restrict__ dbeta,
-    size_t nvec, int C, int relu, float inv_m) {
+    const unsigned char* __restrict__ bits, size_t nvec, int C, int relu, float inv_m) {
   const int cvn = C / V;
   const size_t T0 = (size_t)blockIdx.x * kBnThreads + threadIdx.x;
   const size_t stride = (size_t)gridDim.x * kBnThreads;
@@ -226,13 +237,19 @@ __global__ void __launch_bounds__(kBnThreads, 4) bn_apply_bwd_kernel(
   }
   for (size_t v = T0; v < nvec; v += stride) {
     Pack<T, V> xv = ld_pack<T, V>(x + v * V), gv = ld_pack<T, V>(dy + v * V), yv, ox, orr;
-    if (relu && !mask_from_x) yv = ld_pack<T, V>(y + v * V);
+    unsigned mb = 0;
+    if (relu && !mask_from_x) {
+      if (bits) mb = bits[v];
+      else yv = ld_pack<T, V>(y + v * V);
+    }
 #pragma unroll
     for (int k = 0; k < V; ++k) {
       float g = (float)to_acc<T>(gv.v[k]);
       if (mask_from_x) {
         if (!((float)to_acc<T>(xv.v[k]) * k1[k] + sh[k] > 0.f)) g = 0.f;
-      } else if (relu && !((float)to_acc<T>(yv.v[k]) > 0.f)) g = 0.f;
+      } else if (relu) {
+        if (bits ? !((mb >> k) & 1u) : !((float)to_acc<T>(yv.v[k]) > 0.f)) g = 0.f;
+      }
       float xhat = ((float)to_acc<T>(xv.v[k]) - mu[k]) * is[k];
       ox.v[k] = from_acc<T>((typename AccOf<T>::type)(k1[k] * (g - k2[k] - xhat * k3[k])));
       orr.v[k] = from_acc<T>((typename AccOf<T>::type)g);
@@ -252,7 +269,7 @@ static int bn_check(int64_t rows, int C, int V) {
 template <typename T>
 static int bn_fwd_t(const void* x, const void* res, void* y, const float* gamma, const float* beta, float* rmean,
                     float* rvar, float* smean, float* sinv, int64_t rows, int C, float eps, float momentum, int relu,
-                    int training, void* scratch, cudaStream_t s) {
+                    int training, void* bits, void* scratch, cudaStream_t s) {
   constexpr int V = 16 / sizeof(T);
   int st = bn_check(rows, C, V);
   if (st) return st;
@@ -260,8 +277,8 @@ static int bn_fwd_t(const void* x, const void* res, void* y, const float* gamma,
   int grid = bn_grid(nvec);
   const int reverse = tunable("bn_reverse_stats") != 0;
   if (training) {
-    bn_reduce_kernel<T, V, false, false><<<grid, kBnThreads, 0, s>>>((const T*)x, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nvec, C, 0, reverse,
-                                                              (float*)scratch);
+    bn_reduce_kernel<T, V, false, false><<<grid, kBnThreads, 0, s>>>((const T*)x, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr,
+                                                                     nullptr, nvec, C, 0, reverse, (float*)scratch);
     float m = (float)rows;
     bn_finalize_fwd_kernel<<<(C + 31) / 32, dim3(32, 32), 0, s>>>((const float*)scratch, grid, C, 1.f / m,
                                                            rows > 1 ? m / (m - 1.f) : 1.f, eps, momentum, smean, sinv,
@@ -269,7 +286,8 @@ static int bn_fwd_t(const void* x, const void* res, void* y, const float* gamma,
   }
   // the apply pass keeps no partials and needs 32 registers: eight blocks per SM
   const int apply_grid = (int)std::max<size_t>(1, std::min<size_t>((nvec + kBnThreads - 1) / kBnThreads, 2 * kBnMaxGrid));
-  bn_apply_fwd_kernel<T, V><<<apply_grid, kBnThreads, 0, s>>>((const T*)x, (const T*)res, (T*)y, gamma, beta, smean, sinv, nvec, C, relu);
+  bn_apply_fwd_kernel<T, V><<<apply_grid, kBnThreads, 0, s>>>((const T*)x, (const T*)res, (T*)y, gamma, beta, smean, sinv,
+                                                              (unsigned char*)bits, nvec, C, relu);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? TMPI_OK : fail(TMPI_ERR_CUDA, "bn forward launch: %s", cudaGetErrorString(e));
 }
@@ -277,28 +295,30 @@ static int bn_fwd_t(const void* x, const void* res, void* y, const float* gamma,
 template <typename T>
 static int bn_bwd_t(const void* x, const void* y, const void* dy, void* dx, void* dres, const float* gamma,
                     const float* beta, const float* smean, const float* sinv, float* dgamma, float* dbeta, int64_t rows, int C, int relu,
-                    void* scratch, cudaStream_t s) {
+                    const void* bits, void* scratch, cudaStream_t s) {
   constexpr int V = 16 / sizeof(T);
   int st = bn_check(rows, C, V);
   if (st) return st;
-  if (relu && !y && (!beta || dres)) return fail(TMPI_ERR_INVALID, "bn backward: without y the layer needs beta and no residual");
+  if (relu && !y && !bits && (!beta || dres))
+    return fail(TMPI_ERR_INVALID, "bn backward: without y or mask bits the layer needs beta and no residual");
   size_t nvec = (size_t)rows * (C / V);
   int grid = bn_grid(nvec);
   const int reverse = tunable("bn_reverse_stats") != 0;
-  const bool maskx = relu && !y;
+  const bool maskx = relu && !y && !bits;
+  const unsigned char* mb = (const unsigned char*)bits;
   if (maskx)
-    bn_reduce_kernel<T, V, true, true><<<grid, kBnThreads, 0, s>>>((const T*)x, nullptr, (const T*)dy, smean, sinv, gamma, beta, nvec,
-                                                                   C, relu, reverse, (float*)scratch);
+    bn_reduce_kernel<T, V, true, true><<<grid, kBnThreads, 0, s>>>((const T*)x, nullptr, (const T*)dy, smean, sinv, gamma, beta, nullptr,
+                                                                   nvec, C, relu, reverse, (float*)scratch);
   else
-    bn_reduce_kernel<T, V, true, false><<<grid, kBnThreads, 0, s>>>((const T*)x, (const T*)y, (const T*)dy, smean, sinv, gamma, beta,
+    bn_reduce_kernel<T, V, true, false><<<grid, kBnThreads, 0, s>>>((const T*)x, (const T*)y, (const T*)dy, smean, sinv, gamma, beta, mb,
                                                                     nvec, C, relu, reverse, (float*)scratch);
   bn_finalize_bwd_kernel<<<(C + 31) / 32, dim3(32, 32), 0, s>>>((const float*)scratch, grid, C, dgamma, dbeta);
   if (maskx)
     bn_apply_bwd_kernel<T, V, true><<<grid, kBnThreads, 0, s>>>((const T*)x, nullptr, (const T*)dy, (T*)dx, (T*)dres, gamma, beta,
-                                                                smean, sinv, dgamma, dbeta, nvec, C, relu, 1.f / (float)rows);
+                                                                smean, sinv, dgamma, dbeta, nullptr, nvec, C, relu, 1.f / (float)rows);
   else
     bn_apply_bwd_kernel<T, V, false><<<grid, kBnThreads, 0, s>>>((const T*)x, (const T*)y, (const T*)dy, (T*)dx, (T*)dres, gamma, beta,
-                                                                 smean, sinv, dgamma, dbeta, nvec, C, relu, 1.f / (float)rows);
+                                                                 smean, sinv, dgamma, dbeta, mb, nvec, C, relu, 1.f / (float)rows);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? TMPI_OK : fail(TMPI_ERR_CUDA, "bn backward launch: %s", cudaGetErrorString(e));
 }
@@ -551,7 +571,7 @@ static int bn_pool_fwd_t(const void* x, void* y, void* idx, const float* gamma, 
     size_t nvec = (size_t)rows * (C / V);
     int grid = bn_grid(nvec);
     bn_reduce_kernel<T, V, false, false><<<grid, kBnThreads, 0, s>>>((const T*)x, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr,
-                                                                     nvec, C, 0, tunable("bn_reverse_stats") != 0, (float*)scratch);
+                                                                     nullptr, nvec, C, 0, tunable("bn_reverse_stats") != 0, (float*)scratch);
     float m = (float)rows;
     bn_finalize_fwd_kernel<<<(C + 31) / 32, dim3(32, 32), 0, s>>>((const float*)scratch, grid, C, 1.f / m,
                                                            rows > 1 ? m / (m - 1.f) : 1.f, eps, momentum, smean, sinv, rmean, rvar);
@@ -603,34 +623,37 @@ size_t tmpi_bn_scratch_bytes(int channels) { return (size_t)kBnMaxGrid * 2 * cha
 
 // training != 0: batch statistics are computed, saved in save_mean / save_invstd and folded into the
 // running statistics.  training == 0: save_mean / save_invstd are inputs (mean and 1/std to apply).
+// mask_bits (nullable): one byte per 16-byte vector of y, bit k set where element k is positive; the
+// backward of a ReLU layer reads it in place of y.
 int tmpi_bn_relu_fwd(const void* x, const void* residual, void* y, const float* gamma, const float* beta,
                      float* running_mean, float* running_var, float* save_mean, float* save_invstd, int64_t rows,
-                     int channels, float eps, float momentum, int relu, int training, int dtype, void* scratch,
-                     void* stream) {
+                     int channels, float eps, float momentum, int relu, int training, int dtype, void* mask_bits,
+                     void* scratch, void* stream) {
   cudaStream_t s = (cudaStream_t)stream;
   switch (dtype) {
     case TMPI_BF16: return bn_fwd_t<__nv_bfloat16>(x, residual, y, gamma, beta, running_mean, running_var, save_mean,
-                                                   save_invstd, rows, channels, eps, momentum, relu, training, scratch, s);
+                                                   save_invstd, rows, channels, eps, momentum, relu, training, mask_bits, scratch, s);
     case TMPI_F16: return bn_fwd_t<__half>(x, residual, y, gamma, beta, running_mean, running_var, save_mean, save_invstd,
-                                           rows, channels, eps, momentum, relu, training, scratch, s);
+                                           rows, channels, eps, momentum, relu, training, mask_bits, scratch, s);
     case TMPI_F32: return bn_fwd_t<float>(x, residual, y, gamma, beta, running_mean, running_var, save_mean, save_invstd,
-                                          rows, channels, eps, momentum, relu, training, scratch, s);
+                                          rows, channels, eps, momentum, relu, training, mask_bits, scratch, s);
   }
   return fail(TMPI_ERR_UNSUPPORTED, "bn: dtype %d", dtype);
 }
 
-// y == nullptr (ReLU layers without a residual only): the ReLU mask is recomputed from x, gamma and beta.
+// The ReLU mask comes from mask_bits when given (see tmpi_bn_relu_fwd), else from y, else - ReLU layers
+// without a residual only - it is recomputed from x, gamma and beta.
 int tmpi_bn_relu_bwd(const void* x, const void* y, const void* dy, void* dx, void* dresidual, const float* gamma,
                      const float* beta, const float* save_mean, const float* save_invstd, float* dgamma, float* dbeta, int64_t rows,
-                     int channels, int relu, int dtype, void* scratch, void* stream) {
+                     int channels, int relu, int dtype, const void* mask_bits, void* scratch, void* stream) {
   cudaStream_t s = (cudaStream_t)stream;
   switch (dtype) {
     case TMPI_BF16: return bn_bwd_t<__nv_bfloat16>(x, y, dy, dx, dresidual, gamma, beta, save_mean, save_invstd, dgamma, dbeta,
-                                                   rows, channels, relu, scratch, s);
+                                                   rows, channels, relu, mask_bits, scratch, s);
     case TMPI_F16: return bn_bwd_t<__half>(x, y, dy, dx, dresidual, gamma, beta, save_mean, save_invstd, dgamma, dbeta, rows,
-                                           channels, relu, scratch, s);
+                                           channels, relu, mask_bits, scratch, s);
     case TMPI_F32: return bn_bwd_t<float>(x, y, dy, dx, dresidual, gamma, beta, save_mean, save_invstd, dgamma, dbeta, rows,
-                                          channels, relu, scratch, s);
+                                          channels, relu, mask_bits, scratch, s);
   }
   return fail(TMPI_ERR_UNSUPPORTED, "bn: dtype %d", dtype);
 }

@@ -56,24 +56,30 @@ class _BnReluFn(torch.autograd.Function):
         else:
             mean = running_mean.float()
             invstd = torch.rsqrt(running_var.float() + eps)
+        # a ReLU layer with a residual keeps one mask bit per element for its backward (a sixteenth of y)
+        bits = None
+        if relu and residual is not None and any(ctx.needs_input_grad):
+            bits = torch.empty(rows * C // (16 // x.element_size()), dtype=torch.uint8, device=x.device)
         check(lib.tmpi_bn_relu_fwd(
             x.data_ptr(), residual.data_ptr() if residual is not None else None, y.data_ptr(),
             gamma.data_ptr(), beta.data_ptr(),
             running_mean.data_ptr() if (training and running_mean is not None) else None,
             running_var.data_ptr() if (training and running_var is not None) else None,
             mean.data_ptr(), invstd.data_ptr(), rows, C, eps, momentum, int(relu), int(training),
-            dtype_code(x.dtype), _scratch_for(x.device, C).data_ptr(), stream_ptr()))
+            dtype_code(x.dtype), bits.data_ptr() if bits is not None else None,
+            _scratch_for(x.device, C).data_ptr(), stream_ptr()))
         launch_count += 3 if training else 1
-        # a ReLU layer without a residual rebuilds its mask from x in backward and does not keep y
+        # a ReLU layer without a residual rebuilds its mask from x in backward; neither kind reads y again
         ctx.mask_from_x = relu and residual is None
-        ctx.save_for_backward(x, None if ctx.mask_from_x else y, gamma, beta, mean, invstd)
+        keep_y = relu and not ctx.mask_from_x and bits is None
+        ctx.save_for_backward(x, y if keep_y else None, gamma, beta, mean, invstd, bits)
         ctx.relu, ctx.has_res = relu, residual is not None
         return y
 
     @staticmethod
     def backward(ctx, dy):
         global launch_count
-        x, y, gamma, beta, mean, invstd = ctx.saved_tensors
+        x, y, gamma, beta, mean, invstd, bits = ctx.saved_tensors
         dy = dy.contiguous(memory_format=torch.channels_last)
         N, C, H, W = x.shape
         dx = torch.empty_like(x, memory_format=torch.channels_last)
@@ -83,7 +89,8 @@ class _BnReluFn(torch.autograd.Function):
         check(lib.tmpi_bn_relu_bwd(
             x.data_ptr(), y.data_ptr() if y is not None else None, dy.data_ptr(), dx.data_ptr(),
             dres.data_ptr() if dres is not None else None, gamma.data_ptr(), beta.data_ptr(), mean.data_ptr(), invstd.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(),
-            N * H * W, C, int(ctx.relu), dtype_code(x.dtype), _scratch_for(x.device, C).data_ptr(), stream_ptr()))
+            N * H * W, C, int(ctx.relu), dtype_code(x.dtype), bits.data_ptr() if bits is not None else None,
+            _scratch_for(x.device, C).data_ptr(), stream_ptr()))
         launch_count += 3
         return dx, dres, dgamma, dbeta, None, None, None, None, None, None
 
@@ -141,7 +148,7 @@ class _BnReluPoolFn(torch.autograd.Function):
             check(lib.tmpi_bn_relu_bwd(
                 x.data_ptr(), None, da.data_ptr(), dx.data_ptr(), None, gamma.data_ptr(), beta.data_ptr(),
                 mean.data_ptr(), invstd.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(), N * H * W, C, 1,
-                dtype_code(x.dtype), _scratch_for(x.device, C).data_ptr(), stream_ptr()))
+                dtype_code(x.dtype), None, _scratch_for(x.device, C).data_ptr(), stream_ptr()))
             launch_count += 4
         return dx, dgamma, dbeta, None, None, None, None, None
 
