@@ -181,7 +181,9 @@ __global__ void __launch_bounds__(1024) bn_finalize_bwd_kernel(const float* __re
   dgamma[c] = s2;
 }
 
-template <typename T, int V>
+// BITS: also write the ReLU mask byte of every vector (residual layers only; a template parameter so
+// that the other layers keep 32 registers and eight resident blocks)
+template <typename T, int V, bool BITS>
 __global__ void __launch_bounds__(kBnThreads) bn_apply_fwd_kernel(
     const T* __restrict__ x, const T* __restrict__ res, T* __restrict__ y, const float* __restrict__ gamma,
     const float* __restrict__ beta, const float* __restrict__ mean, const float* __restrict__ invstd,
@@ -207,10 +209,10 @@ __global__ void __launch_bounds__(kBnThreads) bn_apply_fwd_kernel(
       if (res) z += (float)to_acc<T>(rv.v[k]);
       if (relu) z = fmaxf(z, 0.f);
       out.v[k] = from_acc<T>((typename AccOf<T>::type)z);
-      if ((float)to_acc<T>(out.v[k]) > 0.f) mb |= 1u << k;     // what `y > 0` would read back
+      if (BITS && (float)to_acc<T>(out.v[k]) > 0.f) mb |= 1u << k;     // what `y > 0` would read back
     }
     st_pack<T, V>(y + v * V, out);
-    if (bits) bits[v] = (unsigned char)mb;
+    if (BITS) bits[v] = (unsigned char)mb;
   }
 }
 
@@ -286,8 +288,12 @@ static int bn_fwd_t(const void* x, const void* res, void* y, const float* gamma,
   }
   // the apply pass keeps no partials and needs 32 registers: eight blocks per SM
   const int apply_grid = (int)std::max<size_t>(1, std::min<size_t>((nvec + kBnThreads - 1) / kBnThreads, 2 * kBnMaxGrid));
-  bn_apply_fwd_kernel<T, V><<<apply_grid, kBnThreads, 0, s>>>((const T*)x, (const T*)res, (T*)y, gamma, beta, smean, sinv,
-                                                              (unsigned char*)bits, nvec, C, relu);
+  if (bits)
+    bn_apply_fwd_kernel<T, V, true><<<apply_grid, kBnThreads, 0, s>>>((const T*)x, (const T*)res, (T*)y, gamma, beta, smean, sinv,
+                                                                      (unsigned char*)bits, nvec, C, relu);
+  else
+    bn_apply_fwd_kernel<T, V, false><<<apply_grid, kBnThreads, 0, s>>>((const T*)x, (const T*)res, (T*)y, gamma, beta, smean, sinv,
+                                                                       nullptr, nvec, C, relu);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? TMPI_OK : fail(TMPI_ERR_CUDA, "bn forward launch: %s", cudaGetErrorString(e));
 }
