@@ -76,7 +76,10 @@ def run(args) -> list:
     from torchmpi_b200 import config
     use_gpu = args.processor == "gpu"
     if use_gpu:
-        config.set("heap_bytes", max(config.get("heap_bytes"), 4 * args.max_bytes + (256 << 20)))
+        # the largest symmetric tensor is the reduce-scatter input: world x max_bytes
+        import os
+        nranks = int(os.environ.get("WORLD_SIZE", "1")) if "reduce_scatter" in args.ops else 1
+        config.set("heap_bytes", max(config.get("heap_bytes"), (nranks + 3) * args.max_bytes + (256 << 20)))
         config.set("staging_bytes", max(config.get("staging_bytes"), min(args.max_bytes, 1 << 30)))
         if args.ctas:
             config.set("comm_max_ctas", args.ctas)
