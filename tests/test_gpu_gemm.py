@@ -163,3 +163,28 @@ def test_fused_gemms_single_rank():
         tp.check()
     finally:
         mpi.stop()
+
+
+def test_wide_head_and_pitched_cross_entropy():
+    """LM head with a vocabulary that is not a multiple of 8: logits live in a pitched buffer, the loss kernel
+    takes the pitch, and forward / dX / dW all run on the CTA-pair kernel.  Against fp32 PyTorch."""
+    from torchmpi_b200.ops import gemm, xent
+    torch.manual_seed(11)
+    for T, d, V in ((256, 256, 50257), (512, 384, 1003)):
+        x = (torch.randn(T, d, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_(True)
+        w = (torch.randn(V, d, device="cuda") * 0.05).to(torch.bfloat16).requires_grad_(True)
+        y = torch.randint(0, V, (T,), device="cuda")
+        logits = gemm.wide_head(x, w)
+        assert logits.shape == (T, V) and logits.stride(0) % 8 == 0
+        loss = xent.cross_entropy(logits, y)
+        loss.backward()
+        xr, wr = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+        lr = torch.nn.functional.linear(xr, wr)
+        ref = torch.nn.functional.cross_entropy(lr, y)
+        ref.backward()
+        assert torch.allclose(logits.float(), lr, rtol=2e-2, atol=2e-2), (T, d, V)
+        assert abs(loss.item() - ref.item()) < 2e-2 * max(1.0, abs(ref.item())), (loss.item(), ref.item())
+        for g, gr in ((x.grad, xr.grad), (w.grad, wr.grad)):
+            rel = (g.float() - gr).norm() / gr.norm()
+            assert rel < 3e-2, (T, d, V, rel.item())
+        gemm.check_status()

@@ -166,6 +166,7 @@ _CUDA_PROTOS = {
     "tmpi_cuda_ps_pull": (_i, [_sz, _vp, _sz, _i, _gp, _vp]),
     "tmpi_sgd_momentum": (_i, [_vp, _i, _vp, _i, _vp, _vp, _sz, _f, _f, _f, _f, _f, _i, _i, _i, _vp]),
     "tmpi_xent_fwd_bwd": (_i, [_vp, _i, _vp, _i, _i, _vp, _vp, _f, _vp, _vp]),
+    "tmpi_xent_fwd_bwd_ld": (_i, [_vp, _i, _vp, _i, _i, _i, _vp, _vp, _f, _vp, _vp]),
     "tmpi_xent_scratch_bytes": (_sz, [_i]),
     "tmpi_cuda_ps_push_async": (_u64, [_sz, _vp, _sz, _i, _i, _gp, _vp]),
     "tmpi_cuda_ps_pull_async": (_u64, [_sz, _vp, _sz, _i, _gp, _vp]),
@@ -184,6 +185,7 @@ _CUDA_PROTOS = {
     "tmpi_maxpool_fwd": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "tmpi_maxpool_bwd": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "tmpi_gemm_bf16": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "tmpi_gemm_bf16_ex": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, _i, _vp]),
     "tmpi_gemm_status": (_i, []),
 }
 

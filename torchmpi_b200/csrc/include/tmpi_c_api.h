@@ -221,6 +221,9 @@ int tmpi_sgd_momentum(void* weight, int weight_dtype, const void* grad, int grad
 size_t tmpi_xent_scratch_bytes(int rows);
 int tmpi_xent_fwd_bwd(const void* logits, int dtype, const int64_t* labels, int rows, int cols,
                       float* loss_sum, void* dlogits, float grad_scale, void* scratch, void* stream);
+// the same with a row pitch `ld` (elements) for logits and dlogits; dlogits columns cols..ld-1 are zeroed
+int tmpi_xent_fwd_bwd_ld(const void* logits, int dtype, const int64_t* labels, int rows, int cols, int ld,
+                      float* loss_sum, void* dlogits, float grad_scale, void* scratch, void* stream);
 int tmpi_absmean_var(const void* x, int dtype, size_t n, double* out2, void* scratch, void* stream);
 size_t tmpi_absmean_var_scratch_bytes(void);
 int tmpi_easgd_elastic(void* local, const void* center, void* delta, size_t n, int dtype,
@@ -263,6 +266,9 @@ int tmpi_stem_patch_width(void);
 // C[M,N] = act(A[M,K] * B[N,K]^T (+ bias)), bf16 in, fp32 accumulate in TMEM.
 int tmpi_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
                    int epilogue, void* stream);
+// explicit row pitches (elements, multiples of 8) of A, B, C as stored; M, N >= 256
+int tmpi_gemm_bf16_ex(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
+                      int64_t lda, int64_t ldb, int64_t ldc, int epilogue, void* stream);
 
 // ---------------------------------------------------------------- tracing
 // ring buffer of (op, algo, bytes, microseconds) records per process

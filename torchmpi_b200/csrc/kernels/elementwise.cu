@@ -31,14 +31,14 @@ static int sm_count() {
 // The last block to finish adds the row losses in row order (deterministic) into loss_out[0].
 template <typename T>
 __global__ void __launch_bounds__(256) xent_kernel(const T* __restrict__ logits, const long long* __restrict__ labels,
-                                                   int rows, int cols, float* __restrict__ loss_out,
+                                                   int rows, int cols, int ld, float* __restrict__ loss_out,
                                                    T* __restrict__ dlogits, float gscale,
                                                    float* __restrict__ row_loss, unsigned* __restrict__ counter) {
   __shared__ float s_red[32];
   __shared__ float s_bcast;
   __shared__ bool s_last;
   const int r = blockIdx.x;
-  const T* x = logits + (size_t)r * cols;
+  const T* x = logits + (size_t)r * ld;               // ld: row pitch in elements (>= cols)
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
 
   float m = -INFINITY;
@@ -69,11 +69,12 @@ __global__ void __launch_bounds__(256) xent_kernel(const T* __restrict__ logits,
   const float inv = 1.f / sum;
   const int label = (int)labels[r];
   if (dlogits) {
-    T* d = dlogits + (size_t)r * cols;
+    T* d = dlogits + (size_t)r * ld;
     for (int c = threadIdx.x; c < cols; c += blockDim.x) {
       float p = __expf((float)to_acc<T>(x[c]) - m) * inv;
       d[c] = from_acc<T>((typename AccOf<T>::type)((p - (c == label ? 1.f : 0.f)) * gscale));
     }
+    for (int c = cols + threadIdx.x; c < ld; c += blockDim.x) d[c] = from_acc<T>((typename AccOf<T>::type)0.f);
   }
   if (threadIdx.x == 0) {
     float xl = (label >= 0 && label < cols) ? (float)to_acc<T>(x[label]) : m;
@@ -104,7 +105,7 @@ __global__ void __launch_bounds__(256) xent_kernel(const T* __restrict__ logits,
 // 2-byte boundaries only, so a few head and tail elements move as scalars.
 template <typename T, int THREADS>
 __global__ void __launch_bounds__(THREADS) xent_row_smem_kernel(
-    const T* __restrict__ logits, const long long* __restrict__ labels, int rows, int cols,
+    const T* __restrict__ logits, const long long* __restrict__ labels, int rows, int cols, int ld,
     float* __restrict__ loss_out, T* __restrict__ dlogits, float gscale, float* __restrict__ row_loss,
     unsigned* __restrict__ counter) {
   extern __shared__ __align__(16) unsigned char s_row_raw[];
@@ -114,7 +115,7 @@ __global__ void __launch_bounds__(THREADS) xent_row_smem_kernel(
   constexpr int V = 16 / sizeof(T);
   const int r = blockIdx.x, tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5, nwarp = THREADS >> 5;
-  const T* x = logits + (size_t)r * cols;
+  const T* x = logits + (size_t)r * ld;               // ld: row pitch in elements (>= cols)
   const unsigned mis = (unsigned)((uintptr_t)x & 15);
   T* srow = reinterpret_cast<T*>(s_row_raw + mis);
   int head = mis ? (int)((16 - mis) / sizeof(T)) : 0;
@@ -187,7 +188,8 @@ __global__ void __launch_bounds__(THREADS) xent_row_smem_kernel(
 
   // pass 3: gradient, written once
   if (dlogits) {
-    T* d = dlogits + (size_t)r * cols;
+    T* d = dlogits + (size_t)r * ld;
+    for (int c = cols + tid; c < ld; c += THREADS) d[c] = from_acc<T>((typename AccOf<T>::type)0.f);   // pitch padding
     auto grad = [&](T v, int c) {
       float p = __expf((float)to_acc<T>(v) - m) * inv;
       return from_acc<T>((typename AccOf<T>::type)((p - (c == label ? 1.f : 0.f)) * gscale));
@@ -339,7 +341,7 @@ using namespace tmpi;
   }
 
 template <typename T>
-static cudaError_t launch_xent(const void* logits, const int64_t* labels, int rows, int cols, float* loss_sum, void* dlogits,
+static cudaError_t launch_xent(const void* logits, const int64_t* labels, int rows, int cols, int ld, float* loss_sum, void* dlogits,
                                float gscale, float* row_loss, unsigned* counter, cudaStream_t s) {
   constexpr int kThreads = 512;
   constexpr size_t kMaxRowBytes = 112 * 1024;          // two such blocks per SM
@@ -350,10 +352,10 @@ static cudaError_t launch_xent(const void* logits, const int64_t* labels, int ro
       cudaFuncSetAttribute(xent_row_smem_kernel<T, kThreads>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxRowBytes);
       attr_set = true;
     }
-    xent_row_smem_kernel<T, kThreads><<<rows, kThreads, row_bytes, s>>>((const T*)logits, (const long long*)labels, rows, cols,
+    xent_row_smem_kernel<T, kThreads><<<rows, kThreads, row_bytes, s>>>((const T*)logits, (const long long*)labels, rows, cols, ld,
                                                                         loss_sum, (T*)dlogits, gscale, row_loss, counter);
   } else {
-    xent_kernel<T><<<rows, 256, 0, s>>>((const T*)logits, (const long long*)labels, rows, cols, loss_sum, (T*)dlogits, gscale,
+    xent_kernel<T><<<rows, 256, 0, s>>>((const T*)logits, (const long long*)labels, rows, cols, ld, loss_sum, (T*)dlogits, gscale,
                                         row_loss, counter);
   }
   return cudaGetLastError();
@@ -383,18 +385,30 @@ int tmpi_sgd_momentum(void* weight, int wdt, const void* grad, int gdt, void* ma
 
 size_t tmpi_xent_scratch_bytes(int rows) { return (size_t)rows * sizeof(float) + 256; }
 
+// ld: row pitch of logits and dlogits in elements (0 or cols: dense rows).  The columns between cols and
+// ld are not read; in dlogits they are set to zero.
+int tmpi_xent_fwd_bwd_ld(const void* logits, int dtype, const int64_t* labels, int rows, int cols, int ld, float* loss_sum,
+                         void* dlogits, float gscale, void* scratch, void* stream);
+
 int tmpi_xent_fwd_bwd(const void* logits, int dtype, const int64_t* labels, int rows, int cols, float* loss_sum,
                       void* dlogits, float gscale, void* scratch, void* stream) {
+  return tmpi_xent_fwd_bwd_ld(logits, dtype, labels, rows, cols, cols, loss_sum, dlogits, gscale, scratch, stream);
+}
+
+int tmpi_xent_fwd_bwd_ld(const void* logits, int dtype, const int64_t* labels, int rows, int cols, int ld, float* loss_sum,
+                         void* dlogits, float gscale, void* scratch, void* stream) {
   if (rows < 1 || cols < 1) return fail(TMPI_ERR_INVALID, "xent: empty input");
+  if (ld == 0) ld = cols;
+  if (ld < cols) return fail(TMPI_ERR_INVALID, "xent: row pitch %d below the row length %d", ld, cols);
   // scratch layout: [counter (256 B, zero before first use)] [row losses]
   unsigned* counter = (unsigned*)scratch;
   float* row_loss = (float*)((char*)scratch + 256);
   cudaStream_t s = (cudaStream_t)stream;
   cudaError_t e;
   switch (dtype) {
-    case TMPI_F32: e = launch_xent<float>(logits, labels, rows, cols, loss_sum, dlogits, gscale, row_loss, counter, s); break;
-    case TMPI_BF16: e = launch_xent<__nv_bfloat16>(logits, labels, rows, cols, loss_sum, dlogits, gscale, row_loss, counter, s); break;
-    case TMPI_F16: e = launch_xent<__half>(logits, labels, rows, cols, loss_sum, dlogits, gscale, row_loss, counter, s); break;
+    case TMPI_F32: e = launch_xent<float>(logits, labels, rows, cols, ld, loss_sum, dlogits, gscale, row_loss, counter, s); break;
+    case TMPI_BF16: e = launch_xent<__nv_bfloat16>(logits, labels, rows, cols, ld, loss_sum, dlogits, gscale, row_loss, counter, s); break;
+    case TMPI_F16: e = launch_xent<__half>(logits, labels, rows, cols, ld, loss_sum, dlogits, gscale, row_loss, counter, s); break;
     default: return fail(TMPI_ERR_UNSUPPORTED, "xent: dtype %d", dtype);
   }
   return e == cudaSuccess ? TMPI_OK : cuda_fail(e, "xent launch");

@@ -92,19 +92,24 @@ bool gemm_pair_applicable(const void* C, int M, int N, int K, int flags) {
   return true;
 }
 
+// lda / ldb / ldc: row pitch of A, B, C as stored, in elements (0: dense).  With explicit pitches the
+// extents themselves need not be multiples of 8 (a [T, 50257] matrix held in rows of 50264).
 int launch_gemm_pair(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int epilogue,
-                     int* status_word, cudaStream_t stream) {
+                     int* status_word, cudaStream_t stream, int64_t lda, int64_t ldb, int64_t ldc) {
   CUtensorMap ma, mb, mc;
   int st;
   const bool a_km = (epilogue & gemm::A_IS_KM) != 0;       // A given as [K, M], M contiguous
-  if (a_km) st = make_tmap_bf16(&ma, A, (uint64_t)K, (uint64_t)M, (uint64_t)M, gemm2::BK);
-  else st = make_tmap_bf16(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)K, gemm2::BM);
+  if (!lda) lda = a_km ? M : K;
+  if (a_km) st = make_tmap_bf16(&ma, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, gemm2::BK);
+  else st = make_tmap_bf16(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, gemm2::BM);
   if (st) return st;
   const bool b_kn = (epilogue & gemm::B_IS_KN) != 0;       // B given as [K, N], N contiguous
-  if (b_kn) st = make_tmap_bf16(&mb, B, (uint64_t)K, (uint64_t)N, (uint64_t)N, gemm2::BK);
-  else st = make_tmap_bf16(&mb, B, (uint64_t)N, (uint64_t)K, (uint64_t)K, gemm2::BN / 2);
+  if (!ldb) ldb = b_kn ? N : K;
+  if (b_kn) st = make_tmap_bf16(&mb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, gemm2::BK);
+  else st = make_tmap_bf16(&mb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, gemm2::BN / 2);
   if (st) return st;
-  if ((st = make_tmap_bf16(&mc, C, (uint64_t)M, (uint64_t)N, (uint64_t)N, gemm2::BM))) return st;
+  if (!ldc) ldc = N;
+  if ((st = make_tmap_bf16(&mc, C, (uint64_t)M, (uint64_t)N, (uint64_t)ldc, gemm2::BM))) return st;
   gemm::Problem p{};
   p.M = M; p.N = N; p.K = K;
   p.tiles_m = (M + 2 * gemm2::BM - 1) / (2 * gemm2::BM);

@@ -109,7 +109,7 @@ int gemm_sm_count() {
 
 bool gemm_pair_applicable(const void* C, int M, int N, int K, int flags);
 int launch_gemm_pair(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int epilogue,
-                     int* status_word, cudaStream_t stream);
+                     int* status_word, cudaStream_t stream, int64_t lda, int64_t ldb, int64_t ldc);
 
 static int* gemm_status_word() {
   static int* dev_ptr = nullptr;
@@ -137,7 +137,7 @@ int tmpi_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int 
   if (k_rows && K % 8) return fail(TMPI_ERR_INVALID, "gemm: K must be a multiple of 8 (16-byte rows for TMA)");
   if ((epilogue & gemm::EPI_BIAS) && !bias) return fail(TMPI_ERR_INVALID, "gemm: bias epilogue without bias");
   if (tunable("gemm_pair") && gemm_pair_applicable(C, M, N, K, epilogue))
-    return launch_gemm_pair(A, B, C, bias, M, N, K, epilogue, gemm_status_word(), (cudaStream_t)stream);
+    return launch_gemm_pair(A, B, C, bias, M, N, K, epilogue, gemm_status_word(), (cudaStream_t)stream, 0, 0, 0);
   if (epilogue & (gemm::B_IS_KN | gemm::A_IS_KM))
     return fail(TMPI_ERR_UNSUPPORTED, "gemm: operands given as [K, M] / [K, N] need the CTA-pair kernel (M, N >= 256, M, N %% 8 == 0)");
   CUtensorMap ma, mb;
@@ -168,6 +168,19 @@ int tmpi_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int 
   gemm::gemm_bf16_kernel<<<grid, gemm::THREADS, gemm::SMEM_BYTES, (cudaStream_t)stream>>>(ma, mb, mc, (__nv_bfloat16*)C, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? TMPI_OK : fail(TMPI_ERR_CUDA, "gemm launch: %s", cudaGetErrorString(e));
+}
+
+// The same product with explicit row pitches (elements) of A, B and C as stored: the extents need not
+// be multiples of 8 as long as the pitches are (a [T, 50257] logit matrix kept in rows of 50264
+// elements).  CTA-pair kernel only: M, N >= 256.
+int tmpi_gemm_bf16_ex(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int64_t lda,
+                      int64_t ldb, int64_t ldc, int epilogue, void* stream) {
+  if (M < 256 || N < 256 || K < 1) return fail(TMPI_ERR_UNSUPPORTED, "gemm_ex: needs M, N >= 256 (got %d x %d x %d)", M, N, K);
+  if ((epilogue & gemm::EPI_BIAS) && !bias) return fail(TMPI_ERR_INVALID, "gemm: bias epilogue without bias");
+  if ((lda | ldb | ldc) % 8 || lda <= 0 || ldb <= 0 || ldc <= 0)
+    return fail(TMPI_ERR_INVALID, "gemm_ex: row pitches must be positive multiples of 8 elements");
+  if (((uintptr_t)A | (uintptr_t)B | (uintptr_t)C) & 15) return fail(TMPI_ERR_INVALID, "gemm_ex: operands must be 16-byte aligned");
+  return launch_gemm_pair(A, B, C, bias, M, N, K, epilogue, gemm_status_word(), (cudaStream_t)stream, lda, ldb, ldc);
 }
 
 // Non-zero after a GEMM CTA gave up on a bounded wait (1000 + the point where it happened); clears it.

@@ -97,6 +97,9 @@ class GPT2(nn.Module):
         for b in self.blocks:
             x = b(x)
         x = self.ln_f(x).to(self.wte.weight.dtype)
+        if self.config.tc_linear:
+            from ..ops import gemm
+            return gemm.wide_head(x.reshape(B * T, -1), self.wte.weight)      # [B*T, vocab] view of a pitched buffer
         return F.linear(x.view(B * T, -1), self.wte.weight)
 
 

@@ -99,6 +99,60 @@ def check_status() -> None:
         raise TorchMPIError(3, f"tcgen05 GEMM: a bounded wait ran out (code {st})")
 
 
+def _gemm_ex(a, b, c, M, N, K, lda, ldb, ldc, flags):
+    global launch_count
+    check(lib.tmpi_gemm_bf16_ex(a.data_ptr(), b.data_ptr(), c.data_ptr(), None, M, N, K, lda, ldb, ldc, flags, stream_ptr()))
+    launch_count += 1
+
+
+class _WideHeadFn(torch.autograd.Function):
+    """``x @ w.T`` for an output width that is not a multiple of 8 (a vocabulary of 50257).  A library GEMM
+    falls back to unvectorised kernels for such a matrix; here the result lives in a buffer whose row pitch
+    is rounded up to 8 elements and a view of its first ``V`` columns is returned, so that all three GEMMs
+    (forward, dX, dW) run on the CTA-pair kernel with explicit pitches and no padding copies."""
+
+    @staticmethod
+    def forward(ctx, x2, w):
+        T, d = x2.shape
+        V = w.shape[0]
+        Vp = (V + 7) // 8 * 8
+        buf = torch.empty((T, Vp), dtype=x2.dtype, device=x2.device)
+        _gemm_ex(x2, w, buf, T, V, d, d, d, Vp, 0)
+        ctx.save_for_backward(x2, w)
+        return buf[:, :V]
+
+    @staticmethod
+    def backward(ctx, dl):
+        x2, w = ctx.saved_tensors
+        T, d = x2.shape
+        V = w.shape[0]
+        if not (dl.stride(1) == 1 and dl.stride(0) % 8 == 0 and dl.data_ptr() % 16 == 0):
+            pad = torch.zeros((T, (V + 7) // 8 * 8), dtype=dl.dtype, device=dl.device)
+            pad[:, :V] = dl
+            dl = pad[:, :V]
+        ld = dl.stride(0)
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = torch.empty((T, d), dtype=x2.dtype, device=x2.device)
+            _gemm_ex(dl, w, dx, T, d, V, ld, d, d, B_IS_KN)                  # dX = dL @ W, W read as [K = V, N = d]
+        if ctx.needs_input_grad[1]:
+            dw = torch.empty((V, d), dtype=w.dtype, device=w.device)
+            _gemm_ex(dl, x2, dw, V, d, T, ld, d, d, A_IS_KM | B_IS_KN)       # dW = dL.T @ X, both as stored
+        return dx, dw
+
+
+def wide_head(x2: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``x2 @ w.T`` (``x2 [T, d]``, ``w [V, d]``) for any ``V``; see ``_WideHeadFn``.  Falls back to
+    ``F.linear`` when the CTA-pair kernel does not apply."""
+    T, d = x2.shape
+    V = w.shape[0]
+    if (x2.is_cuda and x2.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and T >= 256 and V >= 256 and d >= 256
+            and d % 8 == 0 and T % 8 == 0 and bool(config_get("gemm_pair")) and has_symbol("tmpi_gemm_bf16_ex")
+            and x2.is_contiguous() and w.is_contiguous()):
+        return _WideHeadFn.apply(x2, w)
+    return torch.nn.functional.linear(x2, w)
+
+
 class _LinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, bias, gelu):

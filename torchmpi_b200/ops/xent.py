@@ -27,19 +27,25 @@ class _XentFn(torch.autograd.Function):
         global launch_count
         launch_count += 1
         rows, cols = logits.shape
-        x = logits.contiguous()
-        dlogits = torch.empty_like(x)
+        # rows may sit in a wider buffer (a [T, 50257] logit matrix kept with a pitch of 50264 so that the
+        # GEMMs around it can use 16-byte rows): the kernel takes the pitch, and the gradient keeps it
+        if logits.stride(1) == 1 and logits.stride(0) >= cols and rows > 1:
+            x, ld = logits, logits.stride(0)
+        else:
+            x, ld = logits.contiguous(), cols
+        buf = torch.empty((rows, ld), dtype=x.dtype, device=x.device)
         loss = torch.empty(1, dtype=torch.float32, device=x.device)
-        check(lib.tmpi_xent_fwd_bwd(x.data_ptr(), dtype_code(x.dtype), labels.data_ptr(), rows, cols,
-                                    loss.data_ptr(), dlogits.data_ptr(), 1.0 / rows,
-                                    _scratch_for(x.device, rows).data_ptr(), stream_ptr()))
-        ctx.save_for_backward(dlogits)
+        check(lib.tmpi_xent_fwd_bwd_ld(x.data_ptr(), dtype_code(x.dtype), labels.data_ptr(), rows, cols, ld,
+                                       loss.data_ptr(), buf.data_ptr(), 1.0 / rows,
+                                       _scratch_for(x.device, rows).data_ptr(), stream_ptr()))
+        ctx.grad_buf, ctx.cols = buf, cols
         return loss[0] / rows
 
     @staticmethod
     def backward(ctx, grad_out):
-        (dlogits,) = ctx.saved_tensors
-        return dlogits * grad_out.to(dlogits.dtype), None
+        buf, ctx.grad_buf = ctx.grad_buf, None          # scaled in place: backward runs once
+        buf.mul_(grad_out.to(buf.dtype))
+        return buf[:, :ctx.cols], None
 
 
 def cross_entropy(logits: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
