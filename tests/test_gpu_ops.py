@@ -215,3 +215,29 @@ def test_bn_relu_maxpool_stage_matches_separate_ops(dtype, fused_bwd):
         assert rel < (2e-2 if dtype == torch.bfloat16 else 1e-4), (N, C, H, W, rel.item())
         assert torch.allclose(m.weight.grad, ref_bn.weight.grad, rtol=2e-2, atol=2e-2 * ref_bn.weight.grad.abs().max().item())
         assert torch.allclose(m.bias.grad, ref_bn.bias.grad, rtol=2e-2, atol=2e-2 * ref_bn.bias.grad.abs().max().item())
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_layernorm_matches_torch(dtype):
+    """One-pass layer norm (forward, dx, dgamma, dbeta) against fp32 PyTorch on the same operands."""
+    from torchmpi_b200.ops.layernorm import LayerNorm, supported
+    torch.manual_seed(9)
+    for rows, C in ((8192, 1024), (777, 256), (33, 2048 if dtype == torch.bfloat16 else 1024), (4096, 768)):
+        ln = LayerNorm(C).cuda().to(dtype)
+        with torch.no_grad():
+            ln.weight.copy_(torch.randn(C) * 0.5 + 1.0)
+            ln.bias.copy_(torch.randn(C) * 0.2)
+        x = (torch.randn(rows, C, device="cuda") * 2 + 0.5).to(dtype).requires_grad_(True)
+        assert supported(x, ln.weight, ln.bias), (rows, C)
+        y = ln(x)
+        dy = torch.randn_like(y)
+        y.backward(dy)
+        xr = x.detach().float().requires_grad_(True)
+        wr, br = ln.weight.detach().float().requires_grad_(True), ln.bias.detach().float().requires_grad_(True)
+        yr = torch.nn.functional.layer_norm(xr, (C,), wr, br, ln.eps)
+        yr.backward(dy.float())
+        tol = 3e-2 if dtype == torch.bfloat16 else 1e-4
+        assert torch.allclose(y.float(), yr, rtol=tol, atol=tol), (rows, C)
+        for g, gr in ((x.grad, xr.grad), (ln.weight.grad, wr.grad), (ln.bias.grad, br.grad)):
+            rel = (g.float() - gr).norm() / gr.norm()
+            assert rel < (2e-2 if dtype == torch.bfloat16 else 1e-5), (rows, C, rel.item())

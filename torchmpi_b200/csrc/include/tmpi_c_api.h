@@ -230,8 +230,15 @@ int tmpi_easgd_elastic(void* local, const void* center, void* delta, size_t n, i
                        float alpha, void* stream);
 int tmpi_downpour_accum(void* accum, const void* grad, size_t n, int dtype, float scale,
                         int zero_first, void* stream);
-int tmpi_layernorm_gelu(const void* x, const void* gamma, const void* beta, void* y,
-                        int rows, int cols, int dtype, float eps, int apply_gelu, void* stream);
+// layer normalisation over the last dimension of [rows, channels]; x, y, gamma, beta share the dtype;
+// mean / rstd ([rows], fp32) are written by forward and read by backward
+int tmpi_layernorm_supported(int channels, int dtype);
+size_t tmpi_layernorm_scratch_bytes(int channels);
+int tmpi_layernorm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd,
+                       int rows, int channels, float eps, int dtype, void* stream);
+int tmpi_layernorm_bwd(const void* x, const void* dy, const void* gamma, const float* mean, const float* rstd,
+                       void* dx, void* dgamma, void* dbeta, int rows, int channels, int dtype, void* scratch,
+                       void* stream);
 int tmpi_bn_relu_fwd(const void* x, const void* residual, void* y, const float* gamma,
                      const float* beta, float* running_mean, float* running_var,
                      float* save_mean, float* save_invstd, int64_t rows, int channels,

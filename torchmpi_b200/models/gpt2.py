@@ -4,7 +4,8 @@ Used by the hierarchical-training config: synchronous fused allreduce inside a g
 GPU-resident parameter server across groups.  The reference has no sequence model
 (its largest network is a 6-layer Linear stack, test/async.lua:37-43).  Attention uses PyTorch's
 scaled-dot-product attention; the matrix products of the MLP and projections go through
-``ops.gemm.linear`` (the tcgen05 kernel) when ``tc_linear=True``; the loss is ``ops.xent``.
+``ops.gemm.linear`` (the tcgen05 kernel) when ``tc_linear=True``, which also selects the one-pass
+layer norm of ``ops.layernorm`` and the pitched LM head of ``ops.gemm.wide_head``; the loss is ``ops.xent``.
 """
 from __future__ import annotations
 
@@ -49,14 +50,21 @@ class _Linear(nn.Linear):
         return F.gelu(y) if self.gelu else y
 
 
+def _layer_norm(c: "GPT2Config") -> nn.LayerNorm:
+    if c.tc_linear:
+        from ..ops.layernorm import LayerNorm
+        return LayerNorm(c.n_embd)
+    return nn.LayerNorm(c.n_embd)
+
+
 class Block(nn.Module):
     def __init__(self, c: GPT2Config):
         super().__init__()
         self.n_head = c.n_head
-        self.ln1 = nn.LayerNorm(c.n_embd)
+        self.ln1 = _layer_norm(c)
         self.qkv = _Linear(c.n_embd, 3 * c.n_embd, c.tc_linear)
         self.proj = _Linear(c.n_embd, c.n_embd, c.tc_linear)
-        self.ln2 = nn.LayerNorm(c.n_embd)
+        self.ln2 = _layer_norm(c)
         self.fc = _Linear(c.n_embd, 4 * c.n_embd, c.tc_linear, gelu=True)
         self.out = _Linear(4 * c.n_embd, c.n_embd, c.tc_linear)
 
@@ -76,7 +84,7 @@ class GPT2(nn.Module):
         self.wte = nn.Embedding(c.vocab_size, c.n_embd)
         self.wpe = nn.Embedding(c.block_size, c.n_embd)
         self.blocks = nn.ModuleList([Block(c) for _ in range(c.n_layer)])
-        self.ln_f = nn.LayerNorm(c.n_embd)
+        self.ln_f = _layer_norm(c)
         self.apply(self._init)
         for b in self.blocks:   # scaled init of the residual projections
             for lin in (b.proj, b.out):
