@@ -31,6 +31,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--update-frequency", type=int, default=4)
     ap.add_argument("--tc-linear", type=int, default=1)
+    ap.add_argument("--profile-one-step", action="store_true",
+                    help="after the warm-up run one step between cudaProfilerStart/Stop and exit (no timing)")
     args = ap.parse_args()
 
     import torchmpi_b200 as mpi
@@ -79,6 +81,14 @@ def main():
         step(i)
     torch.cuda.synchronize()
     mpi.barrier()
+    if args.profile_one_step:
+        # for `ncu --profile-from-start off`: exactly one training step lies inside the profiler range
+        torch.cuda.profiler.start()
+        step(args.warmup)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        mpi.stop()
+        return
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(args.steps):
