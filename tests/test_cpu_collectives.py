@@ -125,6 +125,10 @@ def _matrix(rank, world):
         res = ns.allgather_tensor(inp, out)
         expect = torch.cat([torch.full((5 + r,), float(r)) for r in range(n)])
         assert res.numel() == expect.numel() and torch.equal(res.view(-1), expect)
+    # equal contributions announced by the caller: no count exchange on the control plane
+    for ns in (mpi, mpi.p2p):
+        res = ns.allgather_tensor(torch.full((7,), float(rank)), torch.empty(7 * n), equal_counts=True)
+        assert torch.equal(res.view(-1), torch.arange(n, dtype=torch.float32).repeat_interleave(7))
     # reduce_scatter
     inp = torch.arange(n * 10, dtype=torch.float32) + rank
     out = torch.empty(10)
