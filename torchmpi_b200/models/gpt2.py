@@ -112,8 +112,13 @@ class GPT2(nn.Module):
 
 
 class LMLoss(nn.Module):
-    """Next-token cross-entropy over flattened logits; the fused kernel on CUDA."""
+    """Next-token cross-entropy over flattened logits; the fused kernel on CUDA.  ``unit_grad``: see
+    ``ops.xent.cross_entropy`` (for training loops that call ``loss.backward()`` on this loss itself)."""
+
+    def __init__(self, unit_grad: bool = False):
+        super().__init__()
+        self.unit_grad = unit_grad
 
     def forward(self, logits: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
         from ..ops import xent
-        return xent.cross_entropy(logits, targets.reshape(-1))
+        return xent.cross_entropy(logits, targets.reshape(-1), self.unit_grad)

@@ -23,8 +23,9 @@ def _scratch_for(dev: torch.device, rows: int) -> torch.Tensor:
 
 class _XentFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, logits: torch.Tensor, labels: torch.Tensor):
+    def forward(ctx, logits: torch.Tensor, labels: torch.Tensor, unit_grad: bool = False):
         global launch_count
+        ctx.unit_grad = unit_grad
         launch_count += 1
         rows, cols = logits.shape
         # rows may sit in a wider buffer (a [T, 50257] logit matrix kept with a pitch of 50264 so that the
@@ -44,20 +45,28 @@ class _XentFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_out):
         buf, ctx.grad_buf = ctx.grad_buf, None          # scaled in place: backward runs once
-        buf.mul_(grad_out.to(buf.dtype))
-        return buf[:, :ctx.cols], None
+        if not ctx.unit_grad:
+            buf.mul_(grad_out.to(buf.dtype))
+        return buf[:, :ctx.cols], None, None
 
 
-def cross_entropy(logits: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
+def cross_entropy(logits: torch.Tensor, labels: torch.Tensor, unit_grad: bool = False) -> torch.Tensor:
+    """``unit_grad=True`` is a promise that backward starts at this loss (``loss.backward()``, incoming gradient
+    1): the stored gradient is then handed on as it is, without a pass that multiplies it by the incoming
+    gradient.  A scaled or combined loss must leave it off."""
     if logits.is_cuda:
         if not has_symbol("tmpi_xent_fwd_bwd"):
             raise RuntimeError("torchmpi_b200: native kernel 'tmpi_xent_fwd_bwd' is missing")
         if logits.dim() != 2 or labels.dtype != torch.int64:
             raise ValueError("cross_entropy expects [rows, classes] logits and int64 labels")
-        return _XentFn.apply(logits, labels.contiguous())
+        return _XentFn.apply(logits, labels.contiguous(), unit_grad)
     return torch.nn.functional.cross_entropy(logits.float(), labels)
 
 
 class CrossEntropyLoss(torch.nn.Module):
+    def __init__(self, unit_grad: bool = False):
+        super().__init__()
+        self.unit_grad = unit_grad
+
     def forward(self, logits, labels):
-        return cross_entropy(logits, labels)
+        return cross_entropy(logits, labels, self.unit_grad)

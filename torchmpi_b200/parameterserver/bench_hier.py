@@ -62,7 +62,7 @@ def main():
     group = mpi.intra_members(1)
     engine = AllReduceSGDEngine(usegpu=True, devicesync=False, fused=True, momentum=0.9,
                                 gradient_scale=1.0 / len(group))
-    criterion = gpt2.LMLoss()
+    criterion = gpt2.LMLoss(unit_grad=True)          # the engine calls backward on this loss itself
     state = {"network": model, "criterion": criterion, "iterator": None, "lr": 1e-3, "lrcriterion": 0.0,
              "maxepoch": 1, "sample": None, "epoch": 0, "t": 0, "training": True}
     engine._setup(model, criterion)
