@@ -188,3 +188,19 @@ def test_wide_head_and_pitched_cross_entropy():
             rel = (g.float() - gr).norm() / gr.norm()
             assert rel < 3e-2, (T, d, V, rel.item())
         gemm.check_status()
+
+
+def test_bias_grad_with_and_without_gelu():
+    """Column sum fused with the GELU backward against PyTorch in fp32."""
+    from torchmpi_b200.ops import gemm
+    torch.manual_seed(13)
+    for rows, C in ((8192, 1024), (777, 4096), (33, 3072)):
+        dy = torch.randn(rows, C, device="cuda").to(torch.bfloat16)
+        z = (torch.randn(rows, C, device="cuda") * 1.5).to(torch.bfloat16)
+        dz, db = gemm.bias_grad(dy, z)
+        ref = torch.ops.aten.gelu_backward(dy.float(), z.float())
+        assert torch.allclose(dz.float(), ref, rtol=2e-2, atol=2e-2)
+        assert torch.allclose(db.float(), dz.float().sum(0), rtol=1e-2, atol=0.05 * rows ** 0.5)
+        same, db2 = gemm.bias_grad(dy)
+        assert same is dy
+        assert torch.allclose(db2.float(), dy.float().sum(0), rtol=1e-2, atol=0.05 * rows ** 0.5)

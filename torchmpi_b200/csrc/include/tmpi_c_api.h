@@ -230,6 +230,11 @@ int tmpi_easgd_elastic(void* local, const void* center, void* delta, size_t n, i
                        float alpha, void* stream);
 int tmpi_downpour_accum(void* accum, const void* grad, size_t n, int dtype, float scale,
                         int zero_first, void* stream);
+// bias gradient of a linear layer: db[c] = sum_r dz[r, c]; with z given, dz = dy * gelu'(z) is computed and
+// written in the same pass (channels a multiple of 1024 for 16-bit types, 512 for fp32)
+size_t tmpi_bias_grad_scratch_bytes(int channels);
+int tmpi_bias_grad(const void* dy, const void* z, void* dz, void* db, int rows, int channels, int dtype,
+                   void* scratch, void* stream);
 // layer normalisation over the last dimension of [rows, channels]; x, y, gamma, beta share the dtype;
 // mean / rstd ([rows], fp32) are written by forward and read by backward
 int tmpi_layernorm_supported(int channels, int dtype);

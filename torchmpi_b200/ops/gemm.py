@@ -153,6 +153,35 @@ def wide_head(x2: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     return torch.nn.functional.linear(x2, w)
 
 
+_bg_scratch = {}
+
+
+def bias_grad(dy2: torch.Tensor, z: Optional[torch.Tensor] = None):
+    """``(dz, db)`` with ``dz = dy2 * gelu'(z)`` (``dy2`` itself when ``z`` is None) and ``db = dz.sum(0)``, in one
+    pass over ``dy2`` (and ``z``) where the kernel applies (csrc/kernels/bias_grad.cu); PyTorch ops otherwise."""
+    global launch_count
+    rows, C = dy2.shape
+    per_slab = 128 * (16 // dy2.element_size())
+    if not (dy2.is_cuda and dy2.is_contiguous() and C % per_slab == 0 and has_symbol("tmpi_bias_grad")
+            and dy2.dtype in (torch.bfloat16, torch.float16, torch.float32)
+            and (z is None or (z.is_contiguous() and z.dtype == dy2.dtype))):
+        dz = torch.ops.aten.gelu_backward(dy2, z) if z is not None else dy2
+        return dz, dz.sum(0)
+    key = (dy2.device.index, torch.cuda.current_stream().cuda_stream)
+    need = lib.tmpi_bias_grad_scratch_bytes(C)
+    buf = _bg_scratch.get(key)
+    if buf is None or buf.numel() < need:
+        buf = _bg_scratch[key] = torch.empty(need, dtype=torch.uint8, device=dy2.device)
+    dz = torch.empty_like(dy2) if z is not None else dy2
+    db = torch.empty(C, dtype=dy2.dtype, device=dy2.device)
+    from .._lib import dtype_code
+    check(lib.tmpi_bias_grad(dy2.data_ptr(), z.data_ptr() if z is not None else None,
+                             dz.data_ptr() if z is not None else None, db.data_ptr(), rows, C, dtype_code(dy2.dtype),
+                             buf.data_ptr(), stream_ptr()))
+    launch_count += 2
+    return dz, db
+
+
 class _LinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, bias, gelu):
@@ -171,11 +200,13 @@ class _LinearFn(torch.autograd.Function):
     def backward(ctx, dy):
         x2, w, z = ctx.saved_tensors
         dy2 = dy.reshape(-1, dy.shape[-1]).contiguous()
-        if ctx.gelu:
+        db = None
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            dy2, db = bias_grad(dy2, z if ctx.gelu else None)       # GELU backward and the column sum in one pass
+        elif ctx.gelu:
             dy2 = torch.ops.aten.gelu_backward(dy2, z)
         dx = matmul_nn(dy2, w) if ctx.needs_input_grad[0] else None
         dw = matmul_tn(dy2, x2) if ctx.needs_input_grad[1] else None
-        db = dy2.sum(0) if ctx.has_bias and ctx.needs_input_grad[2] else None
         return (dx.reshape(ctx.shape) if dx is not None else None), dw, db, None
 
 

@@ -142,11 +142,10 @@ class _TPMLPFn(torch.autograd.Function):
         # the two weight gradients are local GEMMs whose contraction dimension is the slow one of both
         # operands: the CTA-pair kernel reads them as they lie (MN-major descriptors)
         dw2 = gemm.matmul_tn(dy_full, h)                                                      # [D, F/R]
-        db2 = dy_full.sum(0, dtype=torch.float32).to(dy_full.dtype) if ctx.has_b2 else None
-        dz = torch.ops.aten.gelu_backward(dh, z)
+        db2 = gemm.bias_grad(dy_full)[1] if ctx.has_b2 else None
+        dz, db1 = gemm.bias_grad(dh, z) if ctx.has_b1 else (torch.ops.aten.gelu_backward(dh, z), None)
         dx = tp.gemm_rs(dz, w1, w_is_kn=True)                                                 # [rows, D] = dz @ w1
         dw1 = gemm.matmul_tn(dz, x_full)                                                      # [F/R, D]
-        db1 = dz.sum(0, dtype=torch.float32).to(dz.dtype) if ctx.has_b1 else None
         return dx, dw1, db1, dw2, db2, None, None, None
 
 
