@@ -87,6 +87,13 @@ def cases(small: bool):
 
     from torchmpi_b200 import config
     from torchmpi_b200.ops import gemm
+    br, bc = (8192, 4096)
+    bdy = torch.randn(br, bc, device=dev).to(torch.bfloat16)
+    bz = torch.randn(br, bc, device=dev).to(torch.bfloat16)
+    out["bias_grad_gelu_bwd"] = (lambda: gemm.bias_grad(bdy, bz), br * bc * 2 * 3)      # dy, z read; dz written
+    out["bias_grad_plain"] = (lambda: gemm.bias_grad(bdy), br * bc * 2)
+    bn_ = bdy[:, :1024].contiguous()
+    out["bias_grad_plain_1024"] = (lambda: gemm.bias_grad(bn_), br * 1024 * 2)
     for name, (M, N, K) in {"gemm_bf16_8192": (8192, 8192, 8192), "gemm_bf16_tp_col": (8192, 4096, 8192),
                             "gemm_bf16_tp_row": (8192, 8192, 4096)}.items():
         if small and name != "gemm_bf16_tp_col":
