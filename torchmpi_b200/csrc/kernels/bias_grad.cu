@@ -14,7 +14,7 @@ namespace tmpi {
 
 constexpr int kBgThreads = 256, kBgCols = 128;      // 128 column groups x 2 rows per block
 constexpr int kBgMaxRowBlocks = 4 * 148;            // partial rows the scratch buffer holds
-constexpr int kBgFinCols = 32, kBgFinGroups = 8;    // finalize: 32 columns x 8 groups of partial rows per block
+constexpr int kBgFinCols = 32, kBgFinGroups = 32;   // finalize: 32 columns x 32 groups of partial rows per block
 
 // d/dz [z * Phi(z)] = Phi(z) + z * phi(z).  Phi through the rational erf approximation of Abramowitz and
 // Stegun 7.1.26 (absolute error 1.5e-7), which shares its exp(-z^2 / 2) with phi: one ex2, one rcp and a
@@ -88,8 +88,8 @@ bias_grad_kernel(const T* __restrict__ dy, const T* __restrict__ z, T* __restric
   }
 }
 
-// One block per 32 columns; eight warps each add a contiguous range of the partial rows (four loads in
-// flight), then warp 0 adds the eight sums in order: the result does not depend on the launch.
+// One block per 32 columns; 32 warps each add a contiguous range of the partial rows, then warp 0 adds
+// the 32 sums in order: the result does not depend on the launch.
 template <typename T>
 __global__ void __launch_bounds__(kBgFinCols * kBgFinGroups)
 bias_grad_finalize_kernel(const float* __restrict__ partial, int nblocks, int C, T* __restrict__ db) {
@@ -99,10 +99,12 @@ bias_grad_finalize_kernel(const float* __restrict__ partial, int nblocks, int C,
   int b = grp * per;
   const int end = min(nblocks, b + per);
   float t = 0.f;
-  for (; b + 4 <= end; b += 4) {
-    const float a0 = partial[(size_t)b * C + c], a1 = partial[(size_t)(b + 1) * C + c];
-    const float a2 = partial[(size_t)(b + 2) * C + c], a3 = partial[(size_t)(b + 3) * C + c];
-    t += a0; t += a1; t += a2; t += a3;
+  for (; b + 8 <= end; b += 8) {                        // eight loads in flight, added in row order
+    float a[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) a[u] = partial[(size_t)(b + u) * C + c];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) t += a[u];
   }
   for (; b < end; ++b) t += partial[(size_t)b * C + c];
   __shared__ float s[kBgFinGroups][kBgFinCols];

@@ -11,7 +11,7 @@ from typing import Optional
 
 import torch
 
-from .._lib import lib, check, has_symbol, stream_ptr, TorchMPIError
+from .._lib import lib, check, dtype_code, has_symbol, stream_ptr, TorchMPIError
 
 EPI_NONE, EPI_BIAS, EPI_GELU = 0, 1, 2
 B_IS_KN = 4          # flag in the same word: the second operand is [K, N] with N contiguous
@@ -154,6 +154,7 @@ def wide_head(x2: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
 
 
 _bg_scratch = {}
+_bg_need = {}
 
 
 def bias_grad(dy2: torch.Tensor, z: Optional[torch.Tensor] = None):
@@ -167,17 +168,24 @@ def bias_grad(dy2: torch.Tensor, z: Optional[torch.Tensor] = None):
             and (z is None or (z.is_contiguous() and z.dtype == dy2.dtype))):
         dz = torch.ops.aten.gelu_backward(dy2, z) if z is not None else dy2
         return dz, dz.sum(0)
-    key = (dy2.device.index, torch.cuda.current_stream().cuda_stream)
-    need = lib.tmpi_bias_grad_scratch_bytes(C)
+    sp = torch.cuda.current_stream().cuda_stream
+    key = (dy2.device.index, sp)
+    need = _bg_need.get(C)
+    if need is None:
+        need = _bg_need[C] = lib.tmpi_bias_grad_scratch_bytes(C)
     buf = _bg_scratch.get(key)
     if buf is None or buf.numel() < need:
         buf = _bg_scratch[key] = torch.empty(need, dtype=torch.uint8, device=dy2.device)
-    dz = torch.empty_like(dy2) if z is not None else dy2
     db = torch.empty(C, dtype=dy2.dtype, device=dy2.device)
-    from .._lib import dtype_code
-    check(lib.tmpi_bias_grad(dy2.data_ptr(), z.data_ptr() if z is not None else None,
-                             dz.data_ptr() if z is not None else None, db.data_ptr(), rows, C, dtype_code(dy2.dtype),
-                             buf.data_ptr(), stream_ptr()))
+    if z is None:
+        dz = dy2
+        st = lib.tmpi_bias_grad(dy2.data_ptr(), None, None, db.data_ptr(), rows, C, dtype_code(dy2.dtype), buf.data_ptr(), sp)
+    else:
+        dz = torch.empty_like(dy2)
+        st = lib.tmpi_bias_grad(dy2.data_ptr(), z.data_ptr(), dz.data_ptr(), db.data_ptr(), rows, C, dtype_code(dy2.dtype),
+                                buf.data_ptr(), sp)
+    if st:
+        check(st)
     launch_count += 2
     return dz, db
 
