@@ -33,7 +33,7 @@ __device__ __forceinline__ float gelu_grad(float z) {
 
 // partial[blockIdx.y * C + c]
 template <typename T, int V, bool GELU>
-__global__ void __launch_bounds__(kBgThreads, GELU ? 3 : 4)
+__global__ void __launch_bounds__(kBgThreads, 4)
 bias_grad_kernel(const T* __restrict__ dy, const T* __restrict__ z, T* __restrict__ dz, float* __restrict__ partial,
                  int rows, int C) {
   const int tx = threadIdx.x % kBgCols, ty = threadIdx.x / kBgCols;
@@ -41,7 +41,7 @@ bias_grad_kernel(const T* __restrict__ dy, const T* __restrict__ z, T* __restric
   float acc[V];
 #pragma unroll
   for (int k = 0; k < V; ++k) acc[k] = 0.f;
-  constexpr int U = 4;                                  // rows in flight per thread
+  constexpr int U = GELU ? 2 : 4;                       // rows in flight per thread (63 registers either way)
   const int step = 2 * gridDim.y;
   auto one = [&](const Pack<T, V>& g, const Pack<T, V>& a, size_t at) {
     if (GELU) {
@@ -124,7 +124,7 @@ static int bias_grad_t(const void* dy, const void* z, void* dz, void* db, int ro
   if (rows < 1 || C % (kBgCols * V)) return fail(TMPI_ERR_UNSUPPORTED, "bias_grad: C=%d must be a multiple of %d", C, kBgCols * V);
   if (z && !dz) return fail(TMPI_ERR_INVALID, "bias_grad: z given without an output for dz");
   const int slabs = C / (kBgCols * V);
-  const int per_sm = z ? 3 : 4;                          // resident blocks per SM of the two variants
+  const int per_sm = 4;                                  // resident blocks per SM
   const int rb = std::max(1, std::min((rows + 1) / 2, std::max(1, per_sm * 148 / slabs)));
   const dim3 grid(slabs, rb);
   if (z) bias_grad_kernel<T, V, true><<<grid, kBgThreads, 0, s>>>((const T*)dy, (const T*)z, (T*)dz, (float*)scratch, rows, C);
