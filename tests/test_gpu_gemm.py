@@ -204,3 +204,17 @@ def test_bias_grad_with_and_without_gelu():
         same, db2 = gemm.bias_grad(dy)
         assert same is dy
         assert torch.allclose(db2.float(), dy.float().sum(0), rtol=1e-2, atol=0.05 * rows ** 0.5)
+
+
+def test_gelu_forward_kernel():
+    """The erf-form GELU through the rational approximation against PyTorch in fp32."""
+    from torchmpi_b200.ops import gemm
+    torch.manual_seed(17)
+    for shape, dt in (((8192, 4096), torch.bfloat16), ((333, 1000), torch.float32), ((64, 40), torch.float16)):
+        z = (torch.randn(*shape, device="cuda") * 2.5).to(dt)
+        y = gemm.gelu(z)
+        ref = torch.nn.functional.gelu(z.float())
+        tol = 1e-5 if dt == torch.float32 else 2e-2
+        assert torch.allclose(y.float(), ref, rtol=tol, atol=tol), (shape, dt)
+    edge = torch.tensor([-30.0, -8.0, -0.0, 0.0, 8.0, 30.0, float("inf")], device="cuda").repeat(4)[:24].contiguous()
+    assert torch.allclose(gemm.gelu(edge), torch.nn.functional.gelu(edge), atol=1e-5)

@@ -176,6 +176,7 @@ _CUDA_PROTOS = {
     "tmpi_downpour_accum": (_i, [_vp, _vp, _sz, _i, _f, _i, _vp]),
     "tmpi_bias_grad_scratch_bytes": (_sz, [_i]),
     "tmpi_bias_grad": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp]),
+    "tmpi_gelu_fwd": (_i, [_vp, _vp, _sz, _i, _vp]),
     "tmpi_layernorm_supported": (_i, [_i, _i]),
     "tmpi_layernorm_scratch_bytes": (_sz, [_i]),
     "tmpi_layernorm_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _vp]),

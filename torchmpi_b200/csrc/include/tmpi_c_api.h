@@ -235,6 +235,8 @@ int tmpi_downpour_accum(void* accum, const void* grad, size_t n, int dtype, floa
 size_t tmpi_bias_grad_scratch_bytes(int channels);
 int tmpi_bias_grad(const void* dy, const void* z, void* dz, void* db, int rows, int channels, int dtype,
                    void* scratch, void* stream);
+// y = gelu(z), erf form, n elements (a multiple of 16 bytes, pointers 16-byte aligned)
+int tmpi_gelu_fwd(const void* z, void* y, size_t n, int dtype, void* stream);
 // layer normalisation over the last dimension of [rows, channels]; x, y, gamma, beta share the dtype;
 // mean / rstd ([rows], fp32) are written by forward and read by backward
 int tmpi_layernorm_supported(int channels, int dtype);

@@ -5,6 +5,7 @@
 // kernels, the second re-reading dz.  Columns are processed in slabs of 1024 (128 threads x one
 // 16-byte pack), two rows at a time per block; every thread keeps its eight column sums in
 // registers, blocks write partials and a second kernel adds them in block order (deterministic).
+// The GELU forward with the same approximation of the normal distribution lives here too.
 #include "vec.cuh"
 #include "../include/tmpi_c_api.h"
 #include "../runtime/common.h"
@@ -16,19 +17,69 @@ constexpr int kBgThreads = 256, kBgCols = 128;      // 128 column groups x 2 row
 constexpr int kBgMaxRowBlocks = 4 * 148;            // partial rows the scratch buffer holds
 constexpr int kBgFinCols = 32, kBgFinGroups = 32;   // finalize: 32 columns x 32 groups of partial rows per block
 
-// d/dz [z * Phi(z)] = Phi(z) + z * phi(z).  Phi through the rational erf approximation of Abramowitz and
+// gelu(z) = z * Phi(z);  d/dz [z * Phi(z)] = Phi(z) + z * phi(z).  Phi through the rational erf approximation of Abramowitz and
 // Stegun 7.1.26 (absolute error 1.5e-7), which shares its exp(-z^2 / 2) with phi: one ex2, one rcp and a
 // dozen FMAs per element keep the kernel memory bound where erff() made it ALU bound.
-__device__ __forceinline__ float gelu_grad(float z) {
-  const float e = __expf(-0.5f * z * z);
+__device__ __forceinline__ void normal_parts(float z, float* cdf, float* e) {
+  *e = __expf(-0.5f * z * z);
   const float t = __fdividef(1.f, fmaf(0.3275911f * 0.70710678118654752f, fabsf(z), 1.f));
   float poly = fmaf(1.061405429f, t, -1.453152027f);
   poly = fmaf(poly, t, 1.421413741f);
   poly = fmaf(poly, t, -0.284496736f);
   poly = fmaf(poly, t, 0.254829592f);
-  const float q = 0.5f * poly * t * e;                  // 1 - Phi(|z|)
-  const float cdf = z >= 0.f ? 1.f - q : q;
+  const float q = 0.5f * poly * t * *e;                 // 1 - Phi(|z|)
+  *cdf = z >= 0.f ? 1.f - q : q;
+}
+
+__device__ __forceinline__ float gelu_grad(float z) {
+  float cdf, e;
+  normal_parts(z, &cdf, &e);
   return fmaf(z * 0.3989422804014327f, e, cdf);
+}
+
+__device__ __forceinline__ float gelu_value(float z) {
+  float cdf, e;
+  normal_parts(z, &cdf, &e);
+  return z * cdf;
+}
+
+// y = gelu(z), one 16-byte pack per thread and step, four steps in flight.
+template <typename T, int V>
+__global__ void __launch_bounds__(256) gelu_fwd_kernel(const T* __restrict__ z, T* __restrict__ y, size_t npacks) {
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  constexpr int U = 4;
+  for (; i + (U - 1) * stride < npacks; i += U * stride) {
+    Pack<T, V> a[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) a[u] = ld_pack<T, V>(z + (i + u * stride) * V);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      Pack<T, V> o;
+#pragma unroll
+      for (int k = 0; k < V; ++k) o.v[k] = from_acc<T>((typename AccOf<T>::type)gelu_value((float)to_acc<T>(a[u].v[k])));
+      st_pack<T, V>(y + (i + u * stride) * V, o);
+    }
+  }
+  for (; i < npacks; i += stride) {
+    Pack<T, V> a = ld_pack<T, V>(z + i * V), o;
+#pragma unroll
+    for (int k = 0; k < V; ++k) o.v[k] = from_acc<T>((typename AccOf<T>::type)gelu_value((float)to_acc<T>(a.v[k])));
+    st_pack<T, V>(y + i * V, o);
+  }
+}
+
+template <typename T>
+static int gelu_fwd_t(const void* z, void* y, size_t n, cudaStream_t s) {
+  constexpr int V = 16 / sizeof(T);
+  if (n % V || ((uintptr_t)z & 15) || ((uintptr_t)y & 15))
+    return fail(TMPI_ERR_UNSUPPORTED, "gelu_fwd: n=%zu must be a multiple of %d and the pointers 16-byte aligned", n, V);
+  const size_t npacks = n / V;
+  if (!npacks) return TMPI_OK;
+  const int blocks = (int)std::min<size_t>((npacks + 255) / 256, (size_t)148 * 8);
+  gelu_fwd_kernel<T, V><<<blocks, 256, 0, s>>>((const T*)z, (T*)y, npacks);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? TMPI_OK : fail(TMPI_ERR_CUDA, "gelu_fwd launch: %s", cudaGetErrorString(e));
 }
 
 // partial[blockIdx.y * C + c]
@@ -153,6 +204,17 @@ int tmpi_bias_grad(const void* dy, const void* z, void* dz, void* db, int rows, 
     case TMPI_F32: return bias_grad_t<float>(dy, z, dz, db, rows, channels, scratch, s);
   }
   return fail(TMPI_ERR_UNSUPPORTED, "bias_grad: dtype %d", dtype);
+}
+
+// y = gelu(z) (erf form) for n elements of `dtype`; the forward companion of tmpi_bias_grad's derivative.
+int tmpi_gelu_fwd(const void* z, void* y, size_t n, int dtype, void* stream) {
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (dtype) {
+    case TMPI_BF16: return gelu_fwd_t<__nv_bfloat16>(z, y, n, s);
+    case TMPI_F16: return gelu_fwd_t<__half>(z, y, n, s);
+    case TMPI_F32: return gelu_fwd_t<float>(z, y, n, s);
+  }
+  return fail(TMPI_ERR_UNSUPPORTED, "gelu_fwd: dtype %d", dtype);
 }
 
 }  // extern "C"

@@ -153,6 +153,22 @@ def wide_head(x2: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     return torch.nn.functional.linear(x2, w)
 
 
+def gelu(z: torch.Tensor) -> torch.Tensor:
+    """``gelu(z)`` (erf form, no autograd) through ``tmpi_gelu_fwd`` (csrc/kernels/bias_grad.cu: rational erf, so the pass
+    is memory bound) where it applies; ``F.gelu`` otherwise.  ``bias_grad(dy, z)`` is its backward."""
+    global launch_count
+    if not (z.is_cuda and z.is_contiguous() and z.dtype in (torch.bfloat16, torch.float16, torch.float32)
+            and (z.numel() * z.element_size()) % 16 == 0 and z.data_ptr() % 16 == 0 and has_symbol("tmpi_gelu_fwd")):
+        return torch.nn.functional.gelu(z)
+    y = torch.empty_like(z)
+    st = lib.tmpi_gelu_fwd(z.data_ptr(), y.data_ptr(), z.numel(), dtype_code(z.dtype), stream_ptr())
+    if st:
+        check(st)
+    launch_count += 1
+    return y
+
+
+_gelu_kernel = gelu          # `_LinearFn.forward` has a flag named `gelu`
 _bg_scratch = {}
 _bg_need = {}
 
@@ -196,7 +212,7 @@ class _LinearFn(torch.autograd.Function):
         x2 = x.reshape(-1, x.shape[-1])
         if gelu:
             z = matmul_nt(x2, w, bias)                       # pre-activation is needed by backward
-            y = torch.nn.functional.gelu(z)
+            y = _gelu_kernel(z)
             ctx.save_for_backward(x2, w, z)
         else:
             y = matmul_nt(x2, w, bias)

@@ -123,7 +123,7 @@ class _TPMLPFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x_shard, w1, b1, w2, b2, tp: TPGroup, full_buf, full_off):
         z = tp.ag_gemm(x_shard, full_off, full_buf, w1, b1)           # [M, F/R] pre-activation
-        h = torch.nn.functional.gelu(z)
+        h = gemm.gelu(z)
         y = tp.gemm_rs(h, w2)                                          # [rows, D]
         if b2 is not None:
             y = y + b2
