@@ -158,3 +158,23 @@ def test_shard_ranges():
         assert e.value - b.value == n // size + (1 if r < n % size else 0)
         covered = e.value
     assert covered == n
+
+
+def test_linear_ops_fall_back_to_pytorch_on_cpu():
+    """``ops.gemm`` wrappers (GELU, bias gradient, Linear) use PyTorch where the CUDA kernels do not apply."""
+    import torch
+    from torchmpi_b200.ops import gemm
+    torch.manual_seed(0)
+    z, dy = torch.randn(16, 64), torch.randn(16, 64)
+    assert torch.allclose(gemm.gelu(z), torch.nn.functional.gelu(z))
+    dz, db = gemm.bias_grad(dy, z)
+    ref = torch.ops.aten.gelu_backward(dy, z)
+    assert torch.allclose(dz, ref) and torch.allclose(db, ref.sum(0))
+    same, db2 = gemm.bias_grad(dy)
+    assert same is dy and torch.allclose(db2, dy.sum(0))
+    lin = gemm.Linear(64, 32, gelu=True)
+    x = torch.randn(4, 64, requires_grad=True)
+    lin(x).sum().backward()
+    xr = x.detach().clone().requires_grad_(True)
+    torch.nn.functional.gelu(torch.nn.functional.linear(xr, lin.weight.detach(), lin.bias.detach())).sum().backward()
+    assert torch.allclose(x.grad, xr.grad, atol=1e-6)
