@@ -241,6 +241,14 @@ def dtype_code(dt: torch.dtype) -> int:
         raise TypeError(f"torchmpi_b200: unsupported dtype {dt}") from None
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def stream_ptr(stream=None) -> int:
-    s = stream if stream is not None else torch.cuda.current_stream()
-    return s.cuda_stream
+    """The ``cudaStream_t`` of ``stream`` (default: the current stream of the current device) as an integer.
+    The raw accessor avoids building a ``torch.cuda.Stream`` object for every kernel launch."""
+    if stream is not None:
+        return stream.cuda_stream
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
+    return torch.cuda.current_stream().cuda_stream
