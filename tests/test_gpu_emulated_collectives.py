@@ -101,6 +101,38 @@ def test_allreduce_rank_fill_is_exact(emu):
     status_ok(h)
 
 
+def test_oneshot_slots_stay_inside_their_lane(emu):
+    """One-shot allreduces on lane 0 and lane 1, even and odd epochs: each lane may only write its own
+    2 * world slots; the other lanes' slots and the bounce buffers must keep their contents."""
+    from torchmpi_b200._lib import lib, check
+    h, W = emu, emu.world
+    lib.tmpi_cuda_heap_reset_allocator(0)
+    lay = h.layout()
+    n = 4096
+    off, ts = fill(h, n, torch.float32, 21)
+    want = sum(t.double() for t in ts)
+    region = lay["arena_off"] - lay["slots_off"]               # slots of all lanes + both bounce buffers
+    lane_bytes = 2 * W * lay["slot_bytes"]
+    views = [h.view(lay["slots_off"], region, peer=r) for r in range(W)]
+    for lane in (0, 1):
+        for v in views:
+            v.fill_(0x5A)
+        g, keep = group(W, lane)
+        for _ in range(3):                                      # consecutive epochs: both parities are used
+            for r, t in enumerate(ts):
+                t.copy_(torch.randn(n, generator=torch.Generator(device="cuda").manual_seed(21 + r), device="cuda"))
+            want = sum(t.double() for t in ts)
+            check(lib.tmpi_cuda_allreduce_heap(off, off, n, 7, 1.0, C.byref(g), 1, torch.cuda.current_stream().cuda_stream))
+            torch.cuda.synchronize()
+            h.check_status(lane)
+            for t in ts:
+                assert torch.allclose(t.double(), want, atol=1e-4)
+        lo, hi = lane * lane_bytes, (lane + 1) * lane_bytes
+        for v in views:
+            assert bool((v[:lo] == 0x5A).all()) and bool((v[hi:] == 0x5A).all()), f"lane {lane} wrote outside its slots"
+            assert not bool((v[lo:hi] == 0x5A).all())
+
+
 @pytest.mark.parametrize("algo", [1, 2])    # 1 = pull (auto small), 2 = chunked
 def test_broadcast(emu, algo):
     from torchmpi_b200._lib import lib, check

@@ -249,6 +249,7 @@ def _absent_peer(rank, world):
     import torchmpi_b200 as mpi
     from torchmpi_b200 import config
     config.set("device_wait_budget_ms", 1000)
+    config.set("device_wait_startup_grace_ms", 0)      # the steady-state budget from the first call on
     config.set("use_nvls", 0)
     mpi.start(with_cuda=True)
     dev = mpi.device

@@ -51,6 +51,66 @@ def test_noalloc_xent_matches_regular_entry_point_twice():
         assert torch.allclose(loss_a[0], ref, atol=1e-2, rtol=1e-4)
 
 
+def _both(lib_mod, noalloc, logits, labels, want_grad, stream_ptr):
+    """(loss, dlogits) from the allocation-free entry point and from the ordinary one, on one stream."""
+    lib = lib_mod.lib
+    rows, cols = logits.shape
+    loss_a, loss_b = torch.zeros(1, device="cuda"), torch.zeros(1, device="cuda")
+    d_a = torch.empty_like(logits) if want_grad else None
+    d_b = torch.empty_like(logits) if want_grad else None
+    scratch = torch.zeros(lib.tmpi_xent_scratch_bytes(rows), dtype=torch.uint8, device="cuda")
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    st = noalloc(logits.data_ptr(), 6, labels.data_ptr(), rows, cols, loss_a.data_ptr(),
+                 d_a.data_ptr() if want_grad else None, 1.0 / rows, stream_ptr)
+    assert st == 0, lib_mod.last_error()
+    torch.cuda.synchronize()
+    # the driver's own count of free device memory: a cudaMalloc inside the library would show here
+    assert torch.cuda.mem_get_info()[0] == free_before
+    lib_mod.check(lib.tmpi_xent_fwd_bwd(logits.data_ptr(), 6, labels.data_ptr(), rows, cols, loss_b.data_ptr(),
+                                        d_b.data_ptr() if want_grad else None, 1.0 / rows, scratch.data_ptr(), stream_ptr))
+    torch.cuda.synchronize()
+    return loss_a, loss_b, d_a, d_b
+
+
+def test_noalloc_xent_largest_row_count_and_no_gradient():
+    """rows == TMPI_XENT_NOALLOC_MAX_ROWS is accepted; dlogits == NULL computes the loss only."""
+    _lib, noalloc = _symbols()
+    torch.cuda.set_device(0)
+    torch.manual_seed(11)
+    stream = torch.cuda.current_stream().cuda_stream
+    warm = (torch.randn(8, 64, device="cuda")).to(torch.bfloat16)          # first call on the device does the set-up
+    _both(_lib, noalloc, warm, torch.randint(0, 64, (8,), device="cuda"), True, stream)
+    logits = torch.randn(16384, 136, device="cuda").to(torch.bfloat16)
+    labels = torch.randint(0, 136, (16384,), device="cuda")
+    for want_grad in (True, False):
+        la, lb, da, db = _both(_lib, noalloc, logits, labels, want_grad, stream)
+        assert torch.allclose(la, lb, atol=1e-3, rtol=1e-5)
+        if want_grad:
+            assert torch.allclose(da.float(), db.float(), atol=1e-6, rtol=2e-2)
+
+
+def test_noalloc_xent_on_a_side_stream_after_the_default_stream():
+    """Two calls in sequence on one non-default stream, right after a call on the default stream: the
+    shared array is cleared per call on the caller's stream, so each result must match."""
+    _lib, noalloc = _symbols()
+    torch.cuda.set_device(0)
+    torch.manual_seed(13)
+    logits = (torch.randn(512, 777, device="cuda") * 3).to(torch.bfloat16)
+    labels = torch.randint(0, 777, (512,), device="cuda")
+    la, lb, _, _ = _both(_lib, noalloc, logits, labels, True, torch.cuda.current_stream().cuda_stream)
+    assert torch.allclose(la, lb, atol=1e-4, rtol=1e-5)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            la, lb, da, db = _both(_lib, noalloc, logits, labels, True, side.cuda_stream)
+            assert torch.allclose(la, lb, atol=1e-4, rtol=1e-5)
+            assert torch.allclose(da.float(), db.float(), atol=1e-6, rtol=2e-2)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+
+
 def test_noalloc_xent_rejects_too_many_rows():
     _lib, noalloc = _symbols()
     rows = 16384 + 1

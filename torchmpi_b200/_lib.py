@@ -147,6 +147,7 @@ _CUDA_PROTOS = {
     "tmpi_cuda_heap_alloc": (_sz, [_sz, _sz]),
     "tmpi_cuda_heap_reset_allocator": (_i, [_sz]),
     "tmpi_cuda_heap_world": (_i, []),
+    "tmpi_cuda_heap_layout": (_i, [C.POINTER(C.c_size_t), _i]),
     "tmpi_cuda_heap_rank": (_i, []),
     "tmpi_cuda_allreduce": (_i, [_vp, _vp, _sz, _i, _d, _gp, _i, _vp]),
     "tmpi_cuda_allreduce_heap": (_i, [_sz, _sz, _sz, _i, _d, _gp, _i, _vp]),

@@ -25,7 +25,8 @@ template <typename T> __device__ __forceinline__ T* at(char* base, size_t off) {
 __device__ __forceinline__ size_t ceil_div(size_t a, size_t b) { return (a + b - 1) / b; }
 
 // ------------------------------------------------------------------ one-shot (push)
-// Slot of writer w with parity q inside a heap: in_off + (q * kMaxPeers + w) * aux.
+// Slot of writer w (a heap rank) with parity q inside a heap: in_off + (q * world + w) * aux, where the
+// host passes the heap's world size in a.root; a lane's region is 2 * world slots (layout_heap).
 template <typename T, int V>
 __device__ void body_ar_oneshot(const CollArgs& a, int* s_abort) {
   const Peers& P = a.P;
@@ -39,7 +40,7 @@ __device__ void body_ar_oneshot(const CollArgs& a, int* s_abort) {
     Pack<T, V> x = ld_pack<T, V>(in + i * V);
     for (int m = 0; m < P.n; ++m) {
       if (m == P.me) continue;
-      size_t slot = a.in_off + ((size_t)(P.epoch[m] & 1) * kMaxPeers + my_rank) * a.aux;
+      size_t slot = a.in_off + ((size_t)(P.epoch[m] & 1) * (size_t)a.root + my_rank) * a.aux;
       st_pack_peer<T, V>(at<T>(P.base[m], slot) + i * V, x);
     }
   }
@@ -51,7 +52,7 @@ __device__ void body_ar_oneshot(const CollArgs& a, int* s_abort) {
       if (m == P.me) {
         x = ld_pack<T, V>(in + i * V);
       } else {
-        size_t slot = a.in_off + ((size_t)(P.epoch[m] & 1) * kMaxPeers + P.rank_of[m]) * a.aux;
+        size_t slot = a.in_off + ((size_t)(P.epoch[m] & 1) * (size_t)a.root + P.rank_of[m]) * a.aux;
         x = ld_pack_peer<T, V>(at<T>(P.base[P.me], slot) + i * V);
       }
       if (m == 0) acc.set(x); else acc.add(x);

@@ -15,15 +15,17 @@ static int cuda_fail(cudaError_t e, const char* what) {
   return fail(TMPI_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
 }
 
+// SM count of the current device (cached per device; a race writes the same value twice).
 static int sm_count() {
-  static int n = 0;
-  if (!n) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    if (n <= 0) n = 148;
+  static int n[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (!n[dev]) {
+    int v = 0;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+    n[dev] = v;
   }
-  return n;
+  return n[dev];
 }
 
 // ------------------------------------------------------------------ softmax cross-entropy
@@ -347,11 +349,10 @@ static cudaError_t launch_xent(const void* logits, const int64_t* labels, int ro
   constexpr size_t kMaxRowBytes = 112 * 1024;          // two such blocks per SM
   const size_t row_bytes = (size_t)cols * sizeof(T) + 16;
   if (row_bytes <= kMaxRowBytes && ((uintptr_t)logits % sizeof(T)) == 0) {
-    static bool attr_set = false;                        // per instantiation
-    if (!attr_set) {
-      cudaFuncSetAttribute(xent_row_smem_kernel<T, kThreads>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxRowBytes);
-      attr_set = true;
-    }
+    // the attribute belongs to the (function, device) pair; setting it is cheap, so every call does it
+    cudaError_t ae = cudaFuncSetAttribute(xent_row_smem_kernel<T, kThreads>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int)kMaxRowBytes);
+    if (ae != cudaSuccess) return ae;
     xent_row_smem_kernel<T, kThreads><<<rows, kThreads, row_bytes, s>>>((const T*)logits, (const long long*)labels, rows, cols, ld,
                                                                         loss_sum, (T*)dlogits, gscale, row_loss, counter);
   } else {

@@ -48,8 +48,12 @@ Tunable g_tunables[] = {
   {"opt_max_ctas", {32}},                  // CTAs of the fused allreduce+SGD kernel (runs beside backward)
   {"comm_threads", {512}},
   {"num_comm_lanes", {2}},                 // ordered launch lanes (stream + flag set each)
-  {"device_wait_budget_ms", {20000}},      // bounded spin of device flag waits
+  {"device_wait_budget_ms", {2000}},       // bounded spin of device flag waits in steady state
+  {"device_wait_startup_budget_ms", {20000}},  // the same budget during the start-up grace period (ranks enter
+                                           // their first steps seconds apart: module loading, autotuning)
+  {"device_wait_startup_grace_ms", {30000}},   // length of that period, counted from the creation of the heap
   {"host_wait_budget_ms", {10000}},        // the reference's 10 s deadlock heuristic
+  {"handle_wait_budget_ms", {60000}},      // default budget of tmpi_handle_wait (a handle may cover a long task)
   {"bucket_bytes", {32 << 20}},            // gradient bucket size of the engine
   {"heap_bytes", {int64_t(1) << 30}},      // symmetric heap per rank
   {"staging_bytes", {64 << 20}},           // bounce buffer inside the heap for foreign tensors

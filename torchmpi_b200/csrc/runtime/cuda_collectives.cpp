@@ -132,7 +132,8 @@ static int allreduce_any(const void* in, void* out, size_t n, int dtype, double 
   }
   if (g->lane > 1) return fail(TMPI_ERR_INVALID, "lane %d has no bounce buffer", g->lane);
   size_t boff = bounce_off(h, g->lane);
-  if (a == 2 || a == 1) {
+  // use_staged_collectives (the reference's knob for its staged ring): always copy in, reduce in the heap, copy out
+  if ((a == 2 || a == 1) && !tunable("use_staged_collectives")) {
     // two-shot straight from / to the caller's tensors: the bounce region is only scratch
     // (R slots + one result slice per chunk), no copy kernels around the collective
     const int R = g->nmembers;

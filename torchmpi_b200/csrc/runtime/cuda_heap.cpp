@@ -14,6 +14,8 @@
 // to an NVLink multicast object (NVLS).  An *emulated* heap puts all ranks' slabs
 // on one device in one process, for exercising the multi-rank kernels on a
 // single GPU with cooperative launches.
+#include <chrono>
+#include <algorithm>
 #include "cuda_state.h"
 #include <algorithm>
 #include <cstring>
@@ -44,10 +46,24 @@ int layout_heap(CudaHeap& h, size_t arena_bytes) {
   h.arena_off = round_up(h.bounce_off + 2 * h.bounce_bytes, 1 << 16);
   h.arena_cursor = h.arena_off;
   h.total_bytes = round_up(h.arena_off + arena_bytes, (size_t)2 << 20);
+  // the one-shot kernel addresses slot (parity * world + writer) of a lane: the last lane's last slot must
+  // end before the bounce buffers, and a lane's region must end where the next lane's begins
+  if (oneshot_slots_off(h, kHeapLanes - 1) + (size_t)2 * h.world * h.slot_bytes > h.bounce_off)
+    return fail(TMPI_ERR_STATE, "heap layout: one-shot slots overlap the bounce buffers");
   return TMPI_OK;
 }
 
+// Steady-state budget, or the start-up budget while the grace period after the heap's creation runs.
+int64_t device_wait_budget_ms() {
+  int64_t b = tunable("device_wait_budget_ms");
+  const CudaHeap& h = heap();
+  const auto age = std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - h.created).count();
+  if (age < tunable("device_wait_startup_grace_ms")) b = std::max<int64_t>(b, tunable("device_wait_startup_budget_ms"));
+  return b;
+}
+
 int setup_common(CudaHeap& h) {
+  h.created = std::chrono::steady_clock::now();
   CK(cudaHostAlloc((void**)&h.status_host, sizeof(int) * 4 * kHeapLanes, cudaHostAllocMapped));
   memset(h.status_host, 0, sizeof(int) * 4 * kHeapLanes);
   CK(cudaHostGetDevicePointer((void**)&h.status_dev, h.status_host, 0));
@@ -76,7 +92,7 @@ int fill_peers(Peers* P, const int* members, int n, int me, int lane) {
   }
   P->n = n; P->me = me; P->lane = lane;
   P->status = h.status_dev + 4 * lane;
-  P->budget_ns = (unsigned long long)tunable("device_wait_budget_ms") * 1000000ull;
+  P->budget_ns = (unsigned long long)device_wait_budget_ms() * 1000000ull;
   P->mc_base = h.mc_base;
   return TMPI_OK;
 }
@@ -119,8 +135,9 @@ int tmpi_cuda_heap_create(size_t bytes, int rank, int world, int backend) {
     return fail(TMPI_ERR_INVALID, "bad rank/world %d/%d (at most %d ranks per heap)", rank, world, kMaxPeers);
   h.rank = rank; h.world = world; h.backend = backend; h.emulated = false;
   CK(cudaGetDevice(&h.device));
-  layout_heap(h, bytes);
-  int st = setup_common(h);
+  int st = layout_heap(h, bytes);
+  if (st) return st;
+  st = setup_common(h);
   if (st) return st;
   if (backend == 1) {
     st = vmm_create(h);
@@ -143,8 +160,9 @@ int tmpi_cuda_heap_create_emulated(size_t bytes, int world) {
   if (world < 1 || world > 8) return fail(TMPI_ERR_INVALID, "emulation supports 1..8 ranks");
   h.rank = 0; h.world = world; h.backend = 0; h.emulated = true;
   CK(cudaGetDevice(&h.device));
-  layout_heap(h, bytes);
-  int st = setup_common(h);
+  int st = layout_heap(h, bytes);
+  if (st) return st;
+  st = setup_common(h);
   if (st) return st;
   for (int r = 0; r < world; ++r) {
     void* p = nullptr;
@@ -223,6 +241,13 @@ void* tmpi_cuda_heap_base(int peer) {
 void* tmpi_cuda_heap_mc_base(void) { return heap().live ? heap().mc_base : nullptr; }
 size_t tmpi_cuda_heap_capacity(void) { return heap().live ? heap().total_bytes - heap().arena_off : 0; }
 int tmpi_cuda_heap_world(void) { return heap().live ? heap().world : 0; }
+int tmpi_cuda_heap_layout(size_t* out, int n) {
+  const CudaHeap& h = heap();
+  if (!h.live) return fail(TMPI_ERR_STATE, "CUDA heap not created");
+  const size_t v[6] = {h.slots_off, h.slot_bytes, h.bounce_off, h.bounce_bytes, h.arena_off, h.total_bytes};
+  for (int i = 0; i < n && i < 6; ++i) out[i] = v[i];
+  return TMPI_OK;
+}
 int tmpi_cuda_heap_rank(void) { return heap().live ? heap().rank : -1; }
 
 size_t tmpi_cuda_heap_alloc(size_t bytes, size_t align) {

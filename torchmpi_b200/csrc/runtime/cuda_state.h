@@ -2,6 +2,7 @@
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>
+#include <chrono>
 #include <mutex>
 #include <vector>
 #include "common.h"
@@ -39,6 +40,7 @@ struct CudaHeap {
   CUmemGenericAllocationHandle mc_handle = 0;
   bool mc_bound = false;
   int export_fd = -1, mc_export_fd = -1;
+  std::chrono::steady_clock::time_point created{};   // start of the start-up grace period of device waits
   std::mutex mu;                     // arena + epochs of lanes driven from several threads
 };
 
@@ -59,6 +61,7 @@ int fill_peers(Peers* P, const int* members, int n, int me, int lane);
 // Advances the pair epochs of `lane` for these members by `barriers`.
 void advance_epochs(const int* members, int n, int me, int lane, int barriers);
 
+int64_t device_wait_budget_ms();
 int grid_for(size_t work_items, int threads, const char* cap_name = "comm_max_ctas");
 
 // VMM / multicast backend (cuda_vmm.cpp)

@@ -119,7 +119,7 @@ extern "C" {
 int tmpi_handle_wait(uint64_t id, int64_t timeout_ms) {
   auto h = find(id);
   if (!h) return TMPI_OK;  // unknown or already waited: complete
-  int64_t budget = timeout_ms >= 0 ? timeout_ms : tunable("host_wait_budget_ms") * 6;
+  int64_t budget = timeout_ms >= 0 ? timeout_ms : tunable("handle_wait_budget_ms");
   auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(budget);
   if (h->fut.wait_until(deadline) != std::future_status::ready)
     return fail(TMPI_ERR_TIMEOUT, "handle %llu: host task still running after %lld ms (looks like a deadlock)",

@@ -2,8 +2,8 @@
 //
 // ThreadPool: N workers over one mutex + condition-variable queue, the same
 // shape as the pool the reference actually uses (lib/thread_pool-in.h:47-129).
-// OrderedLane: one worker draining a FIFO, used where the launch order of
-// kernels that wait on peer GPUs must be identical on every rank.
+// A pool of one worker drains its queue in order; the runtime uses such pools ("lanes") where the
+// launch order of kernels that wait on peer GPUs must be identical on every rank.
 #pragma once
 #include <condition_variable>
 #include <deque>

@@ -46,6 +46,7 @@ class CudaHeap:
         self._ps = {}
         self._ps_next = 0
         self._keep = []
+        self._layout = None
         if emulated:
             check(lib.tmpi_cuda_heap_create_emulated(heap_bytes, world))
         else:
@@ -122,9 +123,18 @@ class CudaHeap:
 
     def offset_of(self, t: torch.Tensor) -> int:
         off = t.data_ptr() - self.base()
-        if off < 0 or off + t.numel() * t.element_size() > lib.tmpi_cuda_heap_capacity() + (1 << 34):
+        if off < 0 or off + t.numel() * t.element_size() > self.layout()["total_bytes"]:
             return -1
         return off
+
+    def layout(self) -> dict:
+        """Byte offsets of the regions of one rank's mapping (one-shot slots, bounce buffers, arena)."""
+        if self._layout is None:
+            v = (C.c_size_t * 6)()
+            check(lib.tmpi_cuda_heap_layout(v, 6))
+            self._layout = dict(zip(("slots_off", "slot_bytes", "bounce_off", "bounce_bytes", "arena_off", "total_bytes"),
+                                    (int(x) for x in v)))
+        return self._layout
 
     # ---- groups
     def _group(self, members: Sequence[int], lane: int = LANE_SYNC, me: Optional[int] = None):
@@ -176,22 +186,44 @@ class CudaHeap:
             f()
         return None
 
+    def _staged(self, t: torch.Tensor, copy_in: bool):
+        """(tensor to hand to the kernel, finalizer or None): an aligned stand-in for a tensor that
+        ``_needs_staging``, so that the pack width and the grid do not depend on one rank's pointer."""
+        if t.data_ptr() % 16 == 0:          # aligned on this rank: the variant then depends on counts alone
+            return t, None
+        tmp = torch.empty(t.numel(), dtype=t.dtype, device=t.device)
+        if copy_in:
+            tmp.copy_(t.reshape(-1))
+        return tmp, (lambda: t.reshape(-1).copy_(tmp))
+
     def reduce(self, inp, out, root, members, async_op=False):
+        inp, _ = self._staged(inp, True)
+        out, fin = self._staged(out, False)
         g, arr = self._group(members)
         check(lib.tmpi_cuda_reduce(inp.data_ptr(), out.data_ptr(), inp.numel(), dtype_code(inp.dtype), int(root),
                                    C.byref(g), stream_ptr()))
+        if fin is not None:
+            fin()
         return Handle() if async_op else None
 
     def allgatherv(self, inp, out, counts, members):
+        inp, _ = self._staged(inp, True)
+        out, fin = self._staged(out, False)
         g, arr = self._group(members)
         carr = (C.c_int64 * len(counts))(*counts)
         check(lib.tmpi_cuda_allgatherv(inp.data_ptr(), out.data_ptr(), inp.numel(), carr, dtype_code(inp.dtype),
                                        C.byref(g), stream_ptr()))
+        if fin is not None:
+            fin()
 
     def reduce_scatter(self, inp, out, members, scale=1.0):
+        inp, _ = self._staged(inp, True)
+        out, fin = self._staged(out, False)
         g, arr = self._group(members)
         check(lib.tmpi_cuda_reduce_scatter(inp.data_ptr(), out.data_ptr(), out.numel(), dtype_code(inp.dtype),
                                            float(scale), C.byref(g), stream_ptr()))
+        if fin is not None:
+            fin()
 
     def barrier(self, members, stream=None):
         g, arr = self._group(members)
