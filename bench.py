@@ -14,7 +14,9 @@ events and reported as the max over ranks:
                  each step's loss is read back to the host.
 ``--impl reference`` is the reference arm: the Lua/Torch7/MPI reference cannot be installed in this
 image, so it prints the ``unavailable`` line.  ``--impl nccl-pattern`` runs the reference's call
-pattern (one NCCL allreduce per parameter tensor + per-tensor SGD) for comparison.
+pattern (one NCCL allreduce per parameter tensor + per-tensor SGD) for comparison; the default arm
+(``ours``) runs that comparison too, right after its own measurement, and reports it under ``baseline``
+with ``vs_baseline`` = product / comparison (``--no-baseline`` skips it).
 """
 from __future__ import annotations
 
@@ -39,6 +41,7 @@ def parse():
     ap.add_argument("--fused-bn", type=int, default=int(os.environ.get("TORCHMPI_FUSED_BN", "1")))
     ap.add_argument("--bucket-mb", type=int, default=0)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-baseline", action="store_true", help="skip the nccl-pattern comparison arm after the product arm")
     ap.add_argument("--set", action="append", default=[], metavar="NAME=VALUE", help="set a runtime tunable")
     ap.add_argument("--profile-one-step", action="store_true",
                     help="after the warm-up run one step between cudaProfilerStart/Stop and exit (no timing)")
@@ -124,149 +127,175 @@ def main():
     torch.manual_seed(1234)
     torch.backends.cudnn.benchmark = True
 
-    B = args.batch
-    model = (resnet.resnet50(fused_bn=bool(args.fused_bn)) if args.model == "resnet50"
-             else resnet.resnet_tiny(1000, fused_bn=bool(args.fused_bn)))
-    from torchmpi_b200.models import to_bf16_mixed
-    model = to_bf16_mixed(model.to(dev)).to(memory_format=torch.channels_last)
-    nparams = sum(p.numel() for p in model.parameters())
+    def run_arm(impl: str):
+        """One complete measurement (device-timed value, end-to-end value) of one implementation."""
+        B = args.batch
+        fused = bool(args.fused_bn) and impl == "ours"       # the comparison arm runs eager PyTorch layers
+        model = (resnet.resnet50(fused_bn=fused) if args.model == "resnet50" else resnet.resnet_tiny(1000, fused_bn=fused))
+        from torchmpi_b200.models import to_bf16_mixed
+        model = to_bf16_mixed(model.to(dev)).to(memory_format=torch.channels_last)
+        nparams = sum(p.numel() for p in model.parameters())
 
-    # synthetic data, seeded per rank: a few distinct pinned host batches, cycled
-    g = torch.Generator().manual_seed(1000 + rank)
-    nhost = 3
-    host_x = [torch.randn(B, 3, 224, 224, generator=g).to(torch.bfloat16)
-              .contiguous(memory_format=torch.channels_last).pin_memory() for _ in range(nhost)]
-    host_y = [torch.randint(0, 1000, (B,), generator=g).pin_memory() for _ in range(nhost)]
-    dev_x = [x.to(dev, non_blocking=True) for x in host_x]
-    dev_y = [y.to(dev, non_blocking=True) for y in host_y]
-    h2d_bytes = host_x[0].numel() * host_x[0].element_size() + host_y[0].numel() * host_y[0].element_size()
+        # synthetic data, seeded per rank: a few distinct pinned host batches, cycled
+        g = torch.Generator().manual_seed(1000 + rank)
+        nhost = 3
+        host_x = [torch.randn(B, 3, 224, 224, generator=g).to(torch.bfloat16)
+                  .contiguous(memory_format=torch.channels_last).pin_memory() for _ in range(nhost)]
+        host_y = [torch.randint(0, 1000, (B,), generator=g).pin_memory() for _ in range(nhost)]
+        dev_x = [x.to(dev, non_blocking=True) for x in host_x]
+        dev_y = [y.to(dev, non_blocking=True) for y in host_y]
+        h2d_bytes = host_x[0].numel() * host_x[0].element_size() + host_y[0].numel() * host_y[0].element_size()
 
-    if args.impl == "ours":
-        engine = AllReduceSGDEngine(usegpu=True, devicesync=False, fused=True, momentum=0.9,
-                                    gradient_scale=1.0 / world)
-        criterion = xent.CrossEntropyLoss()
-    else:
-        engine = AllReduceSGDEngine(usegpu=True, devicesync=False, fused=False, momentum=0.9,
-                                    gradient_scale=1.0 / world)
-        criterion = torch.nn.CrossEntropyLoss()
-        mpi.selector.configure()
-        for node in ("singlenode", "multinode"):
-            for mode in ("sync", "async"):
-                mpi.selector.collective_selector["gpu"][node][mode]["allreduceTensor"] = "nccl"
-                mpi.selector.collective_selector["gpu"][node][mode]["broadcastTensor"] = "nccl"
-    state = {"network": model, "criterion": criterion, "iterator": None, "lr": 0.1, "lrcriterion": 0.1,
-             "maxepoch": 1, "sample": None, "epoch": 0, "t": 0, "training": True}
-    engine._setup(model, criterion)
-    model.train()
+        if impl == "ours":
+            engine = AllReduceSGDEngine(usegpu=True, devicesync=False, fused=True, momentum=0.9,
+                                        gradient_scale=1.0 / world)
+            criterion = xent.CrossEntropyLoss()
+        else:
+            engine = AllReduceSGDEngine(usegpu=True, devicesync=False, fused=False, momentum=0.9,
+                                        gradient_scale=1.0 / world)
+            criterion = torch.nn.CrossEntropyLoss()
+            mpi.selector.configure()
+            for node in ("singlenode", "multinode"):
+                for mode in ("sync", "async"):
+                    mpi.selector.collective_selector["gpu"][node][mode]["allreduceTensor"] = "nccl"
+                    mpi.selector.collective_selector["gpu"][node][mode]["broadcastTensor"] = "nccl"
+        state = {"network": model, "criterion": criterion, "iterator": None, "lr": 0.1, "lrcriterion": 0.1,
+                 "maxepoch": 1, "sample": None, "epoch": 0, "t": 0, "training": True}
+        engine._setup(model, criterion)
+        model.train()
 
-    def launches() -> int:
-        n = engine._opt.launches if engine._opt is not None else 0
-        n += getattr(xent, "launch_count", 0)
-        try:
-            from torchmpi_b200.ops import bn_relu, pool, stem_conv
-            n += bn_relu.launch_count + pool.launch_count + stem_conv.launch_count
-        except ImportError:
-            pass
-        return n
+        def launches() -> int:
+            n = engine._opt.launches if engine._opt is not None else 0
+            n += getattr(xent, "launch_count", 0)
+            try:
+                from torchmpi_b200.ops import bn_relu, pool, stem_conv, conv, gemm
+                n += bn_relu.launch_count + pool.launch_count + stem_conv.launch_count + conv.launch_count + gemm.launch_count
+            except ImportError:
+                pass
+            return n
 
-    def sync_all():
-        torch.cuda.synchronize()
-        mpi.barrier()
-        torch.cuda.synchronize()
+        def sync_all():
+            torch.cuda.synchronize()
+            mpi.barrier()
+            torch.cuda.synchronize()
 
-    def timed(step_fn, steps):
-        sync_all()
-        sampler = ClockSampler(dev.index)
-        sampler.start()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        l0 = launches()
-        e0.record()
-        for i in range(steps):
-            step_fn(i)
-        e1.record()
-        sync_all()
-        clocks = sampler.stop()
-        ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64)
-        if world > 1:
-            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return ms.item(), clocks, launches() - l0
+        def timed(step_fn, steps):
+            sync_all()
+            sampler = ClockSampler(dev.index)
+            sampler.start()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            l0 = launches()
+            e0.record()
+            for i in range(steps):
+                step_fn(i)
+            e1.record()
+            sync_all()
+            clocks = sampler.stop()
+            ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64)
+            if world > 1:
+                dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+            return ms.item(), clocks, launches() - l0
 
-    # ---- device-resident input
-    def step_dev(i):
-        engine.train_step(state, {"input": dev_x[i % nhost], "target": dev_y[i % nhost]})
+        # ---- device-resident input
+        def step_dev(i):
+            engine.train_step(state, {"input": dev_x[i % nhost], "target": dev_y[i % nhost]})
 
-    for i in range(args.warmup):
-        step_dev(i)
-    if args.profile_one_step:
-        # for `ncu --profile-from-start off`: exactly one training step lies inside the profiler range
-        torch.cuda.synchronize()
-        torch.cuda.profiler.start()
-        step_dev(0)
-        torch.cuda.synchronize()
-        torch.cuda.profiler.stop()
-        mpi.stop()
-        return 0
-    ms, clocks, nlaunch = timed(step_dev, args.steps)
-    value = world * B * args.steps / (ms / 1e3)
+        for i in range(args.warmup):
+            step_dev(i)
+        if args.profile_one_step:
+            # for `ncu --profile-from-start off`: exactly one training step lies inside the profiler range
+            torch.cuda.synchronize()
+            torch.cuda.profiler.start()
+            step_dev(0)
+            torch.cuda.synchronize()
+            torch.cuda.profiler.stop()
+            mpi.stop()
+            sys.exit(0)
+        ms, clocks, nlaunch = timed(step_dev, args.steps)
+        value = world * B * args.steps / (ms / 1e3)
 
-    # ---- end to end: pinned host batch -> device (prefetched), loss -> host, every step
-    e2e = None
-    if not args.no_e2e:
-        copy_stream = torch.cuda.Stream()
-        bufs = [(torch.empty_like(dev_x[0]), torch.empty_like(dev_y[0])) for _ in range(2)]
-        ready = [torch.cuda.Event() for _ in range(2)]
-        consumed = [torch.cuda.Event() for _ in range(2)]
-        loss_host = torch.zeros(2, dtype=torch.float32).pin_memory()
-        loss_evt = [torch.cuda.Event() for _ in range(2)]
-        losses = []
+        # ---- end to end: pinned host batch -> device (prefetched), loss -> host, every step
+        e2e = None
+        if not args.no_e2e:
+            copy_stream = torch.cuda.Stream()
+            bufs = [(torch.empty_like(dev_x[0]), torch.empty_like(dev_y[0])) for _ in range(2)]
+            ready = [torch.cuda.Event() for _ in range(2)]
+            consumed = [torch.cuda.Event() for _ in range(2)]
+            loss_host = torch.zeros(2, dtype=torch.float32).pin_memory()
+            loss_evt = [torch.cuda.Event() for _ in range(2)]
+            losses = []
 
-        def prefetch(i):
-            k = i % 2
-            with torch.cuda.stream(copy_stream):
-                copy_stream.wait_event(consumed[k])
-                bufs[k][0].copy_(host_x[i % nhost], non_blocking=True)
-                bufs[k][1].copy_(host_y[i % nhost], non_blocking=True)
-                ready[k].record(copy_stream)
+            def prefetch(i):
+                k = i % 2
+                with torch.cuda.stream(copy_stream):
+                    copy_stream.wait_event(consumed[k])
+                    bufs[k][0].copy_(host_x[i % nhost], non_blocking=True)
+                    bufs[k][1].copy_(host_y[i % nhost], non_blocking=True)
+                    ready[k].record(copy_stream)
 
-        def step_e2e(i):
-            k = i % 2
-            if i == 0:
-                prefetch(0)
-            prefetch(i + 1)                      # next batch travels while this one trains
-            torch.cuda.current_stream().wait_event(ready[k])
-            loss = engine.train_step(state, {"input": bufs[k][0], "target": bufs[k][1]})
-            consumed[k].record()
-            if i >= 1:                           # read the previous step's loss: the host never stalls on this step
-                loss_evt[(i - 1) % 2].synchronize()
-                losses.append(float(loss_host[(i - 1) % 2]))
-            loss_host[k:k + 1].copy_(loss.detach().float().reshape(1), non_blocking=True)
-            loss_evt[k].record()
+            def step_e2e(i):
+                k = i % 2
+                if i == 0:
+                    prefetch(0)
+                prefetch(i + 1)                      # next batch travels while this one trains
+                torch.cuda.current_stream().wait_event(ready[k])
+                loss = engine.train_step(state, {"input": bufs[k][0], "target": bufs[k][1]})
+                consumed[k].record()
+                if i >= 1:                           # read the previous step's loss: the host never stalls on this step
+                    loss_evt[(i - 1) % 2].synchronize()
+                    losses.append(float(loss_host[(i - 1) % 2]))
+                loss_host[k:k + 1].copy_(loss.detach().float().reshape(1), non_blocking=True)
+                loss_evt[k].record()
 
-        for k in range(2):
-            consumed[k].record()
-        for i in range(max(3, args.warmup // 2)):
-            step_e2e(i)
-        torch.cuda.synchronize()
-        losses.clear()
-        ms_e, _, _ = timed(step_e2e, args.steps)
-        loss_evt[(args.steps - 1) % 2].synchronize()
-        losses.append(float(loss_host[(args.steps - 1) % 2]))
-        e2e = {"value": world * B * args.steps / (ms_e / 1e3), "unit": "images/s", "ms_per_step": ms_e / args.steps,
-               "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 4, "last_loss": losses[-1]}
+            for k in range(2):
+                consumed[k].record()
+            for i in range(max(3, args.warmup // 2)):
+                step_e2e(i)
+            torch.cuda.synchronize()
+            losses.clear()
+            ms_e, _, _ = timed(step_e2e, args.steps)
+            loss_evt[(args.steps - 1) % 2].synchronize()
+            losses.append(float(loss_host[(args.steps - 1) % 2]))
+            e2e = {"value": world * B * args.steps / (ms_e / 1e3), "unit": "images/s", "ms_per_step": ms_e / args.steps,
+                   "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 4, "last_loss": losses[-1]}
 
-    if engine._opt is not None:
-        engine._opt.check()
-    out = {"metric": "ResNet-50 training throughput (images/s), data-parallel sync SGD via AllReduceSGDEngine",
-           "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-           "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-           "dtype": "bf16", "data": "synthetic (N(0,1) images, uniform labels, seed+rank), random-init weights",
-           "impl": args.impl,
-           "config": {"model": args.model, "params": nparams, "global_batch": B * world, "per_gpu_batch": B,
-                      "image": "3x224x224", "optimizer": "SGD momentum 0.9, fp32 master weights",
-                      "parallelism": f"dp{world}", "memory_format": "channels_last",
-                      "fused_bn": bool(args.fused_bn) and args.impl == "ours",
-                      "l2": "per-step working set (activations of 256 images) far exceeds the 126 MB L2"},
-           "clocks": clocks, "e2e": e2e, "gpu_launches": nlaunch}
+        if engine._opt is not None:
+            engine._opt.check()
+        out = {"metric": "ResNet-50 training throughput (images/s), data-parallel sync SGD via AllReduceSGDEngine",
+               "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+               "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+               "dtype": "bf16", "data": "synthetic (N(0,1) images, uniform labels, seed+rank), random-init weights",
+               "impl": impl,
+               "config": {"model": args.model, "params": nparams, "global_batch": B * world, "per_gpu_batch": B,
+                          "image": "3x224x224", "optimizer": "SGD momentum 0.9, fp32 master weights",
+                          "parallelism": f"dp{world}", "memory_format": "channels_last",
+                          "fused_bn": bool(args.fused_bn) and impl == "ours",
+                          "l2": "per-step working set (activations of 256 images) far exceeds the 126 MB L2"},
+               "clocks": clocks, "e2e": e2e, "gpu_launches": nlaunch}
+        return out, engine
+
+    out, engine = run_arm(args.impl)
+    if args.impl == "ours" and not args.no_baseline and not args.profile_one_step:
+        # The comparison arm, measured in the same process group on the same GPUs right after the product arm: this
+        # repository's restatement of the reference's training pattern - one NCCL allreduce per parameter tensor
+        # issued from a per-parameter hook (torchmpi/nn.lua:49-56,112-242, lib/collectives_cuda.cpp:1046-1052), eager
+        # PyTorch layers, a separate per-tensor SGD step (torchmpi/engine/sgdengine.lua:126-147).  It is NOT the
+        # reference itself (which cannot be installed here; see --impl reference).
+        if engine._opt is not None:
+            engine._opt.remove_hooks()
+        del engine
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        base, engine_b = run_arm("nccl-pattern")
+        out["baseline"] = {"impl": "nccl-pattern", "what": "reference call pattern restated with this box's NCCL; not the reference",
+                           "value": base["value"], "ms_per_step": base["ms_per_step"],
+                           "e2e": base["e2e"]["value"] if base["e2e"] else None,
+                           "ratio": out["value"] / base["value"],
+                           "e2e_ratio": (out["e2e"]["value"] / base["e2e"]["value"]) if (out["e2e"] and base["e2e"]) else None,
+                           "clocks": base["clocks"]}
+        out["vs_baseline"] = out["baseline"]["ratio"]
+        del engine_b
     if rank == 0:
         print(json.dumps(out))
     mpi.stop()

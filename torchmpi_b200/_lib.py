@@ -185,6 +185,7 @@ _CUDA_PROTOS = {
     "tmpi_bn_relu_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _f, _f, _i, _i, _i, _vp, _vp, _vp]),
     "tmpi_bn_relu_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _vp, _vp, _vp]),
     "tmpi_bn_scratch_bytes": (_sz, [_i]),
+    "tmpi_bn_relu_fwd_partials": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _f, _f, _i, _i, _vp, _vp, _i, _vp]),
     "tmpi_bn_relu_pool_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _f, _i, _i, _vp, _vp]),
     "tmpi_bn_relu_pool_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp]),
     "tmpi_stem_im2col": (_i, [_vp, _vp, _i, _i, _i, _i, _vp]),
@@ -194,6 +195,14 @@ _CUDA_PROTOS = {
     "tmpi_gemm_bf16": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "tmpi_gemm_bf16_ex": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, _i, _vp]),
     "tmpi_gemm_status": (_i, []),
+    "tmpi_conv_max_ctas": (_i, []),
+    "tmpi_conv_fwd": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _ip, _vp]),
+    "tmpi_conv_dgrad": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp]),
+    "tmpi_conv_wgrad_workspace_bytes": (_sz, [_i, _i, _i, _i, _i, _i, _i, _i, _i]),
+    "tmpi_conv_wgrad": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _sz, _i, _vp]),
+    "tmpi_conv_status": (_i, []),
+    "tmpi_gemm_tn_splitk_workspace_bytes": (_sz, [_i, _i, _i64]),
+    "tmpi_gemm_bf16_tn_splitk": (_i, [_vp, _vp, _vp, _i, _i, _i64, _i64, _i64, _vp, _sz, _i, _vp]),
 }
 
 

@@ -258,6 +258,29 @@ int tmpi_bn_relu_bwd(const void* x, const void* y, const void* dy, void* dx, voi
                      float* dgamma, float* dbeta, int64_t rows, int channels, int relu, int dtype,
                      const void* mask_bits, void* scratch, void* stream);
 size_t tmpi_bn_scratch_bytes(int channels);
+// training forward of the same stage when the producer of x already left `partial_rows` rows of partial
+// sums, [row][2][channels] floats, in `partials` (the statistics pass is skipped)
+int tmpi_bn_relu_fwd_partials(const void* x, const void* residual, void* y, const float* gamma, const float* beta,
+                              float* running_mean, float* running_var, float* save_mean, float* save_invstd, int64_t rows,
+                              int channels, float eps, float momentum, int relu, int dtype, void* mask_bits,
+                              void* partials, int partial_rows, void* stream);
+
+// ---------------------------------------------------------------- convolutions as implicit GEMMs (conv_gemm.cu)
+// bf16, channels-last, dense; x [N, H, W, Cin], w [Cout, R, S, Cin] (a channels-last Conv2d weight as it lies),
+// y [N, Ho, Wo, Cout]; Cin and Cout multiples of 64, square filters.
+int tmpi_conv_max_ctas(void);
+int tmpi_conv_fwd(const void* x, const void* w, void* y, int N, int H, int W, int Cin, int Cout, int R, int S, int stride,
+                  int pad, float* stats, int* stat_rows, void* stream);
+int tmpi_conv_dgrad(const void* dy, const void* w, void* dx, const void* add, int N, int H, int W, int Cin, int Cout, int R,
+                    int S, int stride, int pad, void* stream);
+size_t tmpi_conv_wgrad_workspace_bytes(int N, int H, int W, int Cin, int Cout, int R, int S, int stride, int pad);
+int tmpi_conv_wgrad(const void* dy, const void* x, void* dw, int N, int H, int W, int Cin, int Cout, int R, int S,
+                    int stride, int pad, void* workspace, size_t workspace_bytes, int accumulate, void* stream);
+int tmpi_conv_status(void);
+// C[M, N] (+)= A^T B for A [K, M], B [K, N] with a long K and a small output (split over K; same kernel family)
+size_t tmpi_gemm_tn_splitk_workspace_bytes(int M, int N, int64_t K);
+int tmpi_gemm_bf16_tn_splitk(const void* A, const void* B, void* C, int M, int N, int64_t K, int64_t lda, int64_t ldb,
+                             void* workspace, size_t workspace_bytes, int accumulate, void* stream);
 // batch-norm + ReLU + max-pool (3x3, stride 2, pad 1) as one stage; y, idx: [N, (H-1)/2+1, (W-1)/2+1, C]
 int tmpi_bn_relu_pool_fwd(const void* x, void* y, void* idx, const float* gamma, const float* beta,
                           float* running_mean, float* running_var, float* save_mean, float* save_invstd,

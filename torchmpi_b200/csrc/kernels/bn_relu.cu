@@ -271,7 +271,7 @@ static int bn_check(int64_t rows, int C, int V) {
 template <typename T>
 static int bn_fwd_t(const void* x, const void* res, void* y, const float* gamma, const float* beta, float* rmean,
                     float* rvar, float* smean, float* sinv, int64_t rows, int C, float eps, float momentum, int relu,
-                    int training, void* bits, void* scratch, cudaStream_t s) {
+                    int training, void* bits, void* scratch, cudaStream_t s, int given_rows = 0) {
   constexpr int V = 16 / sizeof(T);
   int st = bn_check(rows, C, V);
   if (st) return st;
@@ -279,6 +279,9 @@ static int bn_fwd_t(const void* x, const void* res, void* y, const float* gamma,
   int grid = bn_grid(nvec);
   const int reverse = tunable("bn_reverse_stats") != 0;
   if (training) {
+    // given_rows > 0: the producer of x (a convolution epilogue) has left that many rows of partial sums in scratch
+    if (given_rows > 0) grid = given_rows;
+    else
     bn_reduce_kernel<T, V, false, false><<<grid, kBnThreads, 0, s>>>((const T*)x, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr,
                                                                      nullptr, nvec, C, 0, reverse, (float*)scratch);
     float m = (float)rows;
@@ -645,6 +648,19 @@ int tmpi_bn_relu_fwd(const void* x, const void* residual, void* y, const float* 
                                           rows, channels, eps, momentum, relu, training, mask_bits, scratch, s);
   }
   return fail(TMPI_ERR_UNSUPPORTED, "bn: dtype %d", dtype);
+}
+
+// Training forward whose statistics pass has been done already: `partials` holds `partial_rows` (<= 592) rows of
+// per-channel partial sums and sums of squares of x, [row][2][channels] floats, as tmpi_conv_fwd writes them.
+int tmpi_bn_relu_fwd_partials(const void* x, const void* residual, void* y, const float* gamma, const float* beta,
+                              float* running_mean, float* running_var, float* save_mean, float* save_invstd, int64_t rows,
+                              int channels, float eps, float momentum, int relu, int dtype, void* mask_bits,
+                              void* partials, int partial_rows, void* stream) {
+  cudaStream_t s = (cudaStream_t)stream;
+  if (partial_rows < 1 || partial_rows > kBnMaxGrid) return fail(TMPI_ERR_INVALID, "bn: 1..%d rows of partial sums", kBnMaxGrid);
+  if (dtype != TMPI_BF16) return fail(TMPI_ERR_UNSUPPORTED, "bn from partial sums: bf16 only");
+  return bn_fwd_t<__nv_bfloat16>(x, residual, y, gamma, beta, running_mean, running_var, save_mean, save_invstd, rows, channels,
+                                 eps, momentum, relu, 1, mask_bits, partials, s, partial_rows);
 }
 
 // The ReLU mask comes from mask_bits when given (see tmpi_bn_relu_fwd), else from y, else - ReLU layers

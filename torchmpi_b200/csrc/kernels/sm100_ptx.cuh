@@ -68,6 +68,17 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
       ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
 }
 
+// 4-D im2col-mode load (tensor [N, H, W, C], C innermost): `pixels` consecutive filter positions starting at
+// base coordinates (w, h, n) - walked along w, then h, then n, inside the bounding box and with the
+// traversal strides of the tensor map - each read at the tap offset (off_w, off_h); positions outside
+// the image give zeros.  The box lands as [pixel][channel] rows, like a 2-D tile.  No multicast.
+__device__ __forceinline__ void tma_load_im2col_4d(void* smem_dst, const CUtensorMap* map, int c, int w, int h, int n,
+                                                   unsigned short off_w, unsigned short off_h, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c), "r"(w), "r"(h), "r"(n), "h"(off_w), "h"(off_h) : "memory");
+}
+
 // ---------------------------------------------------------------- tensor memory + tcgen05
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t ncols) {   // whole warp
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)), "r"(ncols) : "memory");

@@ -42,11 +42,14 @@ class Bottleneck(nn.Module):
         self.downsample = downsample
 
     def forward(self, x):
-        identity = x if self.downsample is None else self.downsample(x)
+        identity = x if (self.downsample is None or self.fused) else self.downsample(x)
         if self.fused:
-            out = self.bn1(self.conv1(x))
-            out = self.bn2(self.conv2(out))
-            return self.bn3(self.conv3(out), residual=identity)
+            from ..ops.conv import conv_bn
+            if self.downsample is not None:
+                identity = conv_bn(self.downsample[0], self.downsample[1], x)
+            out = conv_bn(self.conv1, self.bn1, x)
+            out = conv_bn(self.conv2, self.bn2, out)
+            return conv_bn(self.conv3, self.bn3, out, residual=identity)
         out = torch.relu(self.bn1(self.conv1(x)))
         out = torch.relu(self.bn2(self.conv2(out)))
         out = self.bn3(self.conv3(out))
@@ -75,7 +78,11 @@ class ResNet(nn.Module):
         self.layer3 = self._make_layer(width * 4, layers[2], 2)
         self.layer4 = self._make_layer(width * 8, layers[3], 2)
         self.avgpool = nn.AdaptiveAvgPool2d(1)
-        self.fc = nn.Linear(width * 8 * 4, num_classes)
+        if fused_bn:
+            from ..ops.gemm import Linear
+            self.fc = Linear(width * 8 * 4, num_classes)     # same parameters as nn.Linear; tcgen05 GEMMs where the shape allows
+        else:
+            self.fc = nn.Linear(width * 8 * 4, num_classes)
         for m in self.modules():
             if isinstance(m, nn.Conv2d):
                 nn.init.kaiming_normal_(m.weight, mode="fan_out", nonlinearity="relu")

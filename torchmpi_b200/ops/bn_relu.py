@@ -42,7 +42,9 @@ def supported(x: torch.Tensor) -> bool:
 
 class _BnReluFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, residual, gamma, beta, running_mean, running_var, eps, momentum, relu, training):
+    def forward(ctx, x, residual, gamma, beta, running_mean, running_var, eps, momentum, relu, training, partial_rows=0):
+        """``partial_rows > 0``: the producer of ``x`` (a convolution of ``ops.conv``) has already left that many
+        rows of partial sums in this stream's scratch buffer, so the statistics pass is skipped."""
         global launch_count
         x = x.contiguous(memory_format=torch.channels_last)
         if residual is not None:
@@ -60,15 +62,26 @@ class _BnReluFn(torch.autograd.Function):
         bits = None
         if relu and residual is not None and any(ctx.needs_input_grad):
             bits = torch.empty(rows * C // (16 // x.element_size()), dtype=torch.uint8, device=x.device)
-        check(lib.tmpi_bn_relu_fwd(
-            x.data_ptr(), residual.data_ptr() if residual is not None else None, y.data_ptr(),
-            gamma.data_ptr(), beta.data_ptr(),
-            running_mean.data_ptr() if (training and running_mean is not None) else None,
-            running_var.data_ptr() if (training and running_var is not None) else None,
-            mean.data_ptr(), invstd.data_ptr(), rows, C, eps, momentum, int(relu), int(training),
-            dtype_code(x.dtype), bits.data_ptr() if bits is not None else None,
-            _scratch_for(x.device, C).data_ptr(), stream_ptr()))
-        launch_count += 3 if training else 1
+        if training and partial_rows > 0:
+            check(lib.tmpi_bn_relu_fwd_partials(
+                x.data_ptr(), residual.data_ptr() if residual is not None else None, y.data_ptr(),
+                gamma.data_ptr(), beta.data_ptr(),
+                running_mean.data_ptr() if running_mean is not None else None,
+                running_var.data_ptr() if running_var is not None else None,
+                mean.data_ptr(), invstd.data_ptr(), rows, C, eps, momentum, int(relu),
+                dtype_code(x.dtype), bits.data_ptr() if bits is not None else None,
+                _scratch_for(x.device, C).data_ptr(), int(partial_rows), stream_ptr()))
+            launch_count += 2
+        else:
+            check(lib.tmpi_bn_relu_fwd(
+                x.data_ptr(), residual.data_ptr() if residual is not None else None, y.data_ptr(),
+                gamma.data_ptr(), beta.data_ptr(),
+                running_mean.data_ptr() if (training and running_mean is not None) else None,
+                running_var.data_ptr() if (training and running_var is not None) else None,
+                mean.data_ptr(), invstd.data_ptr(), rows, C, eps, momentum, int(relu), int(training),
+                dtype_code(x.dtype), bits.data_ptr() if bits is not None else None,
+                _scratch_for(x.device, C).data_ptr(), stream_ptr()))
+            launch_count += 3 if training else 1
         # a ReLU layer without a residual rebuilds its mask from x in backward; neither kind reads y again
         ctx.mask_from_x = relu and residual is None
         keep_y = relu and not ctx.mask_from_x and bits is None
@@ -92,7 +105,7 @@ class _BnReluFn(torch.autograd.Function):
             N * H * W, C, int(ctx.relu), dtype_code(x.dtype), bits.data_ptr() if bits is not None else None,
             _scratch_for(x.device, C).data_ptr(), stream_ptr()))
         launch_count += 3
-        return dx, dres, dgamma, dbeta, None, None, None, None, None, None
+        return dx, dres, dgamma, dbeta, None, None, None, None, None, None, None
 
 
 class _BnReluPoolFn(torch.autograd.Function):
@@ -176,11 +189,11 @@ class FusedBatchNormReLU(nn.BatchNorm2d):
         super().__init__(num_features, eps=eps, momentum=momentum)
         self.relu = relu
 
-    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None, partial_rows: int = 0) -> torch.Tensor:
         if supported(x) and self.weight.dtype == torch.float32:
             # num_batches_tracked is only needed for momentum=None (cumulative average), not supported here
             return _BnReluFn.apply(x, residual, self.weight, self.bias, self.running_mean, self.running_var,
-                                   self.eps, self.momentum, self.relu, self.training)
+                                   self.eps, self.momentum, self.relu, self.training, partial_rows)
         out = F.batch_norm(x, self.running_mean, self.running_var, self.weight, self.bias, self.training,
                            self.momentum, self.eps)
         if residual is not None:

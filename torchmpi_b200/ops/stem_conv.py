@@ -5,7 +5,8 @@
 bf16 CUDA input, forward writes the patch matrix ``col [N*OH*OW, 160]`` with one kernel
 (csrc/kernels/im2col.cu) and multiplies it with the ``[C, 160]`` weight matrix on the tensor cores;
 the result is the channels-last output as it lies.  Backward needs only the weight gradient (the
-image has none): ``dW = dY^T col``, a library GEMM over the saved patch matrix.  Other inputs take
+image has none): ``dW = dY^T col``, a split-K product on the same tensor-core kernel family over the saved
+patch matrix.  Other inputs take
 ``F.conv2d``.
 """
 from __future__ import annotations
@@ -52,7 +53,8 @@ class _StemConvFn(torch.autograd.Function):
         (col,) = ctx.saved_tensors
         Cout = ctx.wshape[0]
         dy2d = dy.contiguous(memory_format=torch.channels_last).permute(0, 2, 3, 1).reshape(-1, Cout)
-        dw2d = torch.matmul(dy2d.t(), col)                                   # [Cout, 160]; plain library GEMM
+        from .conv import matmul_tn_splitk
+        dw2d = matmul_tn_splitk(dy2d, col)                                   # [Cout, 160]: split over the 3.2 M patch rows
         dw = dw2d[:, :PATCH].reshape(Cout, 7, 7, 3).permute(0, 3, 1, 2)
         return None, dw
 
