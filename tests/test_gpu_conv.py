@@ -147,3 +147,65 @@ def test_conv_bn_fused_statistics_match_separate_pass():
     yb.backward(g)
     assert torch.allclose(xa.grad.float(), xb.grad.float(), atol=2e-2, rtol=2e-2)
     assert torch.allclose(wa.float(), c.weight.grad.float(), atol=2e-2, rtol=2e-2)
+
+
+def test_bottleneck_with_fork_and_direct_gradients_matches_eager():
+    """A fused bottleneck block (convolutions on the implicit-GEMM kernel, statistics in the epilogue, the two
+    gradients into the block input summed inside a kernel, parameter gradients added in place into flat buckets)
+    against the same block run with eager PyTorch layers in fp32."""
+    from torchmpi_b200.models.resnet import Bottleneck, _bn
+    from torchmpi_b200.parallel.flat_buckets import FlatBuckets
+    import torch.nn as nn
+    torch.manual_seed(3)
+    for inplanes, planes, stride in ((256, 64, 1), (64, 64, 1), (256, 128, 2)):
+        down_f = down_e = None
+        if stride != 1 or inplanes != planes * 4:
+            down_f = nn.Sequential(nn.Conv2d(inplanes, planes * 4, 1, stride=stride, bias=False), _bn(planes * 4, True, relu=False))
+            down_e = nn.Sequential(nn.Conv2d(inplanes, planes * 4, 1, stride=stride, bias=False), _bn(planes * 4, False, relu=False))
+        fused = Bottleneck(inplanes, planes, stride, down_f, fused_bn=True).cuda()
+        eager = Bottleneck(inplanes, planes, stride, down_e, fused_bn=False).cuda()
+        with torch.no_grad():
+            for m in fused.modules():
+                if isinstance(m, nn.BatchNorm2d):
+                    m.weight.uniform_(0.5, 1.5); m.bias.uniform_(-0.3, 0.3)
+        eager.load_state_dict(fused.state_dict())
+        for m in fused.modules():                       # bf16 convolutions, fp32 batch-norm: the mixed layout of the benchmark
+            if isinstance(m, nn.Conv2d):
+                m.to(torch.bfloat16)
+        fused = fused.to(memory_format=torch.channels_last)
+        for p, q in zip(fused.parameters(), eager.parameters()):       # the eager copy sees the rounded weights
+            q.data.copy_(p.data.float())
+        fb = FlatBuckets(list(fused.parameters()), bucket_bytes=1 << 30)
+        ready = []
+        fb.register_ready_hooks(lambda g: ready.append(g.data_ptr()))
+        x = torch.randn(4, inplanes, 14, 14, device="cuda").to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+        xf = x.clone().requires_grad_(True)
+        xe = x.float().requires_grad_(True)
+        yf = fused(xf * 1.0)              # a non-leaf input, as inside a network
+        ye = eager(xe * 1.0)
+        g = torch.randn_like(ye)
+        yf.backward(g.to(torch.bfloat16))
+        ye.backward(g)
+        torch.cuda.synchronize()
+        # bf16 activations against fp32: a ReLU mask that flips near zero moves single elements a lot, so the
+        # yardstick is the relative error in the 2-norm, not the largest element
+        def rel2(a, b):
+            return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+        tag = f"{inplanes}/{planes}/{stride}"
+        assert rel2(yf, ye) < 2e-2, (tag, "output", rel2(yf, ye))
+        assert rel2(xf.grad, xe.grad) < 0.12, (tag, "input gradient", rel2(xf.grad, xe.grad))
+        assert len(ready) == len(fb.buckets), "every bucket reports its gradients exactly once"
+        for (n, p), q in zip(fused.named_parameters(), eager.parameters()):
+            assert rel2(p.grad, q.grad) < 0.15, (tag, n, rel2(p.grad, q.grad))
+        # the same block without the in-kernel gradient sum and without in-place parameter gradients: same numbers
+        fb.remove_hooks()
+        from torchmpi_b200 import config
+        config.set("grad_fork", 0)
+        ref = {n: p.grad.clone() for n, p in fused.named_parameters()}
+        fb.zero_grad()
+        xg = x.clone().requires_grad_(True)
+        fused(xg * 1.0).backward(g.to(torch.bfloat16))
+        config.set("grad_fork", 1)
+        assert rel2(xg.grad, xf.grad) < 1e-2, (tag, "fork on/off", rel2(xg.grad, xf.grad))
+        for n, p in fused.named_parameters():
+            assert rel2(p.grad, ref[n]) < 1e-2, (tag, n, "direct/returned gradient", rel2(p.grad, ref[n]))

@@ -257,6 +257,10 @@ int tmpi_bn_relu_bwd(const void* x, const void* y, const void* dy, void* dx, voi
                      const float* gamma, const float* beta, const float* save_mean, const float* save_invstd,
                      float* dgamma, float* dbeta, int64_t rows, int channels, int relu, int dtype,
                      const void* mask_bits, void* scratch, void* stream);
+int tmpi_bn_relu_bwd_acc(const void* x, const void* y, const void* dy, void* dx, void* dresidual, const float* gamma,
+                         const float* beta, const float* save_mean, const float* save_invstd, float* dgamma, float* dbeta,
+                         int64_t rows, int channels, int relu, int dtype, const void* mask_bits, void* scratch,
+                         float* acc_gamma, float* acc_beta, void* stream);
 size_t tmpi_bn_scratch_bytes(int channels);
 // training forward of the same stage when the producer of x already left `partial_rows` rows of partial
 // sums, [row][2][channels] floats, in `partials` (the statistics pass is skipped)

@@ -172,13 +172,19 @@ __global__ void __launch_bounds__(1024) bn_finalize_fwd_kernel(
   if (rvar) rvar[c] = (1.f - momentum) * rvar[c] + momentum * var * m_corr;   // unbiased, like torch
 }
 
+// acc_gamma / acc_beta (nullable): the parameters' gradient buffers, to which the sums are added as well (the
+// caller then needs no separate accumulation kernel)
 __global__ void __launch_bounds__(1024) bn_finalize_bwd_kernel(const float* __restrict__ partial, int nblocks, int C,
-                                                               float* __restrict__ dgamma, float* __restrict__ dbeta) {
+                                                               float* __restrict__ dgamma, float* __restrict__ dbeta,
+                                                               float* __restrict__ acc_gamma = nullptr,
+                                                               float* __restrict__ acc_beta = nullptr) {
   float s1, s2;
   if (!bn_partial_sums(partial, nblocks, C, &s1, &s2)) return;
   const int c = blockIdx.x * 32 + threadIdx.x;
   dbeta[c] = s1;
   dgamma[c] = s2;
+  if (acc_beta) acc_beta[c] += s1;
+  if (acc_gamma) acc_gamma[c] += s2;
 }
 
 // BITS: also write the ReLU mask byte of every vector (residual layers only; a template parameter so
@@ -304,7 +310,7 @@ static int bn_fwd_t(const void* x, const void* res, void* y, const float* gamma,
 template <typename T>
 static int bn_bwd_t(const void* x, const void* y, const void* dy, void* dx, void* dres, const float* gamma,
                     const float* beta, const float* smean, const float* sinv, float* dgamma, float* dbeta, int64_t rows, int C, int relu,
-                    const void* bits, void* scratch, cudaStream_t s) {
+                    const void* bits, void* scratch, cudaStream_t s, float* acc_gamma = nullptr, float* acc_beta = nullptr) {
   constexpr int V = 16 / sizeof(T);
   int st = bn_check(rows, C, V);
   if (st) return st;
@@ -321,7 +327,7 @@ static int bn_bwd_t(const void* x, const void* y, const void* dy, void* dx, void
   else
     bn_reduce_kernel<T, V, true, false><<<grid, kBnThreads, 0, s>>>((const T*)x, (const T*)y, (const T*)dy, smean, sinv, gamma, beta, mb,
                                                                     nvec, C, relu, reverse, (float*)scratch);
-  bn_finalize_bwd_kernel<<<(C + 31) / 32, dim3(32, 32), 0, s>>>((const float*)scratch, grid, C, dgamma, dbeta);
+  bn_finalize_bwd_kernel<<<(C + 31) / 32, dim3(32, 32), 0, s>>>((const float*)scratch, grid, C, dgamma, dbeta, acc_gamma, acc_beta);
   if (maskx)
     bn_apply_bwd_kernel<T, V, true><<<grid, kBnThreads, 0, s>>>((const T*)x, nullptr, (const T*)dy, (T*)dx, (T*)dres, gamma, beta,
                                                                 smean, sinv, dgamma, dbeta, nullptr, nvec, C, relu, 1.f / (float)rows);
@@ -676,6 +682,23 @@ int tmpi_bn_relu_bwd(const void* x, const void* y, const void* dy, void* dx, voi
                                            channels, relu, mask_bits, scratch, s);
     case TMPI_F32: return bn_bwd_t<float>(x, y, dy, dx, dresidual, gamma, beta, save_mean, save_invstd, dgamma, dbeta, rows,
                                           channels, relu, mask_bits, scratch, s);
+  }
+  return fail(TMPI_ERR_UNSUPPORTED, "bn: dtype %d", dtype);
+}
+
+// tmpi_bn_relu_bwd that also adds dgamma / dbeta to acc_gamma / acc_beta (the parameters' gradient buffers; nullable).
+int tmpi_bn_relu_bwd_acc(const void* x, const void* y, const void* dy, void* dx, void* dresidual, const float* gamma,
+                         const float* beta, const float* save_mean, const float* save_invstd, float* dgamma, float* dbeta,
+                         int64_t rows, int channels, int relu, int dtype, const void* mask_bits, void* scratch,
+                         float* acc_gamma, float* acc_beta, void* stream) {
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (dtype) {
+    case TMPI_BF16: return bn_bwd_t<__nv_bfloat16>(x, y, dy, dx, dresidual, gamma, beta, save_mean, save_invstd, dgamma, dbeta,
+                                                   rows, channels, relu, mask_bits, scratch, s, acc_gamma, acc_beta);
+    case TMPI_F16: return bn_bwd_t<__half>(x, y, dy, dx, dresidual, gamma, beta, save_mean, save_invstd, dgamma, dbeta, rows,
+                                           channels, relu, mask_bits, scratch, s, acc_gamma, acc_beta);
+    case TMPI_F32: return bn_bwd_t<float>(x, y, dy, dx, dresidual, gamma, beta, save_mean, save_invstd, dgamma, dbeta, rows,
+                                          channels, relu, mask_bits, scratch, s, acc_gamma, acc_beta);
   }
   return fail(TMPI_ERR_UNSUPPORTED, "bn: dtype %d", dtype);
 }

@@ -278,9 +278,10 @@ __device__ void epilogue_store(Shared* sh, unsigned char* stg, float* stats_all,
         }
       }
       __syncwarp();
-      float cs[8], cq[8];
+      // packed fp32 pairs (add.f32x2 / fma.rn.f32x2): column sums and sums of squares of this lane's 8 columns
+      unsigned long long cs2[4], cq2[4];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) { cs[e] = 0.f; cq[e] = 0.f; }
+      for (int e = 0; e < 4; ++e) { cs2[e] = 0ull; cq2[e] = 0ull; }
       __nv_bfloat16* out = p.out + (size_t)row0 * p.N + col0 + chunk * 8;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
@@ -288,22 +289,37 @@ __device__ void epilogue_store(Shared* sh, unsigned char* stg, float* stats_all,
         const uint4 u = *reinterpret_cast<const uint4*>(stg + (size_t)rw * 128 + ((chunk ^ (rw & 7)) << 4));
         if (row0 + rw < p.M) *reinterpret_cast<uint4*>(out + (size_t)rw * p.N) = u;
         if (do_stats) {                         // rows past M hold zeros
-          float f[8];
-          unpack8(u, f);
+          const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
-          for (int e = 0; e < 8; ++e) { cs[e] += f[e]; cq[e] += f[e] * f[e]; }
+          for (int e = 0; e < 4; ++e) {
+            unsigned long long f2;
+            asm("mov.b64 %0, {%1, %2};" : "=l"(f2) : "r"(w[e] << 16), "r"(w[e] & 0xffff0000u));
+            asm("add.rn.f32x2 %0, %0, %1;" : "+l"(cs2[e]) : "l"(f2));
+            asm("fma.rn.f32x2 %0, %1, %1, %0;" : "+l"(cq2[e]) : "l"(f2));
+          }
         }
       }
       if (do_stats) {
+        float cs[8], cq[8];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          uint32_t lo, hi;
+          asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(cs2[e]));
+          cs[2 * e] = __uint_as_float(lo); cs[2 * e + 1] = __uint_as_float(hi);
+          asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(cq2[e]));
+          cq[2 * e] = __uint_as_float(lo); cq[2 * e + 1] = __uint_as_float(hi);
+        }
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           cs[e] += __shfl_xor_sync(0xffffffffu, cs[e], 8); cq[e] += __shfl_xor_sync(0xffffffffu, cq[e], 8);
           cs[e] += __shfl_xor_sync(0xffffffffu, cs[e], 16); cq[e] += __shfl_xor_sync(0xffffffffu, cq[e], 16);
         }
-        if (rsub == 0) {                        // this lane alone owns these slots of the warp's accumulators
-          float* acc = stats + c0 + chunk * 8;
+        // all four lanes of a column chunk now hold the sums: each adds a quarter of them to the warp's
+        // accumulators (slots owned by this lane alone)
+        float* acc = stats + c0 + chunk * 8 + 2 * rsub;
 #pragma unroll
-          for (int e = 0; e < 8; ++e) { acc[e] += cs[e]; acc[BN + e] += cq[e]; }
+        for (int e = 0; e < 8; ++e) {
+          if ((e >> 1) == rsub) { acc[e & 1] += cs[e]; acc[BN + (e & 1)] += cq[e]; }
         }
       }
       __syncwarp();                             // the staging tile is rewritten by the next slice
@@ -411,52 +427,67 @@ conv_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   }
 }
 
-// out[row, n0 + c] (+)= sum over slices of the partial tiles, in slice order; one thread per 8 columns
+// out[row, n0 + c] (+)= sum over slices of the partial tiles.  L lanes (a power of two up to 32) share one group of
+// 8 columns: lane j adds slices j, j + L, ... and the L partial sums are combined by a fixed butterfly, so the
+// result does not depend on timing.
 __global__ void __launch_bounds__(256)
 conv_splitk_reduce_kernel(const float* __restrict__ ws, __nv_bfloat16* __restrict__ out, int M, int N, int tiles_m, int tiles_n,
-                          int slices, int mma_n, int accumulate) {
-  const int groups = N / 8;                                    // N is a multiple of 64
+                          int slices, int mma_n, int accumulate, int L) {
+  const int groups = N / 8;                                    // N is a multiple of 8
   const long long total = (long long)M * groups;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const int row = (int)(i / groups), col = (int)(i - (long long)row * groups) * 8;
-    const int m_blk = row / BM, n_blk = col / BN;
-    const int tile = n_blk * tiles_m + m_blk;
-    const float* src = ws + (((size_t)tile * slices) * BM + (row - m_blk * BM)) * mma_n + (col - n_blk * BN);
+  const int sub = threadIdx.x & (L - 1);
+  const long long per_block = blockDim.x / L;
+  for (long long i0 = (long long)blockIdx.x * per_block; i0 < total; i0 += (long long)gridDim.x * per_block) {
+    const long long i = i0 + threadIdx.x / L;
+    const bool live = i < total;
     float a[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) a[e] = 0.f;
-    int s = 0;
-    for (; s + 4 <= slices; s += 4) {                          // four slices of loads in flight
-      float4 x[4][2];
+    int row = 0, col = 0;
+    if (live) {
+      row = (int)(i / groups); col = (int)(i - (long long)row * groups) * 8;
+      const int m_blk = row / BM, n_blk = col / BN;
+      const int tile = n_blk * tiles_m + m_blk;
+      const float* src = ws + (((size_t)tile * slices) * BM + (row - m_blk * BM)) * mma_n + (col - n_blk * BN);
+      int s = sub;
+      for (; s + 3 * L < slices; s += 4 * L) {                 // four slices of loads in flight
+        float4 x[4][2];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const float4* q = reinterpret_cast<const float4*>(src + (size_t)(s + u) * BM * mma_n);
-        x[u][0] = __ldcs(q); x[u][1] = __ldcs(q + 1);
+        for (int u = 0; u < 4; ++u) {
+          const float4* q = reinterpret_cast<const float4*>(src + (size_t)(s + u * L) * BM * mma_n);
+          x[u][0] = __ldcs(q); x[u][1] = __ldcs(q + 1);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          a[0] += x[u][0].x; a[1] += x[u][0].y; a[2] += x[u][0].z; a[3] += x[u][0].w;
+          a[4] += x[u][1].x; a[5] += x[u][1].y; a[6] += x[u][1].z; a[7] += x[u][1].w;
+        }
       }
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        a[0] += x[u][0].x; a[1] += x[u][0].y; a[2] += x[u][0].z; a[3] += x[u][0].w;
-        a[4] += x[u][1].x; a[5] += x[u][1].y; a[6] += x[u][1].z; a[7] += x[u][1].w;
+      for (; s < slices; s += L) {
+        const float4* q = reinterpret_cast<const float4*>(src + (size_t)s * BM * mma_n);
+        const float4 x0 = __ldcs(q), x1 = __ldcs(q + 1);
+        a[0] += x0.x; a[1] += x0.y; a[2] += x0.z; a[3] += x0.w; a[4] += x1.x; a[5] += x1.y; a[6] += x1.z; a[7] += x1.w;
       }
     }
-    for (; s < slices; ++s) {
-      const float4* q = reinterpret_cast<const float4*>(src + (size_t)s * BM * mma_n);
-      const float4 x0 = __ldcs(q), x1 = __ldcs(q + 1);
-      a[0] += x0.x; a[1] += x0.y; a[2] += x0.z; a[3] += x0.w; a[4] += x1.x; a[5] += x1.y; a[6] += x1.z; a[7] += x1.w;
-    }
-    __nv_bfloat16* dst = out + (size_t)row * N + col;
-    if (accumulate) {
-      float f[8];
-      unpack8(*reinterpret_cast<const uint4*>(dst), f);
+    for (int d = 1; d < L; d <<= 1) {
 #pragma unroll
-      for (int e = 0; e < 8; ++e) a[e] += f[e];
+      for (int e = 0; e < 8; ++e) a[e] += __shfl_xor_sync(0xffffffffu, a[e], d);
     }
-    __nv_bfloat162 h0 = __floats2bfloat162_rn(a[0], a[1]), h1 = __floats2bfloat162_rn(a[2], a[3]);
-    __nv_bfloat162 h2 = __floats2bfloat162_rn(a[4], a[5]), h3 = __floats2bfloat162_rn(a[6], a[7]);
-    uint4 u;
-    u.x = *reinterpret_cast<uint32_t*>(&h0); u.y = *reinterpret_cast<uint32_t*>(&h1);
-    u.z = *reinterpret_cast<uint32_t*>(&h2); u.w = *reinterpret_cast<uint32_t*>(&h3);
-    *reinterpret_cast<uint4*>(dst) = u;
+    if (live && sub == 0) {
+      __nv_bfloat16* dst = out + (size_t)row * N + col;
+      if (accumulate) {
+        float f[8];
+        unpack8(*reinterpret_cast<const uint4*>(dst), f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) a[e] += f[e];
+      }
+      __nv_bfloat162 h0 = __floats2bfloat162_rn(a[0], a[1]), h1 = __floats2bfloat162_rn(a[2], a[3]);
+      __nv_bfloat162 h2 = __floats2bfloat162_rn(a[4], a[5]), h3 = __floats2bfloat162_rn(a[6], a[7]);
+      uint4 u;
+      u.x = *reinterpret_cast<uint32_t*>(&h0); u.y = *reinterpret_cast<uint32_t*>(&h1);
+      u.z = *reinterpret_cast<uint32_t*>(&h2); u.w = *reinterpret_cast<uint32_t*>(&h3);
+      *reinterpret_cast<uint4*>(dst) = u;
+    }
   }
 }
 
@@ -541,6 +572,18 @@ static int conv_launch(const CUtensorMap& ma, const CUtensorMap& mb, conv::Probl
   conv::conv_gemm_kernel<<<grid, conv::THREADS, smem, s>>>(ma, mb, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? TMPI_OK : fail(TMPI_ERR_CUDA, "conv launch: %s", cudaGetErrorString(e));
+}
+
+static int launch_splitk_reduce(const conv::Problem& p, const void* workspace, void* out, int accumulate, cudaStream_t s) {
+  int L = 1;
+  while (L < 32 && L < p.slices) L <<= 1;                       // lanes per group of 8 columns
+  const long long groups = (long long)p.M * (p.N / 8);
+  const long long per_block = 256 / L;
+  const int grid = (int)std::min<long long>((groups + per_block - 1) / per_block, (long long)gemm_sm_count() * 8);
+  conv::conv_splitk_reduce_kernel<<<grid, 256, 0, s>>>((const float*)workspace, (__nv_bfloat16*)out, p.M, p.N, p.tiles_m, p.tiles_n,
+                                                     p.slices, p.mma_n, accumulate, L);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? TMPI_OK : fail(TMPI_ERR_CUDA, "split-K reduce launch: %s", cudaGetErrorString(e));
 }
 
 struct Geom { int N, H, W, Cin, Cout, R, S, stride, pad, Ho, Wo; };
@@ -688,12 +731,7 @@ int tmpi_conv_wgrad(const void* dy, const void* x, void* dw, int N, int H, int W
   p.epi = conv::EPI_SPLITK;
   p.workspace = (float*)workspace;
   if ((st = conv_launch(ma, mb, p, nullptr, (cudaStream_t)stream))) return st;
-  const long long groups = (long long)p.M * (p.N / 8);
-  const int grid = (int)std::min<long long>((groups + 255) / 256, (long long)gemm_sm_count() * 8);
-  conv::conv_splitk_reduce_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const float*)workspace, (__nv_bfloat16*)dw, p.M, p.N,
-                                                                        p.tiles_m, p.tiles_n, p.slices, p.mma_n, accumulate);
-  cudaError_t e = cudaGetLastError();
-  return e == cudaSuccess ? TMPI_OK : fail(TMPI_ERR_CUDA, "conv wgrad reduce launch: %s", cudaGetErrorString(e));
+  return launch_splitk_reduce(p, workspace, dw, accumulate, (cudaStream_t)stream);
 }
 
 // C[M, N] (+)= A^T B for row-major A [K, M] and B [K, N] (both read as they lie) with a long K and a small
@@ -726,12 +764,7 @@ int tmpi_gemm_bf16_tn_splitk(const void* A, const void* B, void* C, int M, int N
   p.epi = conv::EPI_SPLITK;
   p.workspace = (float*)workspace;
   if ((st = conv_launch(ma, mb, p, nullptr, (cudaStream_t)stream))) return st;
-  const long long groups = (long long)M * (N / 8);
-  const int grid = (int)std::min<long long>((groups + 255) / 256, (long long)gemm_sm_count() * 8);
-  conv::conv_splitk_reduce_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const float*)workspace, (__nv_bfloat16*)C, M, N, p.tiles_m,
-                                                                        p.tiles_n, p.slices, p.mma_n, accumulate);
-  cudaError_t e = cudaGetLastError();
-  return e == cudaSuccess ? TMPI_OK : fail(TMPI_ERR_CUDA, "gemm_tn_splitk reduce launch: %s", cudaGetErrorString(e));
+  return launch_splitk_reduce(p, workspace, C, accumulate, (cudaStream_t)stream);
 }
 
 // Non-zero after a convolution CTA gave up on a bounded wait (2000 + the point where it happened); clears it.

@@ -60,6 +60,7 @@ Tunable g_tunables[] = {
   {"use_nvls", {1}},
   {"bn_pool_fused_bwd", {0}},              // stem batch-norm + pool backward as one stage (slower than pool, then batch-norm)
   {"bn_reverse_stats", {1}},               // batch-norm statistics passes walk the tensor from its end (L2 reuse)
+  {"grad_fork", {1}},                      // residual blocks sum the two gradients of their input inside a kernel
   {"conv_own_3x3", {0}},                   // 3x3 convolutions on the implicit-GEMM kernel (1x1 always are)
   {"gemm_pair", {1}},                      // 256 x 256 tiles on CTA pairs (cta_group::2) where the shape allows
   {"ps_poll_us", {100}},

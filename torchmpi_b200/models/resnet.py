@@ -45,11 +45,19 @@ class Bottleneck(nn.Module):
         identity = x if (self.downsample is None or self.fused) else self.downsample(x)
         if self.fused:
             from ..ops.conv import conv_bn
+            from ..parallel.flat_buckets import GradFork
+            # x has two consumers (the first convolution and the identity branch): their gradients are summed
+            # inside the kernel of whichever runs last in backward instead of by a separate add
+            from .. import config
+            fork = GradFork(2) if (torch.is_grad_enabled() and x.requires_grad and config.get("grad_fork")) else None
+            res_fork = None
             if self.downsample is not None:
-                identity = conv_bn(self.downsample[0], self.downsample[1], x)
-            out = conv_bn(self.conv1, self.bn1, x)
+                identity = conv_bn(self.downsample[0], self.downsample[1], x, fork=fork)
+            else:
+                res_fork = fork
+            out = conv_bn(self.conv1, self.bn1, x, fork=fork)
             out = conv_bn(self.conv2, self.bn2, out)
-            return conv_bn(self.conv3, self.bn3, out, residual=identity)
+            return conv_bn(self.conv3, self.bn3, out, residual=identity, res_fork=res_fork)
         out = torch.relu(self.bn1(self.conv1(x)))
         out = torch.relu(self.bn2(self.conv2(out)))
         out = self.bn3(self.conv3(out))

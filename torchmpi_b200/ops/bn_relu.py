@@ -42,9 +42,12 @@ def supported(x: torch.Tensor) -> bool:
 
 class _BnReluFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, residual, gamma, beta, running_mean, running_var, eps, momentum, relu, training, partial_rows=0):
+    def forward(ctx, x, residual, gamma, beta, running_mean, running_var, eps, momentum, relu, training, partial_rows=0,
+                params=None, res_fork=None):
         """``partial_rows > 0``: the producer of ``x`` (a convolution of ``ops.conv``) has already left that many
-        rows of partial sums in this stream's scratch buffer, so the statistics pass is skipped."""
+        rows of partial sums in this stream's scratch buffer, so the statistics pass is skipped.  ``params``: the
+        (weight, bias) Parameters, whose gradients are added in place when a flat bucket owns their buffers;
+        ``res_fork``: a ``GradFork`` shared by the consumers of ``residual``."""
         global launch_count
         x = x.contiguous(memory_format=torch.channels_last)
         if residual is not None:
@@ -87,6 +90,7 @@ class _BnReluFn(torch.autograd.Function):
         keep_y = relu and not ctx.mask_from_x and bits is None
         ctx.save_for_backward(x, y if keep_y else None, gamma, beta, mean, invstd, bits)
         ctx.relu, ctx.has_res = relu, residual is not None
+        ctx.params, ctx.res_fork = params, res_fork
         return y
 
     @staticmethod
@@ -99,13 +103,27 @@ class _BnReluFn(torch.autograd.Function):
         dres = torch.empty_like(x, memory_format=torch.channels_last) if ctx.has_res else None
         dgamma = torch.empty(C, dtype=torch.float32, device=x.device)
         dbeta = torch.empty(C, dtype=torch.float32, device=x.device)
-        check(lib.tmpi_bn_relu_bwd(
+        from ..parallel.flat_buckets import direct_grad, grad_written
+        acc_g = acc_b = None
+        if ctx.params is not None and has_symbol("tmpi_bn_relu_bwd_acc"):
+            acc_g, acc_b = direct_grad(ctx.params[0]), direct_grad(ctx.params[1])
+            if acc_g is None or acc_b is None or not (acc_g.is_contiguous() and acc_b.is_contiguous()
+                                                      and acc_g.dtype == torch.float32 and acc_b.dtype == torch.float32):
+                acc_g = acc_b = None
+        check(lib.tmpi_bn_relu_bwd_acc(
             x.data_ptr(), y.data_ptr() if y is not None else None, dy.data_ptr(), dx.data_ptr(),
             dres.data_ptr() if dres is not None else None, gamma.data_ptr(), beta.data_ptr(), mean.data_ptr(), invstd.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(),
             N * H * W, C, int(ctx.relu), dtype_code(x.dtype), bits.data_ptr() if bits is not None else None,
-            _scratch_for(x.device, C).data_ptr(), stream_ptr()))
+            _scratch_for(x.device, C).data_ptr(), acc_g.data_ptr() if acc_g is not None else None,
+            acc_b.data_ptr() if acc_b is not None else None, stream_ptr()))
         launch_count += 3
-        return dx, dres, dgamma, dbeta, None, None, None, None, None, None, None
+        if acc_g is not None:                  # the parameter gradients were added in place by the finalize kernel
+            grad_written(ctx.params[0])
+            grad_written(ctx.params[1])
+            dgamma = dbeta = None
+        if dres is not None and ctx.res_fork is not None:
+            dres = ctx.res_fork.offer(lambda add: dres if add is None else dres.add_(add))
+        return dx, dres, dgamma, dbeta, None, None, None, None, None, None, None, None, None
 
 
 class _BnReluPoolFn(torch.autograd.Function):
@@ -189,11 +207,14 @@ class FusedBatchNormReLU(nn.BatchNorm2d):
         super().__init__(num_features, eps=eps, momentum=momentum)
         self.relu = relu
 
-    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None, partial_rows: int = 0) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None, partial_rows: int = 0, res_fork=None) -> torch.Tensor:
         if supported(x) and self.weight.dtype == torch.float32:
             # num_batches_tracked is only needed for momentum=None (cumulative average), not supported here
             return _BnReluFn.apply(x, residual, self.weight, self.bias, self.running_mean, self.running_var,
-                                   self.eps, self.momentum, self.relu, self.training, partial_rows)
+                                   self.eps, self.momentum, self.relu, self.training, partial_rows,
+                                   (self.weight, self.bias), res_fork)
+        if res_fork is not None:
+            res_fork.consumers -= 1            # the library path lets autograd add this gradient
         out = F.batch_norm(x, self.running_mean, self.running_var, self.weight, self.bias, self.training,
                            self.momentum, self.eps)
         if residual is not None:

@@ -127,27 +127,41 @@ def check_status() -> None:
 class _ConvFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, stride, pad, stats, state=None):
+        """``state`` (a dict, optional): receives ``rows`` (rows of partial sums written to ``stats``); may carry
+        ``param`` (the Parameter behind ``w``: its gradient is then added into ``param.grad`` in place when a flat
+        bucket owns that buffer) and ``fork`` (a ``GradFork`` shared by all consumers of ``x``)."""
         x, w = _cl(x), _cl(w)
         y, rows = conv_forward(x, w, stride, pad, stats)
         ctx.save_for_backward(x, w)
         ctx.stride, ctx.pad = stride, pad
+        ctx.param = ctx.fork = None
         if state is not None:
-            state["rows"] = rows          # rows of partial sums written to `stats`
+            state["rows"] = rows
+            ctx.param, ctx.fork = state.get("param"), state.get("fork")
         return y
 
     @staticmethod
     def backward(ctx, dy):
         x, w = ctx.saved_tensors
         dy = _cl(dy)
+        from ..parallel.flat_buckets import direct_grad, grad_written
         dx = dw = None
         if ctx.needs_input_grad[0]:
-            if ctx.stride == 1:
-                dx = conv_dgrad(dy, w, x.shape, 1, ctx.pad)
-            else:    # strided input gradients stay on the library
-                dx = torch.ops.aten.convolution_backward(dy, x, w, None, (ctx.stride,) * 2, (ctx.pad,) * 2, (1, 1), False,
-                                                         (0, 0), 1, (True, False, False))[0]
+            def make_dx(add):
+                if ctx.stride == 1:
+                    return conv_dgrad(dy, w, x.shape, 1, ctx.pad, add=_cl(add) if add is not None else None)
+                # strided input gradients stay on the library
+                g = torch.ops.aten.convolution_backward(dy, x, w, None, (ctx.stride,) * 2, (ctx.pad,) * 2, (1, 1), False,
+                                                        (0, 0), 1, (True, False, False))[0]
+                return g if add is None else g.add_(add)
+            dx = ctx.fork.offer(make_dx) if ctx.fork is not None else make_dx(None)
         if ctx.needs_input_grad[1]:
-            dw = conv_wgrad(dy, x, w.shape, ctx.stride, ctx.pad)
+            sink = direct_grad(ctx.param)
+            if sink is not None and sink.shape == w.shape and sink.stride() == w.stride() and sink.dtype == w.dtype:
+                conv_wgrad(dy, x, w.shape, ctx.stride, ctx.pad, out=sink, accumulate=True)
+                grad_written(ctx.param)
+            else:
+                dw = conv_wgrad(dy, x, w.shape, ctx.stride, ctx.pad)
         return dx, dw, None, None, None, None
 
 
@@ -157,26 +171,31 @@ def conv2d(x: torch.Tensor, w: torch.Tensor, stride: int = 1, padding: int = 0) 
     return F.conv2d(x, w, None, stride, padding)
 
 
-def conv_bn(conv: nn.Conv2d, bn, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+def conv_bn(conv: nn.Conv2d, bn, x: torch.Tensor, residual: Optional[torch.Tensor] = None, fork=None, res_fork=None) -> torch.Tensor:
     """``bn(conv(x), residual)`` for a ``FusedBatchNormReLU`` ``bn``.  In training, when both kernels apply, the
     convolution's epilogue accumulates the batch statistics of its output (per-CTA partial sums in the
     batch-norm's scratch buffer) and the batch-norm starts at its finalize step: the statistics pass over the
-    activation, one full read of it, is gone."""
+    activation, one full read of it, is gone.  ``fork`` / ``res_fork`` (``GradFork``, optional) are shared with the
+    other consumers of ``x`` / of ``residual``: the gradients into those tensors are then summed inside the kernels."""
     from . import bn_relu
     w = conv.weight
     stride, pad = conv.stride[0], conv.padding[0]
+    fused_bn = isinstance(bn, bn_relu.FusedBatchNormReLU)
+    bn_kw = {"res_fork": res_fork} if (fused_bn and res_fork is not None) else {}
     if not supported(x, w, stride, pad) or not own_kernel_enabled(w.shape[2]):
-        return bn(F.conv2d(x, w, None, conv.stride, conv.padding), residual)
+        if fork is not None:
+            fork.consumers -= 1       # a library convolution: autograd itself adds its gradient into x
+        return bn(F.conv2d(x, w, None, conv.stride, conv.padding), residual, **bn_kw)
+    fn_state = {"param": w, "fork": fork}
     fuse = (bn.training and x.dtype == torch.bfloat16 and bn.weight.dtype == torch.float32
-            and has_symbol("tmpi_bn_relu_fwd_partials") and isinstance(bn, bn_relu.FusedBatchNormReLU))
+            and has_symbol("tmpi_bn_relu_fwd_partials") and fused_bn)
     if not fuse:
-        return bn(_ConvFn.apply(x, w, stride, pad, None), residual)
+        return bn(_ConvFn.apply(x, w, stride, pad, None, fn_state), residual, **bn_kw)
     stats = bn_relu._scratch_for(x.device, w.shape[0]).view(torch.float32)
-    fn_state = {}
     y = _ConvFn.apply(x, w, stride, pad, stats, fn_state)
     if not bn_relu.supported(y):
-        return bn(y, residual)
-    return bn(y, residual, partial_rows=fn_state["rows"])
+        return bn(y, residual, **bn_kw)
+    return bn(y, residual, partial_rows=fn_state["rows"], **bn_kw)
 
 
 def own_kernel_enabled(kernel_size: int) -> bool:

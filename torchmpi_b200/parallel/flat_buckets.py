@@ -40,6 +40,45 @@ def _dense(p: torch.Tensor) -> bool:
         (p.dim() == 5 and p.is_contiguous(memory_format=torch.channels_last_3d))
 
 
+class GradFork:
+    """Sums the gradients that several consumers send into one activation without a separate add kernel.
+
+    Autograd adds the gradients of a tensor that is used twice (the input of a residual block feeds the
+    first convolution and the identity branch) with one more elementwise pass.  The consumers' backward
+    functions can instead ``offer`` their gradient here: every consumer but the last parks its result and
+    returns ``None`` to autograd; the last one computes ``its gradient + the parked sum`` in its own kernel
+    (an epilogue that adds a tensor) and returns the total."""
+
+    def __init__(self, consumers: int):
+        self.consumers, self.seen, self.parked = consumers, 0, None
+
+    def offer(self, make_grad):
+        """``make_grad(add)`` returns this consumer's gradient, plus ``add`` when ``add`` is not None."""
+        self.seen += 1
+        g = make_grad(self.parked)
+        if self.seen < self.consumers:
+            self.parked = g
+            return None
+        self.seen, self.parked = 0, None
+        return g
+
+
+def direct_grad(param):
+    """The gradient buffer that a backward kernel may add to in place of returning a gradient for ``param``
+    (its view of a flat bucket whose readiness callback is installed), or None."""
+    if param is None or getattr(param, "_tmpi_grad_sink", None) is None or param.grad is None:
+        return None
+    return param.grad
+
+
+def grad_written(param) -> None:
+    """Tells the bucket of ``param`` that its gradient has been added to ``param.grad`` in place.  Autograd may
+    still run the parameter's post-accumulate hook afterwards although the backward function returned no
+    gradient for it (it does in current PyTorch): that second report is recognised by the flag and dropped."""
+    param._tmpi_reported = True
+    param._tmpi_grad_sink(param, direct=True)
+
+
 class FlatBuckets:
     def __init__(self, params: Sequence[torch.nn.Parameter], bucket_bytes: int = 32 << 20,
                  pad_to: int = 1024, allocator: Optional[Callable] = None, reverse: bool = True,
@@ -146,7 +185,10 @@ class FlatBuckets:
         for b in self.buckets:
             b.pending = len(b.params)
             for p in b.params:
-                def hook(param, b=b):
+                def hook(param, b=b, direct=False):
+                    if not direct and getattr(param, "_tmpi_reported", False):
+                        param._tmpi_reported = False      # already reported by the kernel that wrote the gradient
+                        return
                     if on_begin is not None:
                         on_begin()
                     b.pending -= 1
@@ -154,6 +196,7 @@ class FlatBuckets:
                         b.pending = len(b.params)
                         on_bucket(b if pass_bucket else b.grad)
                 handles.append(p.register_post_accumulate_grad_hook(hook))
+                p._tmpi_grad_sink = hook      # kernels that add to p.grad in place call this instead (see direct_grad)
         self._hooks += handles
         return handles
 
@@ -161,3 +204,7 @@ class FlatBuckets:
         for h in self._hooks:
             h.remove()
         self._hooks = []
+        for b in self.buckets:
+            for p in b.params:
+                if hasattr(p, "_tmpi_grad_sink"):
+                    del p._tmpi_grad_sink
