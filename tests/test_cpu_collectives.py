@@ -157,7 +157,7 @@ def _matrix(rank, world):
     return True
 
 
-@pytest.mark.parametrize("world", [2, 3])
+@pytest.mark.parametrize("world", [2, 3, 5, 8])
 def test_collective_matrix(world):
     assert all(run_ranks(_matrix, world, timeout=300))
 
@@ -180,6 +180,25 @@ def _hier_allreduce(rank, world, cartesian):
         mpi.allreduce_tensor(t)
         assert torch.all(t == world * (world - 1) / 2)
         mpi.config.set_hierarchical_collectives()
+        # asynchronous flavour on the hierarchical span: a live handle at once, the whole chain behind it
+        import time
+        t = torch.full((5000,), float(rank))
+        t0 = time.perf_counter()
+        h = mpi.async_.allreduce_tensor(t)
+        launch_us = (time.perf_counter() - t0) * 1e6
+        assert h is not None and launch_us < 50000
+        mpi.sync_handle(h)
+        assert torch.all(t == world * (world - 1) / 2), (cartesian, t[:3])
+        # reduce to a root that is not the first member of its group
+        for root in range(world):
+            src = torch.full((777,), float(rank + 1))
+            dst = torch.full((777,), -1.0)
+            mpi.reduce_tensor(root, src, dst)
+            assert torch.all(src == rank + 1)
+            if rank == root:
+                assert torch.all(dst == world * (world + 1) / 2), (cartesian, root, dst[:3])
+            else:
+                assert torch.all(dst == -1.0)
         mpi.stop()
     return True
 
@@ -187,3 +206,41 @@ def _hier_allreduce(rank, world, cartesian):
 @pytest.mark.parametrize("cartesian", [True, False])
 def test_hierarchical_allreduce_equals_flat(cartesian):
     assert all(run_ranks(_hier_allreduce, 4, cartesian))
+
+
+def _independent_push(rank, world):
+    """Two disjoint groups of a level split themselves independently: only the members of a communicator take
+    part in its push (lib/c_api.h:42-47), so one group can push a level the other never does."""
+    import torchmpi_b200 as mpi
+    mpi.start(with_cuda=False)
+    base = mpi.num_communicators
+    lvl1 = mpi.push_communicator("left" if rank < 2 else "right")          # {0, 1} and {2, 3}
+    assert mpi.size() == 2
+    if rank < 2:
+        # only the left group goes deeper, twice, while the right group works at its own level
+        lvl2 = mpi.push_communicator(f"solo{rank}")
+        assert mpi.size() == 1 and lvl2 == lvl1 + 1
+        mpi.set_communicator(lvl1)
+        lvl3 = mpi.push_communicator("again")
+        assert mpi.size() == 2 and lvl3 == lvl2 + 1
+        t = torch.full((100,), float(rank))
+        mpi.set_collective_span(lvl3, lvl3)
+        mpi.allreduce_tensor(t)
+        assert torch.all(t == 1.0)
+        assert mpi.num_communicators == base + 3
+    else:
+        t = torch.full((100,), float(rank))
+        mpi.set_collective_span(lvl1, lvl1)
+        for _ in range(3):
+            mpi.allreduce_tensor(t, scale=0.5)
+        assert torch.all(t == 2.5)
+        assert mpi.num_communicators == base + 1
+        assert mpi.num_nodes_in_communicator() == 1
+    mpi.set_communicator(0)
+    mpi.barrier()
+    mpi.stop()
+    return True
+
+
+def test_groups_push_communicators_independently():
+    assert all(run_ranks(_independent_push, 4))

@@ -41,6 +41,22 @@ def _trace_and_checkpoint(rank, world, tmpdir):
     for a, b in zip(other.parameters(), want):
         assert torch.equal(a, b)
     mpinn.check_with_allreduce(other)
+    # parameter-server shards travel with the checkpoint: what the servers hold at save time is what they hold after load
+    from torchmpi_b200 import parameterserver as ps
+    seed = torch.arange(1000, dtype=torch.float32) * (1.0 if rank == 0 else 0.0)
+    server = ps.init(seed.clone())
+    if rank == 0:
+        ps.send(server, torch.arange(1000, dtype=torch.float32) + 5.0, "copy").wait()
+    mpi.barrier()
+    path2 = os.path.join(tmpdir, "ckpt_ps.pt")
+    checkpoint.save(path2, model, parameter_servers=[server])
+    if rank == 0:
+        ps.send(server, torch.zeros(1000), "zero").wait()       # lose the contents
+    mpi.barrier()
+    checkpoint.load(path2, other, parameter_servers=[server])
+    got = torch.empty(1000)
+    ps.receive(server, got).wait()
+    assert torch.equal(got, torch.arange(1000, dtype=torch.float32) + 5.0)
     mpi.stop()
     return True
 

@@ -18,6 +18,7 @@ import torch as _torch
 
 from . import _lib, config
 from ._lib import TorchMPIError, TimeoutError_ as TimeoutError  # noqa: A001
+from .watchdog import CommunicatorPoisoned
 from .bootstrap import start, stop
 from .runtime import (S as _S, barrier, rank, size, world_rank, world_size, communicator_names,
                       push_communicator, set_communicator, set_collective_span, collective_span,

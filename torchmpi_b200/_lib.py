@@ -93,6 +93,7 @@ _PROTOS = {
     "tmpi_comm_rank_in": (_i, [_i, _i]),
     "tmpi_comm_key": (_i, [_i, C.c_char_p, _i]),
     "tmpi_comm_current_members": (_i, [_ip, _i]),
+    "tmpi_comm_group_of": (_i, [_i, _i, _ip, _i]),
     "tmpi_comm_names": (_i, [C.c_char_p, _i]),
     "tmpi_comm_has_inter_collective": (_i, [_i]),
     "tmpi_comm_has_intra_collective": (_i, [_i]),
@@ -105,6 +106,7 @@ _PROTOS = {
     "tmpi_handle_stream_wait": (_i, [_u64, _vp]),
     "tmpi_sync_all": (_i, []),
     "tmpi_handles_in_flight": (_i, []),
+    "tmpi_test_lost_handle": (_u64, []),
     "tmpi_test_sleep_task": (_u64, [_i, _i, _i]),
     "tmpi_shm_create": (_i, [_cp, _sz, _i, _i, C.POINTER(_vp)]),
     "tmpi_shm_attach": (_i, [_i, _cp]),

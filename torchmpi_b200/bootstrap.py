@@ -120,6 +120,10 @@ def start(with_cuda: Optional[bool] = None,
     jid = [uuid.uuid4().hex[:12] if S.rank == 0 else None]
     dist.broadcast_object_list(jid, src=0)
     S.job_id = jid[0]
+    names = [None] * S.world
+    dist.all_gather_object(names, S.host_name)
+    S.host_names = tuple(names)
+    S.push_seq = {}
     _setup_host_heap()
 
     if S.with_cuda:
@@ -145,9 +149,11 @@ def start(with_cuda: Optional[bool] = None,
     S.need_inter_node_collectives = runtime.num_nodes_in_communicator() > 1
     if collective_communicator is not None:
         collective_communicator()
-    from . import selector
+    from . import selector, watchdog
     selector.configure()
     runtime.barrier()
+    watchdog.reset()
+    watchdog.start()
     if S.rank == 0:
         log.info("communicators:\n%s", runtime.communicator_names())
 
@@ -156,11 +162,16 @@ def stop() -> None:
     """Drains asynchronous work, frees parameter servers and heaps, leaves the job."""
     if not S.started:
         return
+    from . import watchdog
+    lost = watchdog.poisoned()
+    watchdog.stop(goodbye=True)
+    watchdog.reset()              # the teardown below must run even after a failure
     try:
-        runtime.set_communicator(0)
+        check(lib.tmpi_comm_set_typed(0, 0))
         if S.with_cuda:
             torch.cuda.synchronize()
-        runtime.barrier()
+        if lost is None:
+            runtime.barrier()
     except Exception as e:  # a dead peer must not stop our own cleanup
         log.warning("stop(): barrier failed: %s", e)
     lib.tmpi_sync_all()
@@ -169,7 +180,8 @@ def stop() -> None:
     cache.free_all_tensor_references()
     if S.cuda_heap is not None:
         try:
-            runtime.barrier()
+            if lost is None:
+                runtime.barrier()
         except Exception:
             pass
         S.cuda_heap.destroy()

@@ -23,6 +23,8 @@ from typing import Optional, Sequence
 import torch
 import torch.distributed as dist
 
+from . import gdist
+
 from . import _lib, config, runtime
 from ._lib import lib, check, dtype_code
 from .handles import Handle
@@ -105,7 +107,7 @@ def _flat_allreduce(inp, out, members, backend, scale, algo, async_op) -> Option
     group = runtime.group_for(members)
     if backend == "gloo" and inp.is_cuda:
         host = inp.detach().cpu()
-        work = dist.all_reduce(host, group=group, async_op=True)
+        work = gdist.all_reduce(host, group, async_op=True)
 
         def fin():
             _scale_inplace(host, scale)
@@ -114,7 +116,7 @@ def _flat_allreduce(inp, out, members, backend, scale, algo, async_op) -> Option
     else:
         if out is not inp:
             out.copy_(inp)
-        work = dist.all_reduce(out, group=group, async_op=True)
+        work = gdist.all_reduce(out, group, async_op=True)
         h = Handle(works=[work], finalizers=[lambda: _scale_inplace(out, scale)], keep=(out,))
     if async_op:
         return h
@@ -142,10 +144,10 @@ def _flat_broadcast(t, root, members, backend, async_op) -> Optional[Handle]:
     group = runtime.group_for(members)
     if backend == "gloo" and t.is_cuda:
         host = t.detach().cpu()
-        work = dist.broadcast(host, src=members[root], group=group, async_op=True)
+        work = gdist.broadcast(host, members[root], group, async_op=True)
         h = Handle(works=[work], finalizers=[lambda: t.copy_(host)], keep=(host,))
     else:
-        h = Handle(works=[dist.broadcast(t, src=members[root], group=group, async_op=True)], keep=(t,))
+        h = Handle(works=[gdist.broadcast(t, members[root], group, async_op=True)], keep=(t,))
     if async_op:
         return h
     h.wait()
@@ -172,7 +174,7 @@ def _flat_reduce(inp, out, root, members, backend, async_op) -> Optional[Handle]
     group = runtime.group_for(members)
     # torch.distributed reduces in place and leaves non-root buffers undefined: work on a copy
     tmp = (inp.detach().cpu() if (backend == "gloo" and inp.is_cuda) else inp.clone())
-    work = dist.reduce(tmp, dst=members[root], group=group, async_op=True)
+    work = gdist.reduce(tmp, members[root], group, async_op=True)
 
     def fin():
         if me == root:
@@ -232,15 +234,77 @@ def allreduce_tensor(inp: torch.Tensor, out: Optional[torch.Tensor] = None, *, s
         with _trace.timed("allreduce", str(algo), inp.numel() * inp.element_size(), inp.is_cuda):
             return _flat_allreduce(inp, out, plan[1], backend, scale, a, False)
     _, inner, inter, cartesian = plan
-    # staged composition; the stages depend on each other, so an async caller gets a completed handle
-    _wait(_flat_allreduce(inp, out, inner, backend, 1.0, a, False))
-    if cartesian:
-        _wait(_flat_allreduce(out, out, inter, backend, scale, a, False))
-    else:
-        if len(inter) > 1:
-            _wait(_flat_allreduce(out, out, inter, backend, scale, a, False))
-        _wait(_flat_broadcast(out, 0, inner, backend, False))
-    return Handle() if async_op else None
+
+    def stages(run):
+        """The intra -> inter (-> broadcast) chain; ``run(thunk)`` executes one stage."""
+        run(lambda asy: _flat_allreduce(inp, out, inner, backend, 1.0 if len(inter) > 1 or not cartesian else scale, a, asy))
+        if cartesian:
+            if len(inter) > 1:
+                run(lambda asy: _flat_allreduce(out, out, inter, backend, scale, a, asy))
+        else:
+            if len(inter) > 1:
+                run(lambda asy: _flat_allreduce(out, out, inter, backend, scale, a, asy))
+            run(lambda asy: _flat_broadcast(out, 0, inner, backend, asy))
+
+    if not async_op:
+        stages(lambda thunk: _wait(thunk(False)))
+        return None
+    return _async_chain(inp, out, backend, inner, stages)
+
+
+class _ThreadWork:
+    """A chain of dependent stages run to completion on a helper thread; looks like a work object of
+    ``torch.distributed`` to ``Handle`` (``wait`` / ``is_completed``)."""
+
+    def __init__(self, fn):
+        import threading
+        self.error = None
+
+        def body():
+            try:
+                fn()
+            except BaseException as e:      # re-raised in wait()
+                self.error = e
+        self.thread = threading.Thread(target=body, daemon=True)
+        self.thread.start()
+
+    def is_completed(self) -> bool:
+        return not self.thread.is_alive()
+
+    def wait(self) -> None:
+        self.thread.join()
+        if self.error is not None:
+            raise self.error
+
+
+def _async_chain(inp, out, backend, inner, stages) -> Handle:
+    """Asynchronous hierarchical allreduce: the whole chain is handed off and a live handle returned at once,
+    as the reference does with its collective offload pool (lib/collectives_cuda.cpp:771-803,840-864).
+
+    GPU tensors on the peer-memory backend: every stage is enqueued on the ordered asynchronous lane (one
+    worker thread, one stream), so the stages run in order on the device with no host wait in between and
+    the launch returns within microseconds.  Other backends: one helper thread runs the stages in order."""
+    be = _resolve_backend(inp, backend, inner, "allreduce")
+    on_lane = (be == "p2p" and inp.is_cuda and S.cuda_heap is not None
+               and not S.cuda_heap._needs_staging(inp) and not S.cuda_heap._needs_staging(out))
+    if on_lane:
+        h = Handle()
+        stages(lambda thunk: h.merge(thunk(True)))
+        return h
+    stream = torch.cuda.current_stream() if inp.is_cuda else None
+    ready = stream.record_event() if stream is not None else None
+
+    def run_all():
+        if inp.is_cuda:
+            torch.cuda.set_device(inp.device)
+            side = torch.cuda.Stream(device=inp.device)
+            side.wait_event(ready)
+            with torch.cuda.stream(side):
+                stages(lambda thunk: _wait(thunk(False)))
+            side.synchronize()
+        else:
+            stages(lambda thunk: _wait(thunk(False)))
+    return Handle(works=[_ThreadWork(run_all)], keep=(inp, out))
 
 
 def broadcast_tensor(root: int, t: torch.Tensor, *, backend: Optional[str] = None, async_op: bool = False):
@@ -262,7 +326,43 @@ def reduce_tensor(root: int, inp: torch.Tensor, out: Optional[torch.Tensor] = No
     inp = _check_tensor(inp, "input")
     out = inp if same else _check_tensor(out, "output")
     b, _ = runtime.collective_span()
-    return _flat_reduce(inp, out, int(root), runtime.intra_members(b), backend, async_op)
+    outer = runtime.intra_members(b)
+    plan = _span_plan()
+    root = int(root)
+    if plan[0] == "flat" or not 0 <= root < len(outer) or S.rank not in plan[1]:
+        return _flat_reduce(inp, out, root, outer, backend, async_op)
+    # hierarchical span: sum inside every inner group to the member that shares the root's position, then
+    # across the groups to the root (cartesian); on a tree level the group roots hold the partial sums, the
+    # root's group root collects them and hands the result on inside its group
+    _, inner, inter, cartesian = plan
+    root_world = outer[root]
+    tmp = torch.empty_like(inp)
+    if cartesian:
+        pos = _position_in_group(root_world, b)
+        _wait(_flat_reduce(inp, tmp, pos, inner, backend, False))
+        if S.rank == inner[pos] and len(inter) > 1:
+            _wait(_flat_reduce(tmp, out if S.rank == root_world else tmp, inter.index(root_world), inter, backend, False))
+        elif S.rank == root_world:
+            out.copy_(tmp)
+    else:
+        _wait(_flat_reduce(inp, tmp, 0, inner, backend, False))
+        root_group = _group_of(root_world, b)
+        if S.rank == inner[0] and len(inter) > 1:
+            _wait(_flat_reduce(tmp, tmp, inter.index(root_group[0]), inter, backend, False))
+        if root_world in inner and root_world != inner[0]:
+            _wait(_flat_broadcast(tmp, 0, inner, backend, False))      # the group root passes the sum on to the root
+        if S.rank == root_world:
+            out.copy_(tmp)
+    return Handle() if async_op else None
+
+
+def _group_of(world_rank: int, outer_level: int) -> tuple:
+    """Inner group (world ranks, in group order) of the span's inner level that contains ``world_rank``."""
+    return runtime.group_of(runtime.collective_span()[1], world_rank)
+
+
+def _position_in_group(world_rank: int, outer_level: int) -> int:
+    return _group_of(world_rank, outer_level).index(world_rank)
 
 
 def sendreceive_tensor(t: torch.Tensor, src: int, dst: int, *, backend: Optional[str] = None):
@@ -283,10 +383,7 @@ def sendreceive_tensor(t: torch.Tensor, src: int, dst: int, *, backend: Optional
     use_host = t.is_cuda and backend == "gloo"
     buf = t.detach().cpu() if use_host else t
     recv = torch.empty_like(buf)
-    ops = [dist.P2POp(dist.isend, buf, members[dst], group=group),
-           dist.P2POp(dist.irecv, recv, members[src], group=group)]
-    for w in dist.batch_isend_irecv(ops):
-        w.wait()
+    gdist.sendrecv(buf, recv, members[dst], members[src], group)
     t.copy_(recv)
     return None
 
@@ -318,7 +415,7 @@ def allgather_tensor(inp: torch.Tensor, out: torch.Tensor, *, backend: Optional[
     else:
         counts_t = torch.zeros(N, dtype=torch.int64)
         counts_t[me] = inp.numel()
-        dist.all_reduce(counts_t, group=group)  # control plane (gloo)
+        gdist.all_reduce(counts_t, group)  # control plane (gloo)
         counts = counts_t.tolist()
     total = sum(counts)
     if out.numel() < total:
@@ -336,14 +433,14 @@ def allgather_tensor(inp: torch.Tensor, out: torch.Tensor, *, backend: Optional[
         src = inp.detach().cpu() if (be == "gloo" and inp.is_cuda) else inp
         outs = [torch.empty(c, dtype=src.dtype, device=src.device) for c in counts]
         if len(set(counts)) == 1:
-            dist.all_gather(outs, src.view(-1), group=group)
+            gdist.all_gather(outs, src.view(-1), group)
         else:
             # unequal counts: pad to the largest
             m = max(counts)
             pad = torch.zeros(m, dtype=src.dtype, device=src.device)
             pad[:src.numel()] = src.view(-1)
             bufs = [torch.empty_like(pad) for _ in range(N)]
-            dist.all_gather(bufs, pad, group=group)
+            gdist.all_gather(bufs, pad, group)
             outs = [bufs[k][:counts[k]] for k in range(N)]
         off = 0
         for k in range(N):
@@ -372,7 +469,7 @@ def reduce_scatter_tensor(inp: torch.Tensor, out: torch.Tensor, *, scale: float 
         return None
     group = runtime.group_for(members)
     if be == "nccl":
-        dist.reduce_scatter_tensor(out.view(-1), inp.view(-1), group=group)
+        gdist.reduce_scatter_tensor(out.view(-1), inp.view(-1), group)
         _scale_inplace(out, scale)
         return None
     tmp = inp.detach().cpu().clone() if inp.is_cuda else inp.clone()
@@ -381,7 +478,7 @@ def reduce_scatter_tensor(inp: torch.Tensor, out: torch.Tensor, *, scale: float 
         check(lib.tmpi_shm_allreduce(tmp.data_ptr(), tmp.data_ptr(), tmp.numel(), dtype_code(tmp.dtype),
                                      float(scale), arr, N, me, 0))
     else:
-        dist.all_reduce(tmp, group=group)
+        gdist.all_reduce(tmp, group)
         _scale_inplace(tmp, scale)
     n = out.numel()
     out.view(-1).copy_(tmp.view(-1)[me * n:(me + 1) * n])

@@ -68,6 +68,7 @@ int tmpi_comm_rank_in(int level, int inter);
 int tmpi_comm_key(int level, char* out, int cap);
 // members of the communicator under the cursor (level 0 is always intra)
 int tmpi_comm_current_members(int* out, int cap);
+int tmpi_comm_group_of(int level, int world_rank, int* out, int cap);   // members of that rank's group at `level` (0: none)
 int tmpi_comm_names(char* out, int cap);
 int tmpi_comm_has_inter_collective(int level);
 int tmpi_comm_has_intra_collective(int level);
@@ -91,6 +92,7 @@ int tmpi_handle_done(uint64_t handle);        // 1 done, 0 running, <0 unknown
 int tmpi_handle_stream_wait(uint64_t handle, void* stream);
 int tmpi_sync_all(void);                       // drain both pools
 int tmpi_handles_in_flight(void);
+uint64_t tmpi_test_lost_handle(void);   // fault injection: a handle that never completes (a dropped request)
 // test helpers: a host task that sleeps, then completes with `status`
 uint64_t tmpi_test_sleep_task(int pool, int ms, int status);
 

@@ -29,6 +29,7 @@ struct Level {
   std::string key;
   std::vector<int> intra;  // world ranks, group-rank order
   std::vector<int> inter;
+  std::vector<std::vector<int>> groups;  // every group of the split this rank took part in (world ranks, group-rank order)
   bool cartesian = true;
 };
 
@@ -109,6 +110,10 @@ int tmpi_comm_push(const char* keys, const int* parent_members, int parent_size,
   l.key = mine;
   l.cartesian = same_size && tunable("use_cartesian_communicator") != 0;
   for (int p : groups[my_group]) l.intra.push_back(parent_members[p]);
+  for (auto& grp : groups) {
+    l.groups.emplace_back();
+    for (int p : grp) l.groups.back().push_back(parent_members[p]);
+  }
   int my_intra = intra_rank_of[me];
   if (l.cartesian || my_intra == 0) {
     // every parent rank holding my intra rank, in parent-rank order
@@ -122,6 +127,25 @@ int tmpi_comm_push(const char* keys, const int* parent_members, int parent_size,
   // a fresh level becomes the cursor, as the reference's start() descends into it
   g.level = idx; g.inter = false;
   return idx;
+}
+
+// The group of the split at `level` that holds `world_rank` (world ranks in group-rank order); the number of
+// members, or 0 when that rank took no part in the split.
+int tmpi_comm_group_of(int level, int world_rank, int* out, int cap) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (level < 0 || level >= (int)g.levels.size()) return -fail(TMPI_ERR_INVALID, "communicator level %d out of range", level);
+  const Level& l = g.levels[level];
+  if (level == 0) {
+    int n = (int)l.intra.size();
+    for (int i = 0; i < n && i < cap; ++i) out[i] = l.intra[i];
+    return n;
+  }
+  for (auto& grp : l.groups)
+    if (index_of(grp, world_rank) >= 0) {
+      for (size_t i = 0; i < grp.size() && (int)i < cap; ++i) out[i] = grp[i];
+      return (int)grp.size();
+    }
+  return 0;
 }
 
 int tmpi_comm_num_levels(void) { std::lock_guard<std::mutex> lk(g_mu); return (int)g.levels.size(); }

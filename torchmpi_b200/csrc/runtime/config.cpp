@@ -64,6 +64,9 @@ Tunable g_tunables[] = {
   {"conv_own_3x3", {0}},                   // 3x3 convolutions on the implicit-GEMM kernel (1x1 always are)
   {"gemm_pair", {1}},                      // 256 x 256 tiles on CTA pairs (cta_group::2) where the shape allows
   {"ps_poll_us", {100}},
+  {"watchdog_interval_ms", {1000}},        // heartbeat period of the host watchdog (0: no watchdog)
+  {"watchdog_budget_ms", {10000}},         // a peer whose heartbeat stands still this long is declared lost
+  {"fault_drop_ps_requests", {0}},         // fault injection (host side): parameter-server requests are dropped
   {"trace", {0}},
 };
 constexpr int kNumTunables = sizeof(g_tunables) / sizeof(g_tunables[0]);

@@ -23,6 +23,7 @@ namespace {
 struct Handle {
   std::shared_future<int> fut;
   std::atomic<void*> event{nullptr};
+  bool lost = false;                      // fault injection: a request whose completion never arrives
 };
 
 std::mutex g_mu;
@@ -174,8 +175,32 @@ int tmpi_sync_all(void) {
     for (auto& kv : g_handles) ids.push_back(kv.first);
   }
   int st = TMPI_OK;
-  for (auto id : ids) { int s = tmpi_handle_wait(id, -1); if (s != TMPI_OK) st = s; }
+  for (auto id : ids) {
+    auto h = find(id);
+    if (h && h->lost) { erase(id); continue; }      // nothing will ever complete it
+    int s = tmpi_handle_wait(id, -1);
+    if (s != TMPI_OK) st = s;
+  }
   return st;
+}
+
+// Fault injection on the host: a handle that stands for a request that was dropped on the way - its task never
+// reports back.  Waiting on it must end in TMPI_ERR_TIMEOUT within the caller's budget.
+uint64_t tmpi_test_lost_handle(void) {
+  static std::vector<std::shared_ptr<std::promise<int>>> never;   // kept alive: a destroyed promise would complete the future
+  static std::mutex mu;
+  uint64_t id = g_next.fetch_add(1);
+  auto h = std::make_shared<Handle>();
+  auto prom = std::make_shared<std::promise<int>>();
+  h->fut = prom->get_future().share();
+  h->lost = true;
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    never.push_back(prom);
+  }
+  std::lock_guard<std::mutex> lk(g_mu);
+  g_handles[id] = h;
+  return id;
 }
 
 int tmpi_handles_in_flight(void) {

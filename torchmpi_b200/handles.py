@@ -44,7 +44,12 @@ class Handle:
         if self._done:
             return
         for i in self.ids:
-            check(lib.tmpi_handle_wait(i, timeout_ms))
+            st = lib.tmpi_handle_wait(i, timeout_ms)
+            if st == 3:        # TMPI_ERR_TIMEOUT: the peer or the request is gone; later calls must not wait again
+                from . import watchdog
+                from ._lib import last_error
+                watchdog.poison("an asynchronous operation timed out: " + last_error())
+            check(st)
         for w in self.works:
             w.wait()
         for f in self.finalizers:

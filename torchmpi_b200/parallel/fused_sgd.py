@@ -120,12 +120,14 @@ class FusedSGD:
         """Raises if a device-side wait of the optimizer lane gave up."""
         self.heap.check_status(LANE_OPT)
 
-    # ---- checkpointing (collective: every rank calls)
+    # ---- checkpointing (collective over the optimizer's members: every one of them calls)
     def state_dict(self) -> dict:
-        from .. import collectives
-        out = {"step": self.step_count, "buckets": []}
+        """Full (unsharded) fp32 master weights and momentum per bucket, gathered over the ranks that share this
+        optimizer, with the layout that produced them (bucket lengths, group size, parameter offsets and sizes),
+        so that a job with another group size or bucket size can still place every parameter's state."""
+        out = {"step": self.step_count, "group_size": self.N, "buckets": []}
         for b in self.buckets.buckets:
-            entry = {}
+            entry = {"numel": b.numel, "offsets": list(b.offsets), "sizes": [p.numel() for p in b.params]}
             for key in ("master", "momentum"):
                 shard = b.extra[key]
                 if shard is None:
@@ -133,7 +135,8 @@ class FusedSGD:
                     continue
                 full = torch.empty(b.numel, dtype=torch.float32, device=shard.device)
                 if self.N > 1:
-                    collectives.allgather_tensor(shard, full)
+                    self.heap.allgatherv(shard, full, [shard.numel()] * self.N, self.members)
+                    torch.cuda.current_stream().synchronize()
                 else:
                     full.copy_(shard)
                 entry[key] = full.cpu()
@@ -141,11 +144,46 @@ class FusedSGD:
         return out
 
     def load_state_dict(self, state: dict) -> None:
+        """Loads a ``state_dict``.  Same layout: this rank's shard is cut out of every bucket.  Another group size
+        or bucket size: the state is re-placed parameter by parameter (the parameters and their order must be the
+        same); anything else raises."""
+        saved = state["buckets"]
+        mine = self.buckets.buckets
+        same = len(saved) == len(mine) and all(e.get("numel", b.numel) == b.numel for e, b in zip(saved, mine)) \
+            and state.get("group_size", self.N) == self.N
+        if same:
+            for b, entry in zip(mine, saved):
+                for key in ("master", "momentum"):
+                    if b.extra[key] is not None and entry.get(key) is not None:
+                        b.extra[key].copy_(entry[key][self._shard(b)])
+            self.step_count = int(state["step"])
+            return
+        if any("sizes" not in e for e in saved):
+            raise ValueError("optimizer state was saved with another bucket layout and carries no per-parameter "
+                             "layout; it cannot be re-placed")
+        old_sizes = [n for e in saved for n in e["sizes"]]
+        new_sizes = [p.numel() for b in mine for p in b.params]
+        if old_sizes != new_sizes:
+            raise ValueError(f"optimizer state holds {len(old_sizes)} parameters of other sizes than this model's "
+                             f"{len(new_sizes)}; refusing to load misaligned state")
+        for key in ("master", "momentum"):
+            pieces = []
+            for e in saved:
+                for off, n in zip(e["offsets"], e["sizes"]):
+                    pieces.append(None if e.get(key) is None else e[key][off:off + n])
+            it = iter(pieces)
+            for b in mine:
+                if b.extra[key] is None:
+                    for _ in b.params:
+                        next(it)
+                    continue
+                full = torch.zeros(b.numel, dtype=torch.float32)
+                for off, p in zip(b.offsets, b.params):
+                    piece = next(it)
+                    if piece is not None:
+                        full[off:off + p.numel()] = piece
+                b.extra[key].copy_(full[self._shard(b)])
         self.step_count = int(state["step"])
-        for b, entry in zip(self.buckets.buckets, state["buckets"]):
-            for key in ("master", "momentum"):
-                if b.extra[key] is not None and entry.get(key) is not None:
-                    b.extra[key].copy_(entry[key][self._shard(b)])
 
     def remove_hooks(self) -> None:
         self.buckets.remove_hooks()

@@ -147,6 +147,8 @@ class CudaHeap:
         check(lib.tmpi_cuda_collective_status(lane, C.byref(code), C.byref(where), C.byref(peer)))
         if code.value:
             cls = _lib.TimeoutError_ if code.value == _lib.ERR_TIMEOUT else _lib.TorchMPIError
+            from .. import watchdog
+            watchdog.poison(f"device-side wait gave up at point {where.value} waiting for rank {peer.value}")
             raise cls(code.value, f"device-side wait gave up at point {where.value} waiting for rank {peer.value}")
 
     # ---- collectives on tensors

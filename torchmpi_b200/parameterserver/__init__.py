@@ -23,7 +23,7 @@ from typing import Callable, List, Optional, Sequence
 
 import torch
 
-from .. import _lib, cache, runtime
+from .. import _lib, cache, config, runtime
 from .._lib import lib, check, dtype_code
 from ..handles import Handle, sync_handle, sync_handles as _sync_handles
 from ..runtime import S
@@ -76,6 +76,8 @@ class ParameterServer:
         if rule not in RULES:
             raise ValueError(f"unknown update rule '{rule}' (expected one of {sorted(RULES)})")
         self._check(t)
+        if config.get("fault_drop_ps_requests"):      # host-side fault injection: the request never reports back
+            return Handle(ids=[lib.tmpi_test_lost_handle()])
         if self.on_gpu:
             return S.cuda_heap.ps_push(self.impl, t, RULES[rule])
         host = self._to_host(t)
@@ -83,6 +85,8 @@ class ParameterServer:
 
     def receive(self, t: torch.Tensor) -> Handle:
         self._check(t)
+        if config.get("fault_drop_ps_requests"):
+            return Handle(ids=[lib.tmpi_test_lost_handle()])
         if self.on_gpu:
             return S.cuda_heap.ps_pull(self.impl, t)
         if t.is_cuda:

@@ -46,6 +46,8 @@ class State:
     need_inter_node_collectives = False
     num_communicators = 1
     job_id = ""
+    host_names: tuple = ()        # host name of every world rank (gathered once at start)
+    push_seq: dict = {}           # parent members -> number of splits made from that communicator
 
 
 S = State()
@@ -55,6 +57,8 @@ plan_cache: dict = {}       # derived from communicators / span / tunables; clea
 def _require_started() -> None:
     if not S.started:
         raise RuntimeError("torchmpi_b200.start() has not been called")
+    from . import watchdog
+    watchdog.check()          # a lost peer or an expired wait poisons the job: fail at once, do not wait again
 
 
 # ---------------------------------------------------------------- groups
@@ -71,12 +75,48 @@ def group_for(members: Sequence[int]):
         raise RuntimeError(f"no process group for ranks {members}; communicators are created with push_communicator") from None
 
 
-def _ensure_groups(all_member_lists) -> None:
-    """Collective over the world: creates the missing groups in one global order."""
-    wanted = sorted({tuple(m) for m in all_member_lists if 1 < len(m) < S.world})
-    for m in wanted:
-        if m not in S.groups:
-            S.groups[m] = dist.new_group(list(m), backend=_backend_string())
+def _ensure_groups(member_lists, world_collective: bool) -> None:
+    """Makes the groups of a new communicator level.
+
+    ``world_collective``: the split was made by every rank of the job at once (the parent is the world), so
+    ordinary process groups can be created, by all ranks in one global order, for ALL groups of the split.
+    Otherwise only the members are here: the groups of this rank become ``gdist.LightGroup`` objects."""
+    from .gdist import LightGroup
+    if world_collective:
+        for m in sorted({tuple(m) for m in member_lists if 1 < len(m) < S.world}):
+            if m not in S.groups or isinstance(S.groups[m], LightGroup):
+                S.groups[m] = dist.new_group(list(m), backend=_backend_string())
+        return
+    for m in member_lists:
+        m = tuple(m)
+        if 1 < len(m) < S.world and S.rank in m and m not in S.groups:
+            S.groups[m] = LightGroup(m, S.rank)
+
+
+def _all_groups_of_split(parent, keys, cartesian_wanted: bool):
+    """Every intra and inter group of the split of ``parent`` by ``keys`` (one key per parent member), the way
+    ``tmpi_comm_push`` forms them: groups in sorted-key order, members in parent order."""
+    order = sorted(range(len(parent)), key=lambda i: (keys[i], i))
+    groups, last = [], None
+    for i in order:
+        if keys[i] != last:
+            groups.append([])
+            last = keys[i]
+        groups[-1].append(parent[i])
+    same = all(len(g) == len(groups[0]) for g in groups)
+    out = [tuple(g) for g in groups]
+    if same and cartesian_wanted:
+        out += [tuple(g[j] for g in groups) for j in range(len(groups[0]))]
+    else:
+        out.append(tuple(g[0] for g in groups))
+    # inter groups list their members in parent order
+    pos = {r: i for i, r in enumerate(parent)}
+    return [tuple(sorted(g, key=lambda r: pos[r])) for g in out]
+
+
+def _store():
+    from torch.distributed import distributed_c10d
+    return distributed_c10d._get_default_store()
 
 
 def _backend_string() -> str:
@@ -102,6 +142,16 @@ def current_members() -> tuple:
     return tuple(buf[i] for i in range(n))
 
 
+def group_of(level: int, world_rank: int) -> tuple:
+    """Members (world ranks, group order) of the group that ``world_rank`` joined in the split at ``level``; ``()``
+    when that rank was not part of the split."""
+    buf = (C.c_int * MAX_WORLD)()
+    n = lib.tmpi_comm_group_of(int(level), int(world_rank), buf, MAX_WORLD)
+    if n < 0:
+        check(-n)
+    return tuple(buf[i] for i in range(n))
+
+
 def intra_members(level: int) -> tuple:
     return _members(level, False)
 
@@ -113,10 +163,10 @@ def inter_members(level: int) -> tuple:
 def push_communicator(key: str) -> int:
     """Splits the communicator under the cursor by ``key`` and descends into the new level.
 
-    Ranks with equal keys form the new intra group.  Every rank of the world has
-    to make this call at the same point of the program (with its own key), since
-    process groups are created collectively; the reference only requires the
-    members of the current communicator (lib/c_api.h:42-47).
+    Ranks with equal keys form the new intra group.  Only the members of the current communicator make
+    this call (each with its own key), as in the reference (lib/c_api.h:42-47,
+    lib/resources.cpp:187-350): the keys travel through the job's key-value store under a name scoped by
+    the parent communicator, and the process groups of the new level are created by their members alone.
     Returns the new level.
     """
     _require_started()
@@ -124,22 +174,30 @@ def push_communicator(key: str) -> int:
     if len(key.encode()) >= KEY_LEN:
         raise ValueError(f"communicator key longer than {KEY_LEN - 1} bytes")
     parent = current_members()
-    table = [None] * S.world
-    dist.all_gather_object(table, (parent, key))
     keys = bytearray(KEY_LEN * len(parent))
-    for i, r in enumerate(parent):
-        p, k = table[r]
-        if tuple(p) != parent:
-            raise RuntimeError(f"rank {r} pushed a communicator from a different parent {p} than rank {S.rank} ({parent})")
-        kb = k.encode()
-        keys[i * KEY_LEN:i * KEY_LEN + len(kb)] = kb
+    all_keys = [key]
+    if len(parent) > 1:
+        seq = S.push_seq.get(parent, 0)
+        S.push_seq[parent] = seq + 1
+        prefix = f"tmpi/{S.job_id}/push/{'.'.join(map(str, parent))}/{seq}/"
+        store = _store()
+        store.set(prefix + str(S.rank), key)
+        for i, r in enumerate(parent):
+            kb = key.encode() if r == S.rank else bytes(store.get(prefix + str(r)))      # blocks until rank r has pushed
+            keys[i * KEY_LEN:i * KEY_LEN + len(kb)] = kb
+        all_keys = [bytes(keys[i * KEY_LEN:(i + 1) * KEY_LEN]).rstrip(b"\0").decode() for i in range(len(parent))]
+    else:
+        kb = key.encode()
+        keys[:len(kb)] = kb
     level = lib.tmpi_comm_push(bytes(keys), _lib.int_array(parent), len(parent), key.encode())
     if level < 0:
         check(level)
-    mine = (intra_members(level), inter_members(level))
-    everyone = [None] * S.world
-    dist.all_gather_object(everyone, mine)
-    _ensure_groups([g for pair in everyone for g in pair])
+    if len(parent) == S.world:
+        from . import config
+        cart = bool(config.get("use_cartesian_communicator"))
+        _ensure_groups(_all_groups_of_split(parent, all_keys, cart), world_collective=True)
+    else:
+        _ensure_groups([intra_members(level), inter_members(level)], world_collective=False)
     S.num_communicators = lib.tmpi_comm_num_levels()
     plan_cache.clear()
     return level
@@ -198,10 +256,7 @@ def num_nodes_in_communicator() -> int:
     only right when ranks are grouped by host (lib/torch_mpi.cpp:338-342).
     """
     _require_started()
-    members = current_members()
-    names = [None] * S.world
-    dist.all_gather_object(names, S.host_name)
-    return len({names[r] for r in members})
+    return len({S.host_names[r] for r in current_members()})      # host names were gathered once at start
 
 
 def rank() -> int:
@@ -229,4 +284,5 @@ def barrier() -> None:
     g = group_for(current_members())
     if g is not None:
         # a host barrier on the gloo side of the group (the control plane), like MPI_Barrier
-        dist.all_reduce(torch.zeros(1), group=g)
+        from . import gdist
+        gdist.all_reduce(torch.zeros(1), g)

@@ -12,6 +12,7 @@ import torch
 import torch.distributed as dist
 
 from . import runtime
+from . import gdist
 from .runtime import S
 
 _TYPES = {"uint8_t": torch.uint8, "char": torch.int8, "short": torch.int16, "int": torch.int32,
@@ -35,21 +36,21 @@ def _mk(tname: str, dt: torch.dtype):
         members, g = _group()
         t = torch.tensor([v], dtype=dt)
         if g is not None:
-            dist.all_reduce(t, group=g)
+            gdist.all_reduce(t, g)
         return _py(t)
 
     def broadcast(root, v):
         members, g = _group()
         t = torch.tensor([v], dtype=dt)
         if g is not None:
-            dist.broadcast(t, src=members[root], group=g)
+            gdist.broadcast(t, members[root], g)
         return _py(t)
 
     def reduce(root, v):
         members, g = _group()
         t = torch.tensor([v], dtype=dt)
         if g is not None:
-            dist.reduce(t, dst=members[root], group=g)
+            gdist.reduce(t, members[root], g)
         return _py(t) if members[root] == S.rank else v
 
     def sendreceive(v, src, dst):
@@ -58,9 +59,7 @@ def _mk(tname: str, dt: torch.dtype):
         if g is None or (src == me and dst == me):
             return v
         t, r = torch.tensor([v], dtype=dt), torch.zeros(1, dtype=dt)
-        ops = [dist.P2POp(dist.isend, t, members[dst], group=g), dist.P2POp(dist.irecv, r, members[src], group=g)]
-        for w in dist.batch_isend_irecv(ops):
-            w.wait()
+        gdist.sendrecv(t, r, members[dst], members[src], g)
         return _py(r)
 
     for op, fn in (("allreduce", allreduce), ("broadcast", broadcast), ("reduce", reduce), ("sendreceive", sendreceive)):
