@@ -23,6 +23,16 @@ def world_sizes():
     return [w for w in (2, 4, 8) if w <= n] or [2]
 
 
+def all_world_sizes():
+    """Every world size the collective matrix runs at: the powers of two and an odd one, as the reference loops
+    over n = 2 .. GPUs (scripts/test_gpu.sh:47-50).  ``TORCHMPI_TEST_WORLDS=2,8`` narrows the list."""
+    n = ngpus()
+    env = os.environ.get("TORCHMPI_TEST_WORLDS")
+    if env:
+        return [int(w) for w in env.split(",") if int(w) <= max(n, 2)]
+    return [w for w in (2, 3, 4, 8) if w <= n] or [2]
+
+
 def _gather_equal(mpi, t):
     import torch.distributed as dist
     outs = [torch.empty_like(t) for _ in range(mpi.world_size())]
@@ -131,11 +141,11 @@ def _collectives(rank, world, backend):
     return info
 
 
+@pytest.mark.parametrize("world", all_world_sizes())
 @pytest.mark.parametrize("backend", ["ipc", "vmm"])
-def test_gpu_collectives(backend):
-    for world in world_sizes()[:1] if backend == "ipc" else world_sizes()[-1:]:
-        res = run_ranks(_collectives, world, backend, timeout=600)
-        print(backend, world, res[0])
+def test_gpu_collectives(backend, world):
+    res = run_ranks(_collectives, world, backend, timeout=600)
+    print(backend, world, res[0])
 
 
 def _engine(rank, world):
@@ -258,6 +268,8 @@ def _absent_peer(rank, world):
     torch.cuda.synchronize()
     mpi.barrier()
     outcome = "skipped"
+    from torch.distributed import distributed_c10d
+    store = distributed_c10d._get_default_store()
     if rank == 0:
         mpi.p2p.allreduce_tensor(t)          # nobody answers
         torch.cuda.synchronize()
@@ -267,8 +279,16 @@ def _absent_peer(rank, world):
         except mpi.TimeoutError as e:
             outcome = "timeout: " + str(e)
         assert float(torch.ones(8, device=dev).sum()) == 8.0     # context still answers
-    mpi.barrier()                            # both ranks leave between steps, nothing in flight
-    mpi.stop()
+        try:                                  # the job is poisoned: the next collective fails at once
+            mpi.p2p.allreduce_tensor(t)
+            outcome += " / not poisoned"
+        except mpi.CommunicatorPoisoned:
+            pass
+        store.set("tmpi_test/absent_peer_done", "1")
+    else:
+        store.get("tmpi_test/absent_peer_done")                  # learns of the failure on the host, launches nothing
+        mpi.watchdog.poison("rank 0 reported a failed collective")
+    mpi.stop()                               # both ranks leave between steps, nothing in flight, no barrier
     return outcome
 
 

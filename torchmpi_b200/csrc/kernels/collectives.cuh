@@ -396,7 +396,7 @@ __device__ void body_bcast_mc(const CollArgs& a, int* s_abort) {
     if (P.me == a.root) {
       const size_t stride = (size_t)gridDim.x * blockDim.x;
       const T* src = at<T>(P.base[P.me], a.out_off);
-      constexpr int U = 4;
+      constexpr int U = 8;             // bytes in flight per thread: the loads are local, the stores are posted
       size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
       for (; i + (U - 1) * stride < nv; i += U * stride) {
         Pack<T, V> x[U];

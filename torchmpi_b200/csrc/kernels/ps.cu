@@ -75,6 +75,86 @@ __device__ __forceinline__ void ps_range(T* shard, T* data, size_t len, int rule
   }
 }
 
+// All owners inside the inner loop: a thread applies vector i of EVERY shard before it moves on, so that
+// loads from (or reductions into) all peers are in flight at once, as the two-shot allreduce does, instead of
+// the whole grid visiting one owner at a time.  NP owners, known at compile time; every shard's slice of the
+// client's tensor starts on 16 bytes.  U rounds per iteration keep about eight 16-byte transfers in flight.
+template <typename T, int V, int NP>
+__device__ __forceinline__ void ps_all_owners(const PsArgs& a, T* data, size_t t0, size_t stride) {
+  const Peers& P = a.P;
+  T* shard[NP];
+  T* mine[NP];
+  size_t nv[NP], maxnv = 0;
+#pragma unroll
+  for (int j = 0; j < NP; ++j) {
+    const int m = (P.me + j) % NP;            // rotate: clients start at different owners
+    size_t b, e;
+    shard_range(a.n, NP, m, &b, &e);
+    shard[j] = at<T>(P.base[m], a.shard_off);
+    mine[j] = data + b;
+    nv[j] = (e - b) / V;
+    maxnv = nv[j] > maxnv ? nv[j] : maxnv;
+  }
+  constexpr int U = NP >= 8 ? 1 : 8 / NP;
+  const int rule = a.rule;
+  Pack<T, V> z;
+#pragma unroll
+  for (int k = 0; k < V; ++k) z.v[k] = from_acc<T>((typename AccOf<T>::type)0);
+  for (size_t i = t0; i < maxnv; i += U * stride) {
+    Pack<T, V> x[U][NP];
+    if (rule < 0) {                           // pull: all loads first
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int j = 0; j < NP; ++j)
+          if (i + u * stride < nv[j]) x[u][j] = ld_pack_peer<T, V>(shard[j] + (i + u * stride) * V);
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int j = 0; j < NP; ++j)
+          if (i + u * stride < nv[j]) st_pack<T, V>(mine[j] + (i + u * stride) * V, x[u][j]);
+    } else {
+      if (rule != 0) {
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+#pragma unroll
+          for (int j = 0; j < NP; ++j)
+            if (i + u * stride < nv[j]) x[u][j] = ld_pack<T, V>(mine[j] + (i + u * stride) * V);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int j = 0; j < NP; ++j)
+          if (i + u * stride < nv[j]) {
+            T* dst = shard[j] + (i + u * stride) * V;
+            if (rule == 0) st_pack_peer<T, V>(dst, z);
+            else if (rule == 1) st_pack_peer<T, V>(dst, x[u][j]);
+            else red_add_pack<T, V>(dst, x[u][j]);
+          }
+    }
+  }
+  // the elements of each shard beyond its last full pack
+#pragma unroll
+  for (int j = 0; j < NP; ++j) {
+    const int m = (P.me + j) % NP;
+    size_t b, e;
+    shard_range(a.n, NP, m, &b, &e);
+    const size_t body = nv[j] * V;
+    ps_range<T, 1>(shard[j] + body, mine[j] + body, (e - b) - body, rule, t0, stride);
+  }
+}
+
+// true when the slice of every owner starts on a 16-byte boundary of the client's tensor
+template <typename T>
+__device__ __forceinline__ bool ps_slices_aligned(const PsArgs& a, const T* data) {
+  for (int m = 0; m < a.P.n; ++m) {
+    size_t b, e;
+    shard_range(a.n, a.P.n, m, &b, &e);
+    if ((uintptr_t)(data + b) & 15) return false;
+  }
+  return true;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(512) ps_kernel(const __grid_constant__ PsArgs a) {
   const Peers& P = a.P;
@@ -82,6 +162,13 @@ __global__ void __launch_bounds__(512) ps_kernel(const __grid_constant__ PsArgs 
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   const size_t t0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   T* data = reinterpret_cast<T*>(a.data);
+  if ((P.n == 2 || P.n == 4 || P.n == 8) && ps_slices_aligned<T>(a, data)) {
+    if (P.n == 2) ps_all_owners<T, V, 2>(a, data, t0, stride);
+    else if (P.n == 4) ps_all_owners<T, V, 4>(a, data, t0, stride);
+    else ps_all_owners<T, V, 8>(a, data, t0, stride);
+    __threadfence_system();
+    return;
+  }
   for (int j = 0; j < P.n; ++j) {
     const int m = (P.me + j) % P.n;          // start at my own shard: clients spread over owners
     size_t b, e;

@@ -44,6 +44,9 @@ Tunable g_tunables[] = {
   {"oneshot_max_bytes", {512 << 10}},      // <= : one-shot push allreduce
   {"nvls_min_bytes", {1 << 20}},           // >= : multimem allreduce when multicast is bound
   {"comm_max_ctas", {64}},                 // CTAs of a stand-alone collective kernel
+  {"broadcast_algo", {0}},                 // heap broadcasts: 0 by size, 1 pull from the root, 2 scatter + all-gather, 3 multicast store
+  {"bcast_max_ctas", {128}},               // CTAs of the multicast-store broadcast (only the root moves data)
+  {"nvls_max_ctas", {64}},                 // CTAs of the multimem allreduce
   {"ps_max_ctas", {148}},                  // CTAs of a parameter-server push / pull kernel (one per SM: +30 % push bandwidth over 64)
   {"opt_max_ctas", {32}},                  // CTAs of the fused allreduce+SGD kernel (runs beside backward)
   {"comm_threads", {512}},

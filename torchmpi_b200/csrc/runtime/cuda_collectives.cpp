@@ -47,11 +47,12 @@ static int pick_algo(int algo, size_t bytes, int dtype, const tmpi_group_t* g) {
 // Launches one collective op for every rank this process drives (1, or all in emulation).
 // per_rank(r, me, &args) fills the op-specific fields for heap rank members[me].
 template <typename Fill>
-static int run_op(int op, int dtype, const tmpi_group_t* g, int vec, size_t items, cudaStream_t s, Fill fill) {
+static int run_op(int op, int dtype, const tmpi_group_t* g, int vec, size_t items, cudaStream_t s, Fill fill,
+                  const char* cta_cap = "comm_max_ctas") {
   CudaHeap& h = heap();
   int threads = (int)tunable("comm_threads");
   if (threads < 32 || threads > 1024) threads = 512;
-  int grid = grid_for(items, threads);
+  int grid = grid_for(items, threads, cta_cap);
   int nb = barriers_used(op, g->nmembers);
   std::lock_guard<std::mutex> lk(h.mu);
   if (h.emulated) {
@@ -109,7 +110,7 @@ static int allreduce_heap(size_t in_off, size_t out_off, size_t n, int dtype, do
   int op = algo == 3 ? OP_AR_NVLS : OP_AR_TWOSHOT;
   return run_op(op, dtype, g, vec, items / g->nmembers + 1, s, [&](int, CollArgs* a) {
     a->in_off = in_off; a->out_off = out_off; a->n = n; a->scale = (float)scale;
-  });
+  }, algo == 3 ? "nvls_max_ctas" : "comm_max_ctas");
 }
 
 // ---- allreduce on arbitrary device pointers
@@ -178,6 +179,7 @@ static int broadcast_heap(size_t off, size_t n, int dtype, int root, const tmpi_
   // with two ranks a multicast store also sends the data back to the root: the pull is faster there
   bool mc_ok = h.mc_base && whole_heap(g) && vec && tunable("use_nvls");
   const bool mc_auto = mc_ok && g->nmembers > 2;
+  if (algo == 0) algo = (int)tunable("broadcast_algo");      // 0 auto, 1 pull, 2 chunked, 3 multicast store
   if (algo == 3 && mc_ok) op = OP_BCAST_MC;
   else if (algo == 2) op = OP_BCAST_CHUNKED;
   else if (algo == 0) {
@@ -186,7 +188,7 @@ static int broadcast_heap(size_t off, size_t n, int dtype, int root, const tmpi_
   }
   return run_op(op, TMPI_U8, g, vec, items, s, [&](int, CollArgs* a) {
     a->out_off = off; a->n = bytes; a->root = root;
-  });
+  }, op == OP_BCAST_MC ? "bcast_max_ctas" : "comm_max_ctas");
 }
 
 static int broadcast_any(void* buf, size_t n, int dtype, int root, const tmpi_group_t* g, cudaStream_t s) {

@@ -83,6 +83,9 @@ def run(args) -> list:
         config.set("staging_bytes", max(config.get("staging_bytes"), min(args.max_bytes, 1 << 30)))
         if args.ctas:
             config.set("comm_max_ctas", args.ctas)
+    for kv in args.set:
+        name, _, value = kv.partition("=")
+        config.set(name, int(value))
     mpi.start(with_cuda=use_gpu, with_cartesian_communicator=args.cartesian)
     rank, n, dev = mpi.rank(), mpi.size(), mpi.device
     heap = mpi._S.cuda_heap
@@ -155,7 +158,10 @@ def run(args) -> list:
                         row = {"op": op, "variant": variant, "dtype": dname, "bytes": numel * es, "world": n,
                                "us": round(sec * 1e6, 2), "alg_gbs": round(numel * es / sec / 1e9, 2),
                                "bus_gbs": round(bw, 2), "roofline_frac": round(bw / roof, 3),
+                               "roofline_frac_900": round(bw / roofline_bus_bw(op, variant, n, 900.0), 3),
                                "symmetric": bool(args.symmetric)}
+                        if args.tag:
+                            row["tag"] = args.tag
                         rows.append(row)
                         if rank == 0:
                             print(json.dumps(row), flush=True)
@@ -186,7 +192,10 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--ctas", type=int, default=0, help="CTAs per collective kernel (default: the comm_max_ctas tunable)")
-    ap.add_argument("--link-gbs", type=float, default=770.0)
+    ap.add_argument("--link-gbs", type=float, default=770.0,
+                    help="measured per-direction link rate for roofline_frac (the nominal 900 GB/s is reported beside it)")
+    ap.add_argument("--set", action="append", default=[], metavar="NAME=VALUE", help="set a runtime tunable (sweeps)")
+    ap.add_argument("--tag", default="", help="copied into every result row")
     run(ap.parse_args())
 
 
