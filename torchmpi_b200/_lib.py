@@ -13,7 +13,8 @@ from pathlib import Path
 import torch
 
 _PKG = Path(__file__).resolve().parent
-_LIB_PATH = _PKG / "lib" / "libtorchmpi_b200.so"
+_DEBUG_BOUNDS = bool(os.environ.get("TORCHMPI_DEBUG_BOUNDS"))     # the build with recording bounds checks
+_LIB_PATH = _PKG / "lib" / ("libtorchmpi_b200_dbg.so" if _DEBUG_BOUNDS else "libtorchmpi_b200.so")
 
 
 class TorchMPIError(RuntimeError):
@@ -149,6 +150,7 @@ _CUDA_PROTOS = {
     "tmpi_cuda_heap_alloc": (_sz, [_sz, _sz]),
     "tmpi_cuda_heap_reset_allocator": (_i, [_sz]),
     "tmpi_cuda_heap_world": (_i, []),
+    "tmpi_debug_bounds_build": (_i, []),
     "tmpi_cuda_heap_layout": (_i, [C.POINTER(C.c_size_t), _i]),
     "tmpi_cuda_heap_rank": (_i, []),
     "tmpi_cuda_allreduce": (_i, [_vp, _vp, _sz, _i, _d, _gp, _i, _vp]),

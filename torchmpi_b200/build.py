@@ -22,8 +22,11 @@ from pathlib import Path
 
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
-OBJ = PKG.parent / "build" / "obj"
-LIB = PKG / "lib" / "libtorchmpi_b200.so"
+# TORCHMPI_DEBUG_BOUNDS=1 selects the debug build: every peer load / store of the multi-rank kernels checks its
+# address against the mapped heaps, records the first violation in the status word and skips the access
+DEBUG_BOUNDS = bool(os.environ.get("TORCHMPI_DEBUG_BOUNDS"))
+OBJ = PKG.parent / "build" / ("obj_dbg" if DEBUG_BOUNDS else "obj")
+LIB = PKG / "lib" / ("libtorchmpi_b200_dbg.so" if DEBUG_BOUNDS else "libtorchmpi_b200.so")
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC,-Wall,-Wno-unused-function",
@@ -43,7 +46,7 @@ def sources() -> list[Path]:
     return out
 
 
-STAMP = PKG / "lib" / "build.stamp"
+STAMP = PKG / "lib" / ("build_dbg.stamp" if DEBUG_BOUNDS else "build.stamp")
 
 
 def source_hash() -> str:
@@ -90,6 +93,8 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
 def _build_locked(cc: str, force: bool, verbose: bool, ptxas_info: bool) -> Path:
     hm = headers_mtime()
     extra = ["-Xptxas", "-v"] if ptxas_info else []
+    if DEBUG_BOUNDS:
+        extra.append("-DTMPI_DEBUG_BOUNDS")
     todo, objs = [], []
     for src in sources():
         obj = OBJ / (src.parent.name + "_" + src.stem + ".o")

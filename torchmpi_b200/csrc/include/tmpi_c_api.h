@@ -149,6 +149,7 @@ size_t tmpi_cuda_heap_capacity(void);
 size_t tmpi_cuda_heap_alloc(size_t bytes, size_t align);  // symmetric offset; (size_t)-1 on failure
 int tmpi_cuda_heap_reset_allocator(size_t keep_bytes);
 int tmpi_cuda_heap_world(void);
+int tmpi_debug_bounds_build(void);                       // 1: peer accesses are bounds-checked and recorded (debug build)
 // out[0..n): slots_off, slot_bytes, bounce_off, bounce_bytes, arena_off, total_bytes (per-rank mapping)
 int tmpi_cuda_heap_layout(size_t* out, int n);
 int tmpi_cuda_heap_rank(void);

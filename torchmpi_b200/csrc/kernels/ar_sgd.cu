@@ -121,6 +121,7 @@ template <typename T, int V>
 __global__ void __launch_bounds__(512) ar_sgd_kernel(const __grid_constant__ SgdArgs a) {
   __shared__ int s_abort;
   if (threadIdx.x == 0) s_abort = 0;
+  TMPI_DBG_ENTER(a.P, nullptr, 0, nullptr, 0);
   __syncthreads();
   body_ar_sgd<T, V>(a, &s_abort);
 }
@@ -129,6 +130,7 @@ template <typename T, int V>
 __global__ void __launch_bounds__(512) ar_sgd_kernel_emu(const __grid_constant__ SgdArgsPack pack) {
   __shared__ int s_abort;
   if (threadIdx.x == 0) s_abort = 0;
+  TMPI_DBG_ENTER(pack.r[blockIdx.y].P, nullptr, 0, nullptr, 0);
   __syncthreads();
   body_ar_sgd<T, V>(pack.r[blockIdx.y], &s_abort);
 }

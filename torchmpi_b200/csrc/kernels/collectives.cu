@@ -30,6 +30,8 @@ template <int OP, typename T, int V>
 __global__ void __launch_bounds__(1024) coll_kernel(const __grid_constant__ CollArgs a) {
   __shared__ int s_abort;
   if (threadIdx.x == 0) s_abort = 0;
+  // local tensors of ops that take ordinary pointers: generous windows (the strict check is on the heaps)
+  TMPI_DBG_ENTER(a.P, a.in, a.n * sizeof(T) * kMaxPeers, a.out, a.n * sizeof(T) * kMaxPeers);
   __syncthreads();
   run_body<OP, T, V>(a, &s_abort);
 }
@@ -38,6 +40,8 @@ template <int OP, typename T, int V>
 __global__ void __launch_bounds__(1024) coll_kernel_emu(const __grid_constant__ CollArgsPack pack) {
   __shared__ int s_abort;
   if (threadIdx.x == 0) s_abort = 0;
+  TMPI_DBG_ENTER(pack.r[blockIdx.y].P, pack.r[blockIdx.y].in, pack.r[blockIdx.y].n * sizeof(T) * kMaxPeers,
+                 pack.r[blockIdx.y].out, pack.r[blockIdx.y].n * sizeof(T) * kMaxPeers);
   __syncthreads();
   run_body<OP, T, V>(pack.r[blockIdx.y], &s_abort);
 }

@@ -20,6 +20,7 @@
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include "vec.cuh"
 
 namespace tmpi {
 
@@ -42,6 +43,7 @@ struct Peers {
   int* status;                  // host-mapped int[4]; status[0] != 0 after a failure
   unsigned long long budget_ns;
   char* mc_base;                // multicast mapping of the heap (nullptr when absent)
+  size_t heap_bytes;            // bytes of every member's mapping (debug bounds checks)
 };
 
 __device__ __forceinline__ uint32_t* flag_ptr(char* heap_base, int lane, int block, int writer) {
@@ -83,6 +85,26 @@ __device__ __forceinline__ void report(const Peers& P, int code, int where, int 
     __threadfence_system();
   }
 }
+
+#ifdef TMPI_DEBUG_BOUNDS
+// Kernel entry in the debug build: publishes the address ranges that peer accesses of this launch may touch
+// (every thread writes the same values; a block-wide barrier follows in the caller).
+__device__ __forceinline__ void dbg_enter(const Peers& P, const void* local0, size_t len0, const void* local1, size_t len1) {
+  if (threadIdx.x == 0) {
+    int k = 0;
+    for (int i = 0; i < P.n; ++i) { g_dbg.lo[k] = P.base[i]; g_dbg.len[k++] = P.heap_bytes; }
+    g_dbg.lo[k] = P.mc_base; g_dbg.len[k++] = P.heap_bytes;
+    g_dbg.lo[k] = (const char*)local0; g_dbg.len[k++] = len0;
+    g_dbg.lo[k] = (const char*)local1; g_dbg.len[k++] = len1;
+    g_dbg.status = P.status;
+    g_dbg.n = k;
+    __threadfence();
+  }
+}
+#define TMPI_DBG_ENTER(P, l0, n0, l1, n1) dbg_enter((P), (l0), (n0), (l1), (n1))
+#else
+#define TMPI_DBG_ENTER(P, l0, n0, l1, n1)
+#endif
 
 // Barrier number k (1-based within the launch) of this block with the same block of every peer.
 // All threads of the block must call it.  Returns false when a wait ran out: the caller must

@@ -162,6 +162,10 @@ __global__ void __launch_bounds__(512) ps_kernel(const __grid_constant__ PsArgs 
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   const size_t t0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   T* data = reinterpret_cast<T*>(a.data);
+  TMPI_DBG_ENTER(P, nullptr, 0, nullptr, 0);
+#ifdef TMPI_DEBUG_BOUNDS
+  __syncthreads();
+#endif
   if ((P.n == 2 || P.n == 4 || P.n == 8) && ps_slices_aligned<T>(a, data)) {
     if (P.n == 2) ps_all_owners<T, V, 2>(a, data, t0, stride);
     else if (P.n == 4) ps_all_owners<T, V, 4>(a, data, t0, stride);

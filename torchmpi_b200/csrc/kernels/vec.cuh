@@ -46,10 +46,45 @@ __device__ __forceinline__ void st_pack(T* p, const Pack<T, V>& x) {
   *reinterpret_cast<Pack<T, V>*>(p) = x;
 }
 
+// ---------------------------------------------------------------- debug build: recording bounds checks
+// With -DTMPI_DEBUG_BOUNDS every peer load and store first checks that its address lies inside one of the
+// mapped heaps (or one of the launch's two local tensors).  An access outside is NOT made: the first one is
+// recorded in the lane's status word (code 7, the checked line's block and the address bits) and the kernel
+// goes on, so that a wrong offset shows up as a Python error instead of a memory fault.  compute-sanitizer
+// is not available where this library is developed; this build stands in for it on the multi-rank kernels.
+#ifdef TMPI_DEBUG_BOUNDS
+struct DbgBounds {
+  const char* lo[20];      // heap bases of the members, the multicast mapping, two local tensors
+  size_t len[20];
+  int n;
+  int* status;             // host-mapped status word of the lane
+};
+static __device__ DbgBounds g_dbg;   // one copy per translation unit, filled at kernel entry
+__device__ __forceinline__ bool dbg_ok(const void* p, size_t bytes) {
+  const char* c = reinterpret_cast<const char*>(p);
+  for (int i = 0; i < g_dbg.n; ++i)
+    if (g_dbg.lo[i] && c >= g_dbg.lo[i] && c + bytes <= g_dbg.lo[i] + g_dbg.len[i]) return true;
+  if (g_dbg.status && atomicCAS(g_dbg.status, 0, 7) == 0) {
+    g_dbg.status[1] = (int)blockIdx.x;
+    g_dbg.status[2] = (int)threadIdx.x;
+    g_dbg.status[3] = (int)(((uintptr_t)c >> 4) & 0x7fffffff);
+    __threadfence_system();
+  }
+  return false;
+}
+#define TMPI_DBG_CHECK(p, bytes) dbg_ok((p), (bytes))
+#else
+#define TMPI_DBG_CHECK(p, bytes) true
+#endif
+
 // peer / streaming variants: bypass L1 (peer lines must not be cached there)
 template <typename T, int V>
 __device__ __forceinline__ Pack<T, V> ld_pack_peer(const T* p) {
   Pack<T, V> r;
+  if (!TMPI_DBG_CHECK(p, sizeof(T) * V)) {
+    memset(&r, 0, sizeof(r));
+    return r;
+  }
   if constexpr (sizeof(T) * V == 16) {
     uint4 u;
     asm volatile("ld.global.relaxed.sys.v4.u32 {%0,%1,%2,%3}, [%4];"
@@ -67,6 +102,7 @@ __device__ __forceinline__ Pack<T, V> ld_pack_peer(const T* p) {
 }
 template <typename T, int V>
 __device__ __forceinline__ void st_pack_peer(T* p, const Pack<T, V>& x) {
+  if (!TMPI_DBG_CHECK(p, sizeof(T) * V)) return;
   if constexpr (sizeof(T) * V == 16) {
     const uint4 u = *reinterpret_cast<const uint4*>(&x);
     asm volatile("st.global.relaxed.sys.v4.u32 [%0], {%1,%2,%3,%4};"

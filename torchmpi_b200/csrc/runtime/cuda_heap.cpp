@@ -94,6 +94,7 @@ int fill_peers(Peers* P, const int* members, int n, int me, int lane) {
   P->status = h.status_dev + 4 * lane;
   P->budget_ns = (unsigned long long)device_wait_budget_ms() * 1000000ull;
   P->mc_base = h.mc_base;
+  P->heap_bytes = h.total_bytes;
   return TMPI_OK;
 }
 
@@ -240,6 +241,14 @@ void* tmpi_cuda_heap_base(int peer) {
 }
 void* tmpi_cuda_heap_mc_base(void) { return heap().live ? heap().mc_base : nullptr; }
 size_t tmpi_cuda_heap_capacity(void) { return heap().live ? heap().total_bytes - heap().arena_off : 0; }
+// 1 when the library was built with recording bounds checks on peer accesses (-DTMPI_DEBUG_BOUNDS)
+int tmpi_debug_bounds_build(void) {
+#ifdef TMPI_DEBUG_BOUNDS
+  return 1;
+#else
+  return 0;
+#endif
+}
 int tmpi_cuda_heap_world(void) { return heap().live ? heap().world : 0; }
 int tmpi_cuda_heap_layout(size_t* out, int n) {
   const CudaHeap& h = heap();

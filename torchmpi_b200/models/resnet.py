@@ -122,3 +122,9 @@ def resnet50(num_classes: int = 1000, fused_bn: bool = False) -> ResNet:
 def resnet_tiny(num_classes: int = 10, fused_bn: bool = False) -> ResNet:
     """A two-stage miniature for tests and smoke runs."""
     return ResNet([1, 1, 1, 1], num_classes, fused_bn, width=16)
+
+
+def resnet_small(num_classes: int = 10, fused_bn: bool = False) -> ResNet:
+    """One bottleneck block per stage at the real widths (64 .. 2048 channels): small enough for a smoke run,
+    wide enough that every convolution takes the same kernels as ResNet-50."""
+    return ResNet([1, 1, 1, 1], num_classes, fused_bn, width=64)
