@@ -465,8 +465,32 @@ __device__ void body_reduce(const CollArgs& a, int* s_abort) {
   if (!peer_barrier(P, 1, 60, s_abort)) return;
   if (P.me == a.root) {
     const size_t stride = (size_t)gridDim.x * blockDim.x;
+    const size_t t0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     T* out = reinterpret_cast<T*>(a.out);
-    sum_from_peers<T, V>(P, a.in_off, 0, out, nv, a.scale, (size_t)blockIdx.x * blockDim.x + threadIdx.x, stride);
+    bool done = false;
+    if constexpr (Multimem<T>::ok && V * sizeof(T) == 16) {
+      if (a.aux) {
+        // the switch adds the members' vectors on the way: the root receives S bytes instead of (n - 1) S
+        constexpr int U = 8;
+        const T* mc = at<T>(P.mc_base, a.in_off);
+        auto finish = [&](uint4 u, size_t i) {
+          Pack<T, V> x = *reinterpret_cast<Pack<T, V>*>(&u);
+          if (a.scale != 1.0f) { Acc<T, V> acc; acc.set(x); x = acc.pack(a.scale); }
+          st_pack<T, V>(out + i * V, x);
+        };
+        size_t i = t0;
+        for (; i + (U - 1) * stride < nv; i += U * stride) {
+          uint4 u[U];
+#pragma unroll
+          for (int k = 0; k < U; ++k) u[k] = Multimem<T>::ld_reduce(mc + (i + k * stride) * V);
+#pragma unroll
+          for (int k = 0; k < U; ++k) finish(u[k], i + k * stride);
+        }
+        for (; i < nv; i += stride) finish(Multimem<T>::ld_reduce(mc + i * V), i);
+        done = true;
+      }
+    }
+    if (!done) sum_from_peers<T, V>(P, a.in_off, 0, out, nv, a.scale, t0, stride);
   }
   peer_barrier(P, 2, 61, s_abort);
 }

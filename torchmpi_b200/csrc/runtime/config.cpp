@@ -46,7 +46,8 @@ Tunable g_tunables[] = {
   {"comm_max_ctas", {64}},                 // CTAs of a stand-alone collective kernel
   {"broadcast_algo", {0}},                 // heap broadcasts: 0 by size, 1 pull from the root, 2 scatter + all-gather, 3 multicast store
   {"bcast_max_ctas", {128}},               // CTAs of the multicast-store broadcast (only the root moves data)
-  {"nvls_max_ctas", {64}},                 // CTAs of the multimem allreduce
+  {"nvls_max_ctas", {32}},                 // CTAs of the multimem kernels: 32 measured best at 8 GPUs (832 GB/s bus at 1 GiB;
+                                           // 64 MiB: 637 vs 588 with 64 CTAs); the switch reduction saturates, more CTAs only contend
   {"ps_max_ctas", {148}},                  // CTAs of a parameter-server push / pull kernel (one per SM: +30 % push bandwidth over 64)
   {"opt_max_ctas", {32}},                  // CTAs of the fused allreduce+SGD kernel (runs beside backward)
   {"comm_threads", {512}},

@@ -280,10 +280,14 @@ int tmpi_cuda_reduce(const void* in, void* out, size_t n, int dtype, int root, c
     if (!direct && (st = stage_in((const char*)in + o * es, m * es, g, s, &off))) return st;
     char* dst = h.emulated ? (char*)out : (char*)out + o * es;
     bool vec = al16(off) && al16((size_t)dst) && m % V == 0;
+    // with a multicast mapping the root lets the switch do the sum (bf16 / f16 / f32, whole heap, large enough)
+    const bool nvls = vec && h.mc_base && whole_heap(g) && g->nmembers > 2 && tunable("use_nvls") &&
+                      (dtype == TMPI_BF16 || dtype == TMPI_F16 || dtype == TMPI_F32) &&
+                      m * es >= (size_t)tunable("nvls_min_bytes");
     st = run_op(OP_REDUCE, dtype, g, vec, vec ? m / V : m, s, [&](int me, CollArgs* a) {
       a->in_off = off; a->out = h.emulated ? (void*)(h.base[g->members[me]] + (size_t)out) : (void*)dst;
-      a->n = m; a->scale = 1.f; a->root = root;
-    });
+      a->n = m; a->scale = 1.f; a->root = root; a->aux = nvls ? 1 : 0;
+    }, nvls ? "nvls_max_ctas" : "comm_max_ctas");
     if (st) return st;
   }
   return TMPI_OK;

@@ -121,6 +121,81 @@ def cases(small: bool):
     return out
 
 
+def lazy_cases(small: bool) -> dict:
+    """name -> builder; a builder allocates its inputs and returns ``(fn, bytes[, flops])``.  Built only when
+    selected, so that a profiler capture of one kernel holds little memory."""
+    import torch.nn.functional as F
+    from torchmpi_b200.ops import conv, layernorm, pool
+    from torchmpi_b200._lib import lib, dtype_code, stream_ptr, check
+    dev = torch.device("cuda")
+    B = 64 if small else 256
+    out = {}
+
+    def conv_case(hw, ci, co, k, stride, pad, mode):
+        def build():
+            x = torch.randn(B, ci, hw, hw, device=dev).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+            w = (torch.randn(co, ci, k, k, device=dev) * 0.05).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+            y, _ = conv.conv_forward(x, w, stride, pad)
+            dy = torch.randn_like(y)
+            stats = torch.empty(lib.tmpi_conv_max_ctas() * 2 * co, dtype=torch.float32, device=dev)
+            nx, ny, nw = x.numel() * 2, y.numel() * 2, w.numel() * 2
+            flops = 2.0 * y.numel() * ci * k * k
+            if mode == "fwd":
+                return (lambda: conv.conv_forward(x, w, stride, pad)), nx + ny + nw, flops
+            if mode == "fwd_stats":
+                return (lambda: conv.conv_forward(x, w, stride, pad, stats)), nx + ny + nw, flops
+            if mode == "dgrad":
+                return (lambda: conv.conv_dgrad(dy, w, x.shape, 1, pad)), nx + ny + nw, flops
+            if mode == "dgrad_add":
+                other = torch.randn_like(x)
+                return (lambda: conv.conv_dgrad(dy, w, x.shape, 1, pad, add=other)), 2 * nx + ny + nw, flops
+            if mode == "wgrad":
+                return (lambda: conv.conv_wgrad(dy, x, w.shape, stride, pad)), nx + ny + nw, flops
+            if mode == "cudnn_fwd":
+                return (lambda: F.conv2d(x, w, None, stride, pad)), nx + ny + nw, flops
+            raise ValueError(mode)
+        return build
+
+    for tag, geom in {"1x1_56_64_256": (56, 64, 256, 1, 1, 0), "1x1_56_256_64": (56, 256, 64, 1, 1, 0),
+                      "1x1_14_1024_256": (14, 1024, 256, 1, 1, 0), "3x3_56_64_64": (56, 64, 64, 3, 1, 1),
+                      "3x3_14_256_256": (14, 256, 256, 3, 1, 1)}.items():
+        for mode in ("fwd", "fwd_stats", "dgrad", "dgrad_add", "wgrad", "cudnn_fwd"):
+            out[f"conv_{tag}_{mode}"] = conv_case(*geom, mode)
+
+    def ln_case(backward):
+        def build():
+            rows, C = (131072 if not small else 65536), 1024        # > L2 both ways
+            x = torch.randn(rows, C, device=dev).to(torch.bfloat16).requires_grad_(True)
+            g = torch.ones(C, device=dev, dtype=torch.bfloat16, requires_grad=True)
+            b = torch.zeros(C, device=dev, dtype=torch.bfloat16, requires_grad=True)
+            if not backward:
+                return (lambda: layernorm._LayerNormFn.apply(x.detach(), g.detach(), b.detach(), 1e-5)), rows * C * 2 * 2
+            y = layernorm._LayerNormFn.apply(x, g, b, 1e-5)
+            dy = torch.randn_like(y)
+            return (lambda: torch.autograd.grad(y, (x, g, b), dy, retain_graph=True)), rows * C * 2 * 3
+        return build
+    out["layernorm_fwd"] = ln_case(False)
+    out["layernorm_bwd"] = ln_case(True)
+
+    def pool_case():
+        N, C, H = (B, 64, 112)
+        x = torch.randn(N, C, H, H, device=dev).to(torch.bfloat16).contiguous(memory_format=torch.channels_last).requires_grad_(True)
+        y = pool._MaxPoolFn.apply(x, 3, 2, 1)
+        dy = torch.randn_like(y)
+        return (lambda: torch.autograd.grad(y, x, dy, retain_graph=True)), (x.numel() + y.numel()) * 2 + y.numel()
+    out["maxpool_bwd"] = pool_case
+
+    def stem_case():
+        x = torch.randn(B, 3, 224, 224, device=dev).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+        kpad = lib.tmpi_stem_patch_width()
+        col = torch.empty((B * 112 * 112, kpad), dtype=torch.bfloat16, device=dev)
+        def run():
+            check(lib.tmpi_stem_im2col(x.data_ptr(), col.data_ptr(), B, 224, 224, dtype_code(x.dtype), stream_ptr()))
+        return run, x.numel() * 2 + col.numel() * 2
+    out["stem_im2col"] = stem_case
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--kernel", default="all")
@@ -132,9 +207,15 @@ def main():
     flush = torch.zeros(160 << 20, dtype=torch.uint8, device="cuda")
     f = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
     tf_peak = json.loads(f.read_text())["bf16_tflops"] if f.exists() else 1590.0
-    for name, case in cases(args.small).items():
-        if args.kernel != "all" and not name.startswith(args.kernel):
-            continue
+    lazy = lazy_cases(args.small)
+    picked_lazy = {n: b for n, b in lazy.items() if args.kernel == "all" or n.startswith(args.kernel)}
+    if args.kernel != "all" and picked_lazy:
+        eager = {}                                   # a lazily built kernel was named: skip the eager set
+    else:
+        eager = cases(args.small)
+    todo = [(n, c) for n, c in eager.items() if args.kernel == "all" or n.startswith(args.kernel)]
+    todo += [(n, b()) for n, b in picked_lazy.items()]
+    for name, case in todo:
         fn, nbytes = case[0], case[1]
         ms = time_kernel(fn, args.reps, flush)
         gbs = nbytes / ms / 1e6
