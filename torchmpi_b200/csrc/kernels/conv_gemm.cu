@@ -21,9 +21,11 @@
 // time.  Epilogues:
 //   store    bf16 rows: each warp transposes its 32 x 64 slice through a swizzled staging tile and
 //            writes full 128-byte lines; optionally the per-channel sum and sum of squares of the
-//            stored values (the batch statistics of the batch-norm that follows, accumulated per warp
-//            in shared memory and written as one partial row per CTA: no atomics, fixed order), and optionally
-//            "+ R" for a second gradient that flows into the same tensor;
+//            stored values (the batch statistics of the batch-norm that follows, accumulated per lane
+//            in registers over all tiles of the CTA and written as one partial row per CTA: no atomics,
+//            fixed order), and optionally
+//            "+ R" for a second gradient that flows into the same tensor (added to the rounded product,
+//            as a separate accumulation kernel would);
 //   split-K  fp32 partial tiles to a workspace, summed in slice order by a second small kernel
 //            (deterministic).
 // The three passes of a framework convolution go to library kernels; the reference itself has no
@@ -230,110 +232,119 @@ __device__ __forceinline__ void unpack8(const uint4& u, float* f) {
 // - eight lanes per 128-byte row, four rows per instruction - and stores full lines.  The same read
 // feeds the column sums.  Group g (four warps, one per lane quarter) drains accumulator g, so two tiles
 // are in the epilogue at any time and no barrier between warps sits in the loop.
+template <bool do_stats, bool do_add>
 __device__ void epilogue_store(Shared* sh, unsigned char* stg, float* stats_all, const Problem& p, int ew, int quarter, int lane) {
   const int group = ew >> 2;                      // ew: index of this warp among the epilogue warps
-  float* stats = stats_all + (size_t)ew * 2 * BN; // this warp's private column sums
-  const bool do_stats = (p.epi & EPI_STATS) != 0;
   const int chunk = lane & 7, rsub = lane >> 3;
+  // Running column sums of this lane (packed fp32 pairs) for the 8 columns of its chunk in each of the four
+  // 64-column slices of a tile.  The CTA always visits the same n_blk (the grid is a multiple of tiles_n), so
+  // the columns stay the same over all its tiles and the sums live in registers until the kernel ends.
+  unsigned long long cs2[4][4], cq2[4][4];
+#pragma unroll
+  for (int sl = 0; sl < 4; ++sl)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) { cs2[sl][e] = 0ull; cq2[sl][e] = 0ull; }
   int m_blk, n_blk, slice;
   for (int it = group; item(p, it, &m_blk, &n_blk, &slice); it += 2) {
     const uint32_t acc_phase = (it >> 1) & 1;
     if (!sm100::mbar_wait(&sh->acc_full[group], acc_phase, kWaitBudgetNs) || sh->error) { fail(sh, p, 5); break; }
     sm100::tc_fence_after();
     const int row0 = m_blk * BM + quarter * 32;
-    const int row = row0 + lane;
     const uint32_t t_base = sh->tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)group * BN;
-#pragma unroll 1
-    for (int c0 = 0; c0 < p.mma_n; c0 += SLICE) {
+#pragma unroll
+    for (int sl = 0; sl < BN / SLICE; ++sl) {
+      const int c0 = sl * SLICE;
       const int col0 = n_blk * BN + c0;
-      if (col0 >= p.N) break;
-      uint32_t r[2][32];
-      sm100::tmem_ld_32x32(t_base + c0, r[0]);
-      sm100::tmem_ld_32x32(t_base + c0 + 32, r[1]);
-      sm100::tmem_ld_wait();
+      if (c0 < p.mma_n && col0 < p.N) {
+        // the second gradient, read line by line like the store (the eight loads fly while the accumulator is converted)
+        uint4 av[8];
+        if (do_add) {
+          const __nv_bfloat16* addp = p.add + (size_t)row0 * p.N + col0 + chunk * 8;
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        float v[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[h][j]);
-        if ((p.epi & EPI_ADD) && row < p.M) {
-          const uint4* ap = reinterpret_cast<const uint4*>(p.add + (size_t)row * p.N + col0 + h * 32);
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            float f[8];
-            unpack8(__ldg(ap + q), f);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) v[q * 8 + e] += f[e];
+          for (int i = 0; i < 8; ++i) {
+            const int rw = i * 4 + rsub;
+            av[i] = row0 + rw < p.M ? __ldg(reinterpret_cast<const uint4*>(addp + (size_t)rw * p.N)) : make_uint4(0, 0, 0, 0);
           }
         }
+        uint32_t r[2][32];
+        sm100::tmem_ld_32x32(t_base + c0, r[0]);
+        sm100::tmem_ld_32x32(t_base + c0 + 32, r[1]);
+        sm100::tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 32; j += 8) {
-          __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j], v[j + 1]), h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
-          __nv_bfloat162 h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
-          uint4 u;
-          u.x = *reinterpret_cast<uint32_t*>(&h0); u.y = *reinterpret_cast<uint32_t*>(&h1);
-          u.z = *reinterpret_cast<uint32_t*>(&h2); u.w = *reinterpret_cast<uint32_t*>(&h3);
-          const int ck = h * 4 + j / 8;
-          *reinterpret_cast<uint4*>(stg + (size_t)lane * 128 + ((ck ^ (lane & 7)) << 4)) = u;
-        }
-      }
-      __syncwarp();
-      // packed fp32 pairs (add.f32x2 / fma.rn.f32x2): column sums and sums of squares of this lane's 8 columns
-      unsigned long long cs2[4], cq2[4];
+        for (int h = 0; h < 2; ++h) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) { cs2[e] = 0ull; cq2[e] = 0ull; }
-      __nv_bfloat16* out = p.out + (size_t)row0 * p.N + col0 + chunk * 8;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int rw = i * 4 + rsub;
-        const uint4 u = *reinterpret_cast<const uint4*>(stg + (size_t)rw * 128 + ((chunk ^ (rw & 7)) << 4));
-        if (row0 + rw < p.M) *reinterpret_cast<uint4*>(out + (size_t)rw * p.N) = u;
-        if (do_stats) {                         // rows past M hold zeros
-          const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            unsigned long long f2;
-            asm("mov.b64 %0, {%1, %2};" : "=l"(f2) : "r"(w[e] << 16), "r"(w[e] & 0xffff0000u));
-            asm("add.rn.f32x2 %0, %0, %1;" : "+l"(cs2[e]) : "l"(f2));
-            asm("fma.rn.f32x2 %0, %1, %1, %0;" : "+l"(cq2[e]) : "l"(f2));
+          for (int j = 0; j < 32; j += 8) {
+            __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(r[h][j]), __uint_as_float(r[h][j + 1]));
+            __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(r[h][j + 2]), __uint_as_float(r[h][j + 3]));
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[h][j + 4]), __uint_as_float(r[h][j + 5]));
+            __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(r[h][j + 6]), __uint_as_float(r[h][j + 7]));
+            uint4 u;
+            u.x = *reinterpret_cast<uint32_t*>(&h0); u.y = *reinterpret_cast<uint32_t*>(&h1);
+            u.z = *reinterpret_cast<uint32_t*>(&h2); u.w = *reinterpret_cast<uint32_t*>(&h3);
+            const int ck = h * 4 + j / 8;
+            *reinterpret_cast<uint4*>(stg + (size_t)lane * 128 + ((ck ^ (lane & 7)) << 4)) = u;
           }
         }
+        __syncwarp();
+        __nv_bfloat16* out = p.out + (size_t)row0 * p.N + col0 + chunk * 8;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int rw = i * 4 + rsub;
+          uint4 u = *reinterpret_cast<const uint4*>(stg + (size_t)rw * 128 + ((chunk ^ (rw & 7)) << 4));
+          if (row0 + rw < p.M) {
+            if (do_add) {                       // bf16(product) + it, as a separate accumulation kernel would compute
+              __nv_bfloat162* uu = reinterpret_cast<__nv_bfloat162*>(&u);
+              const __nv_bfloat162* aa = reinterpret_cast<const __nv_bfloat162*>(&av[i]);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) uu[e] = __hadd2(uu[e], aa[e]);
+            }
+            *reinterpret_cast<uint4*>(out + (size_t)rw * p.N) = u;
+          }
+          if (do_stats) {                       // rows past M hold zeros
+            const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              unsigned long long f2;
+              asm("mov.b64 %0, {%1, %2};" : "=l"(f2) : "r"(w[e] << 16), "r"(w[e] & 0xffff0000u));
+              asm("add.rn.f32x2 %0, %0, %1;" : "+l"(cs2[sl][e]) : "l"(f2));
+              asm("fma.rn.f32x2 %0, %1, %1, %0;" : "+l"(cq2[sl][e]) : "l"(f2));
+            }
+          }
+        }
+        __syncwarp();                           // the staging tile is rewritten by the next slice
       }
-      if (do_stats) {
-        float cs[8], cq[8];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          uint32_t lo, hi;
-          asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(cs2[e]));
-          cs[2 * e] = __uint_as_float(lo); cs[2 * e + 1] = __uint_as_float(hi);
-          asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(cq2[e]));
-          cq[2 * e] = __uint_as_float(lo); cq[2 * e + 1] = __uint_as_float(hi);
-        }
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          cs[e] += __shfl_xor_sync(0xffffffffu, cs[e], 8); cq[e] += __shfl_xor_sync(0xffffffffu, cq[e], 8);
-          cs[e] += __shfl_xor_sync(0xffffffffu, cs[e], 16); cq[e] += __shfl_xor_sync(0xffffffffu, cq[e], 16);
-        }
-        // all four lanes of a column chunk now hold the sums: each adds a quarter of them to the warp's
-        // accumulators (slots owned by this lane alone)
-        float* acc = stats + c0 + chunk * 8 + 2 * rsub;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          if ((e >> 1) == rsub) { acc[e & 1] += cs[e]; acc[BN + (e & 1)] += cq[e]; }
-        }
-      }
-      __syncwarp();                             // the staging tile is rewritten by the next slice
     }
     sm100::tc_fence_before();
     __syncwarp();
     if (lane == 0) sm100::mbar_arrive(&sh->acc_empty[group]);
   }
   if (do_stats) {
-    // the CTA's partial row: the eight warps' sums over the column window of this CTA (its n_blk never
-    // changes: the grid is a multiple of tiles_n), zeros elsewhere
-    asm volatile("bar.sync 3, 256;" ::: "memory");     // all eight epilogue warps are done adding
+    // once per kernel: add the four row groups of the warp (lanes l, l + 8, l + 16, l + 24 hold the same
+    // columns), park the warp's sums in shared memory, then add the eight warps in a fixed order
+    float* mine = stats_all + (size_t)ew * 2 * BN;
+#pragma unroll
+    for (int sl = 0; sl < 4; ++sl)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        uint32_t lo, hi;
+        float v[4];
+        asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(cs2[sl][e]));
+        v[0] = __uint_as_float(lo); v[1] = __uint_as_float(hi);
+        asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(cq2[sl][e]));
+        v[2] = __uint_as_float(lo); v[3] = __uint_as_float(hi);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          v[k] += __shfl_xor_sync(0xffffffffu, v[k], 8);
+          v[k] += __shfl_xor_sync(0xffffffffu, v[k], 16);
+        }
+        if (rsub == 0) {
+          const int c = sl * SLICE + chunk * 8 + 2 * e;
+          mine[c] = v[0]; mine[c + 1] = v[1]; mine[BN + c] = v[2]; mine[BN + c + 1] = v[3];
+        }
+      }
+    // the CTA's partial row: the sums over its column window, zeros elsewhere
+    asm volatile("bar.sync 3, 256;" ::: "memory");     // all eight epilogue warps have parked their sums
     const int tid = ew * 32 + lane;
-    const float* all = stats_all;
     const int win0 = (blockIdx.x % p.tiles_n) * BN;
     float* dst = p.stats + (size_t)blockIdx.x * 2 * p.N;
     for (int c = tid; c < 2 * p.N; c += 256) {
@@ -341,7 +352,7 @@ __device__ void epilogue_store(Shared* sh, unsigned char* stg, float* stats_all,
       float v = 0.f;
       if (col >= 0 && col < BN) {
 #pragma unroll
-        for (int w = 0; w < EPI_WARPS; ++w) v += all[(w * 2 + which) * BN + col];
+        for (int w = 0; w < EPI_WARPS; ++w) v += stats_all[(w * 2 + which) * BN + col];
       }
       dst[c] = v;
     }
@@ -375,6 +386,8 @@ __device__ void epilogue_splitk(Shared* sh, const Problem& p, int group, int qua
   }
 }
 
+// EPI: the epilogue flags as a template parameter, so that each flavour carries only its own registers
+template <int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
 conv_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Problem p) {
   extern __shared__ unsigned char smem_raw[];
@@ -408,10 +421,11 @@ conv_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     if (sm100::elect_one()) producer(sh, tiles, b_res, p, &map_a, &map_b);
   } else if (warp == 1) {
     if (sm100::elect_one()) mma_issuer(sh, tiles, b_res, p);
-  } else if (p.epi & EPI_SPLITK) {
+  } else if constexpr ((EPI & EPI_SPLITK) != 0) {
     epilogue_splitk(sh, p, (warp - 2) >> 2, warp & 3, lane);
   } else {
-    epilogue_store(sh, staging + (size_t)(warp - 2) * WARP_STAGING_BYTES, stats, p, warp - 2, warp & 3, lane);
+    epilogue_store<(EPI & EPI_STATS) != 0, (EPI & EPI_ADD) != 0>(sh, staging + (size_t)(warp - 2) * WARP_STAGING_BYTES, stats, p,
+                                                              warp - 2, warp & 3, lane);
   }
   __syncwarp();
   sm100::tc_fence_before();
@@ -546,7 +560,15 @@ static int* conv_status_word(int** host_out = nullptr) {
 
 // Plans the shared memory (stages, resident weight) and launches.
 static int conv_launch(const CUtensorMap& ma, const CUtensorMap& mb, conv::Problem& p, int* grid_out, cudaStream_t s) {
-  cudaError_t ae = cudaFuncSetAttribute(conv::conv_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)conv::SMEM_LIMIT);
+  void (*kernel)(const CUtensorMap, const CUtensorMap, const conv::Problem) = nullptr;
+  switch (p.epi) {
+    case 0: kernel = conv::conv_gemm_kernel<0>; break;
+    case conv::EPI_STATS: kernel = conv::conv_gemm_kernel<conv::EPI_STATS>; break;
+    case conv::EPI_ADD: kernel = conv::conv_gemm_kernel<conv::EPI_ADD>; break;
+    case conv::EPI_SPLITK: kernel = conv::conv_gemm_kernel<conv::EPI_SPLITK>; break;
+    default: return fail(TMPI_ERR_INVALID, "conv: unsupported epilogue combination %d", p.epi);
+  }
+  cudaError_t ae = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)conv::SMEM_LIMIT);
   if (ae != cudaSuccess) return fail(TMPI_ERR_CUDA, "conv: shared memory attribute: %s", cudaGetErrorString(ae));
   p.status = conv_status_word();
   p.b_block_bytes = p.mma_n * conv::BK * 2;
@@ -569,7 +591,7 @@ static int conv_launch(const CUtensorMap& ma, const CUtensorMap& mb, conv::Probl
   // statistics: a CTA keeps sums for one window of 256 columns, so every tile it visits must have the same n_blk
   if ((p.epi & conv::EPI_STATS) && grid % p.tiles_n) grid -= grid % p.tiles_n;
   if (grid_out) *grid_out = grid;
-  conv::conv_gemm_kernel<<<grid, conv::THREADS, smem, s>>>(ma, mb, p);
+  kernel<<<grid, conv::THREADS, smem, s>>>(ma, mb, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? TMPI_OK : fail(TMPI_ERR_CUDA, "conv launch: %s", cudaGetErrorString(e));
 }

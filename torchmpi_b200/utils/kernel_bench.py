@@ -193,6 +193,45 @@ def lazy_cases(small: bool) -> dict:
             check(lib.tmpi_stem_im2col(x.data_ptr(), col.data_ptr(), B, 224, 224, dtype_code(x.dtype), stream_ptr()))
         return run, x.numel() * 2 + col.numel() * 2
     out["stem_im2col"] = stem_case
+
+    # multi-rank kernels with a single member (no peer to wait for, so a profiler may replay them): the data
+    # path of the two-shot allreduce and of the parameter-server push / pull on this GPU's own heap
+    _heap = {}
+
+    def heap():
+        if "h" not in _heap:
+            from torchmpi_b200.parallel.symm_heap import CudaHeap
+            _heap["h"] = CudaHeap(0, 1, (1 << 30) + (256 << 20), 0)
+        return _heap["h"]
+
+    def twoshot_case():
+        import ctypes as C
+        from torchmpi_b200 import _lib
+        h = heap()
+        n = (64 if small else 256) << 20
+        _, off_in = h.alloc(n * 2)
+        _, off_out = h.alloc(n * 2)
+        h.view(off_in, n * 2).view(torch.bfloat16).normal_()
+        arr = _lib.int_array([0])
+        g = _lib.Group(arr, 1, 0, 0)
+        def run():
+            check(lib.tmpi_cuda_allreduce_heap(off_in, off_out, n, 6, 1.0, C.byref(g), 2, stream_ptr()))
+        run.keep = (arr, g)
+        return run, n * 2 * 2
+    out["coll_twoshot_one_member"] = twoshot_case
+
+    def ps_case(rule):
+        def build():
+            h = heap()
+            n = (64 if small else 256) << 20
+            t = torch.randn(n, device=dev).to(torch.bfloat16)
+            pid = h.ps_create(t, (0,))
+            if rule < 0:
+                return (lambda: h.ps_pull(pid, t).wait()), n * 2 * 2
+            return (lambda: h.ps_push(pid, t, rule).wait()), n * 2 * (3 if rule == 2 else 2)
+        return build
+    out["ps_push_add_one_member"] = ps_case(2)
+    out["ps_pull_one_member"] = ps_case(-1)
     return out
 
 
