@@ -67,9 +67,11 @@ def test_absmean_var_and_check():
             x = torch.randn(n, device="cuda").to(dtype)
             m, v = stats.absmean_var(x)
             a = x.double().abs()
-            assert abs(m - a.mean().item()) <= 1e-9 * max(1.0, abs(m))
+            # fp64 accumulation of fp32 partial sums over at most 32 elements (fp64 inputs: fp64 throughout)
+            tol_m, tol_v = (1e-9, 1e-7) if dtype == torch.float64 else (5e-7, 2e-6)
+            assert abs(m - a.mean().item()) <= tol_m * max(1.0, abs(m))
             if n > 1:
-                assert abs(v - a.var().item()) <= 1e-7 * max(1.0, v)
+                assert abs(v - a.var().item()) <= tol_v * max(1.0, v)
             assert stats.absmean_var(x) == (m, v)      # deterministic
 
 

@@ -101,6 +101,18 @@ def _collectives(rank, world, backend):
     sym.fill_(rank + 1)
     mpi.p2p.allreduce_tensor(sym)
     assert torch.all(sym == n * (n + 1) // 2)
+    # every broadcast algorithm on a heap tensor whose length does not split evenly (pull, scatter + all-gather,
+    # multicast store, scatter + multicast stores; the multicast ones fall back to the pull without a mapping)
+    symb = heap.empty((1 << 20) + 8 * 13, torch.bfloat16)
+    for algo in (1, 2, 3, 4):
+        mpi.config.set("broadcast_algo", algo)
+        for root in (0, n - 1):
+            symb.copy_((torch.arange(symb.numel(), device=dev) % 251 + rank * 7).to(torch.bfloat16))
+            mpi.p2p.broadcast_tensor(root, symb)
+            expect = (torch.arange(symb.numel(), device=dev) % 251 + root * 7).to(torch.bfloat16)
+            assert torch.equal(symb, expect), (algo, root)
+    mpi.config.set("broadcast_algo", 0)
+    heap.check_status(0)
     # reduce / allgather(v) / reduce_scatter / sendreceive
     for size in (7, 4096, 1 << 18):
         inp = torch.full((size,), float(rank), device=dev)

@@ -415,6 +415,40 @@ __device__ void body_bcast_mc(const CollArgs& a, int* s_abort) {
   }
 }
 
+// Scatter through peer loads, all-gather through the switch, in one pass: member m reads chunk m out of the root's
+// buffer and stores it through the multicast mapping, which delivers it to every member (the root included, where it
+// rewrites the same values).  The root sends each byte once - 1/N of them as multicast stores of its own chunk - and
+// every member's multicast stream carries only 1/N of the message, so no single multicast writer is the limit.
+template <typename T, int V>
+__device__ void body_bcast_scatter_mc(const CollArgs& a, int* s_abort) {
+  if constexpr (V * sizeof(T) == 16) {
+    const Peers& P = a.P;
+    const size_t nv = a.n / V;
+    const size_t per = ceil_div(nv, P.n);
+    size_t lo = per * P.me, hi = lo + per;
+    if (lo > nv) lo = nv;
+    if (hi > nv) hi = nv;
+    if (!peer_barrier(P, 1, 59, s_abort)) return;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    const T* src = at<T>(P.base[a.root], a.out_off);
+    T* mc = at<T>(P.mc_base, a.out_off);
+    constexpr int U = 8;
+    size_t i = lo + (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (; i + (U - 1) * stride < hi; i += U * stride) {
+      Pack<T, V> x[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) x[u] = ld_pack_peer<T, V>(src + (i + u * stride) * V);
+#pragma unroll
+      for (int u = 0; u < U; ++u) multimem_st(mc + (i + u * stride) * V, *reinterpret_cast<uint4*>(&x[u]));
+    }
+    for (; i < hi; i += stride) {
+      Pack<T, V> x = ld_pack_peer<T, V>(src + i * V);
+      multimem_st(mc + i * V, *reinterpret_cast<uint4*>(&x));
+    }
+    peer_barrier(P, 2, 49, s_abort);
+  }
+}
+
 // Broadcast of a tensor that lives outside the heap: the root pushes its buffer into every peer's
 // scratch (one multicast store through the switch when the heap has a multicast mapping, else one
 // store per peer), and after the barrier every other rank copies its scratch into its own tensor.

@@ -101,10 +101,72 @@ __global__ void __launch_bounds__(256) xent_kernel(const T* __restrict__ logits,
   }
 }
 
-// One block per row with the row staged in shared memory: the logits are read from HBM once
-// (16-byte loads; the row keeps its global misalignment in shared memory so that the aligned body
-// maps onto aligned shared addresses) and the gradient is written once.  Rows of 50257 bf16 start on
-// 2-byte boundaries only, so a few head and tail elements move as scalars.
+// Codecs between a 16-byte pack of T and fp32 lanes, for the row staged in shared memory.
+template <typename T> struct RowPack;
+template <> struct RowPack<float> {
+  static constexpr int V = 4;
+  static __device__ __forceinline__ void unpack(const uint4& u, float* f) {
+    f[0] = __uint_as_float(u.x); f[1] = __uint_as_float(u.y); f[2] = __uint_as_float(u.z); f[3] = __uint_as_float(u.w);
+  }
+  static __device__ __forceinline__ uint4 pack(const float* f) {
+    return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
+  }
+  static __device__ __forceinline__ float max(const uint4& u, float m) {
+    return fmaxf(fmaxf(fmaxf(__uint_as_float(u.x), __uint_as_float(u.y)), fmaxf(__uint_as_float(u.z), __uint_as_float(u.w))), m);
+  }
+};
+template <> struct RowPack<__nv_bfloat16> {
+  static constexpr int V = 8;
+  static __device__ __forceinline__ void unpack(const uint4& u, float* f) {   // bf16 -> fp32 is a shift or a mask
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) { f[2 * k] = __uint_as_float(w[k] << 16); f[2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u); }
+  }
+  static __device__ __forceinline__ uint4 pack(const float* f) {
+    uint32_t w[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) { __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * k], f[2 * k + 1]); w[k] = *reinterpret_cast<uint32_t*>(&h); }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+  }
+  static __device__ __forceinline__ float max(const uint4& u, float m) {      // two elements per instruction
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+    __nv_bfloat162 a = __hmax2(__hmax2(h[0], h[1]), __hmax2(h[2], h[3]));
+    return fmaxf(fmaxf(__low2float(a), __high2float(a)), m);
+  }
+};
+template <> struct RowPack<__half> {
+  static constexpr int V = 8;
+  static __device__ __forceinline__ void unpack(const uint4& u, float* f) {
+    const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) { float2 v = __half22float2(h[k]); f[2 * k] = v.x; f[2 * k + 1] = v.y; }
+  }
+  static __device__ __forceinline__ uint4 pack(const float* f) {
+    uint32_t w[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) { __half2 h = __floats2half2_rn(f[2 * k], f[2 * k + 1]); w[k] = *reinterpret_cast<uint32_t*>(&h); }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+  }
+  static __device__ __forceinline__ float max(const uint4& u, float m) {
+    const __half2* h = reinterpret_cast<const __half2*>(&u);
+    __half2 a = __hmax2(__hmax2(h[0], h[1]), __hmax2(h[2], h[3]));
+    return fmaxf(fmaxf(__low2float(a), __high2float(a)), m);
+  }
+};
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// One block per row with the row staged in shared memory: the logits are read from HBM once and the gradient is
+// written once.  The aligned body of the row travels as asynchronous 16-byte copies that are all in flight together
+// (the row keeps its global misalignment in shared memory, so aligned global packs land on aligned shared addresses;
+// rows of 50257 bf16 start on 2-byte boundaries only, and a few head and tail elements move as scalars).  Every
+// thread works on the same packs in all passes, so only the two reductions need the block.  The second pass replaces
+// the logits in shared memory by exp(x - max) (rounded to T), so the gradient pass is one multiplication per element
+// and the exponential is evaluated once; the label's entry is recomputed in fp32 by one thread at the end.
 template <typename T, int THREADS>
 __global__ void __launch_bounds__(THREADS) xent_row_smem_kernel(
     const T* __restrict__ logits, const long long* __restrict__ labels, int rows, int cols, int ld,
@@ -114,7 +176,9 @@ __global__ void __launch_bounds__(THREADS) xent_row_smem_kernel(
   __shared__ float s_red[32];
   __shared__ float s_bcast;
   __shared__ bool s_last;
-  constexpr int V = 16 / sizeof(T);
+  using RP = RowPack<T>;
+  constexpr int V = RP::V;
+  constexpr float kLog2e = 1.4426950408889634f;
   const int r = blockIdx.x, tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5, nwarp = THREADS >> 5;
   const T* x = logits + (size_t)r * ld;               // ld: row pitch in elements (>= cols)
@@ -125,58 +189,55 @@ __global__ void __launch_bounds__(THREADS) xent_row_smem_kernel(
   const int nvec = (cols - head) / V, tail0 = head + nvec * V;
   const uint4* gx = reinterpret_cast<const uint4*>(x + head);
   uint4* sx = reinterpret_cast<uint4*>(srow + head);
+  const int label = (int)labels[r];
 
-  // pass 1: global -> shared, running maximum
+  // pass 1: global -> shared, then the maximum of this thread's packs
+  {
+    const uint32_t s0 = (uint32_t)__cvta_generic_to_shared(sx);
+    for (int i = tid; i < nvec; i += THREADS)
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s0 + 16u * (uint32_t)i), "l"(gx + i) : "memory");
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
   float m = -INFINITY;
   for (int c = tid; c < head; c += THREADS) { T v = x[c]; srow[c] = v; m = fmaxf(m, (float)to_acc<T>(v)); }
   for (int c = tail0 + tid; c < cols; c += THREADS) { T v = x[c]; srow[c] = v; m = fmaxf(m, (float)to_acc<T>(v)); }
-  {
-    constexpr int U = 4;
-    int i = tid;
-    for (; i + (U - 1) * THREADS < nvec; i += U * THREADS) {
-      uint4 u[U];
-#pragma unroll
-      for (int k = 0; k < U; ++k) u[k] = __ldg(gx + i + k * THREADS);
-#pragma unroll
-      for (int k = 0; k < U; ++k) {
-        sx[i + k * THREADS] = u[k];
-        const T* e = reinterpret_cast<const T*>(&u[k]);
-#pragma unroll
-        for (int j = 0; j < V; ++j) m = fmaxf(m, (float)to_acc<T>(e[j]));
-      }
-    }
-    for (; i < nvec; i += THREADS) {
-      uint4 u = __ldg(gx + i);
-      sx[i] = u;
-      const T* e = reinterpret_cast<const T*>(&u);
-#pragma unroll
-      for (int j = 0; j < V; ++j) m = fmaxf(m, (float)to_acc<T>(e[j]));
-    }
-  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  for (int i = tid; i < nvec; i += THREADS) m = RP::max(sx[i], m);
   for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(~0u, m, o));
   if (lane == 0) s_red[warp] = m;
   __syncthreads();                                    // also: the whole row is in shared memory
+  float xl = 0.f;
   if (tid == 0) {
     float v = s_red[0];
     for (int w = 1; w < nwarp; ++w) v = fmaxf(v, s_red[w]);
     s_bcast = v;
+    xl = (label >= 0 && label < cols) ? (float)to_acc<T>(srow[label]) : v;   // before pass 2 overwrites the row
   }
   __syncthreads();
   m = s_bcast;
+  const float mL = m * kLog2e;
 
-  // pass 2: sum of exponentials from shared memory
-  float sum = 0.f;
-  for (int c = tid; c < head; c += THREADS) sum += __expf((float)to_acc<T>(srow[c]) - m);
-  for (int c = tail0 + tid; c < cols; c += THREADS) sum += __expf((float)to_acc<T>(srow[c]) - m);
+  // pass 2: exponentials, kept in shared memory in place of the logits, and their sum
+  float sum0 = 0.f, sum1 = 0.f;
+  auto scalar_exp = [&](int c) {
+    float e = ex2_approx(fmaf((float)to_acc<T>(srow[c]), kLog2e, -mL));
+    sum0 += e;
+    srow[c] = from_acc<T>((typename AccOf<T>::type)e);
+  };
+  for (int c = tid; c < head; c += THREADS) scalar_exp(c);
+  for (int c = tail0 + tid; c < cols; c += THREADS) scalar_exp(c);
   for (int i = tid; i < nvec; i += THREADS) {
-    uint4 u = sx[i];
-    const T* e = reinterpret_cast<const T*>(&u);
+    float f[V];
+    RP::unpack(sx[i], f);
 #pragma unroll
-    for (int j = 0; j < V; ++j) sum += __expf((float)to_acc<T>(e[j]) - m);
+    for (int j = 0; j < V; ++j) f[j] = ex2_approx(fmaf(f[j], kLog2e, -mL));
+#pragma unroll
+    for (int j = 0; j < V; j += 2) { sum0 += f[j]; sum1 += f[j + 1]; }
+    sx[i] = RP::pack(f);
   }
+  float sum = sum0 + sum1;
   for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(~0u, sum, o);
-  __syncthreads();
-  if (lane == 0) s_red[warp] = sum;
+  if (lane == 0) s_red[warp] = sum;                   // s_red was last read before the previous barrier
   __syncthreads();
   if (tid == 0) {
     float v = 0.f;
@@ -186,34 +247,32 @@ __global__ void __launch_bounds__(THREADS) xent_row_smem_kernel(
   __syncthreads();
   sum = s_bcast;
   const float inv = 1.f / sum;
-  const int label = (int)labels[r];
 
-  // pass 3: gradient, written once
+  // pass 3: gradient = exp * (gscale / sum), written once; the label's entry afterwards
   if (dlogits) {
     T* d = dlogits + (size_t)r * ld;
+    const float k = inv * gscale;
     for (int c = cols + tid; c < ld; c += THREADS) d[c] = from_acc<T>((typename AccOf<T>::type)0.f);   // pitch padding
-    auto grad = [&](T v, int c) {
-      float p = __expf((float)to_acc<T>(v) - m) * inv;
-      return from_acc<T>((typename AccOf<T>::type)((p - (c == label ? 1.f : 0.f)) * gscale));
-    };
-    for (int c = tid; c < head; c += THREADS) d[c] = grad(srow[c], c);
-    for (int c = tail0 + tid; c < cols; c += THREADS) d[c] = grad(srow[c], c);
+    auto scalar_grad = [&](int c) { d[c] = from_acc<T>((typename AccOf<T>::type)((float)to_acc<T>(srow[c]) * k)); };
+    for (int c = tid; c < head; c += THREADS) scalar_grad(c);
+    for (int c = tail0 + tid; c < cols; c += THREADS) scalar_grad(c);
     if ((((uintptr_t)d) & 15) == mis) {
       uint4* gd = reinterpret_cast<uint4*>(d + head);
       for (int i = tid; i < nvec; i += THREADS) {
-        uint4 u = sx[i], o;
-        const T* e = reinterpret_cast<const T*>(&u);
-        T* q = reinterpret_cast<T*>(&o);
+        float f[V];
+        RP::unpack(sx[i], f);
 #pragma unroll
-        for (int j = 0; j < V; ++j) q[j] = grad(e[j], head + i * V + j);
-        gd[i] = o;
+        for (int j = 0; j < V; ++j) f[j] *= k;
+        gd[i] = RP::pack(f);
       }
     } else {
-      for (int c = head + tid; c < tail0; c += THREADS) d[c] = grad(srow[c], c);
+      for (int c = head + tid; c < tail0; c += THREADS) scalar_grad(c);
     }
+    __syncthreads();                                  // the label's entry is overwritten after every other store
+    if (tid == 0 && label >= 0 && label < cols)
+      d[label] = from_acc<T>((typename AccOf<T>::type)((ex2_approx(fmaf(xl, kLog2e, -mL)) * inv - 1.f) * gscale));
   }
   if (tid == 0) {
-    float xl = (label >= 0 && label < cols) ? (float)to_acc<T>(srow[label]) : m;
     row_loss[r] = __logf(sum) + m - xl;
     __threadfence();
     s_last = atomicAdd(counter, 1u) == (unsigned)rows - 1;
@@ -255,17 +314,35 @@ __device__ __forceinline__ void absstat_body(const T* __restrict__ x, size_t n, 
   for (size_t i = tail0 + t0; i < n; i += stride) { double v = fabs((double)to_acc<T>(x[i])); a += v; b += v * v; }
   const T* xb = x + head;
   size_t i = t0;
-  for (; i + stride < nv; i += 2 * stride) {
-    Pack<T, V> p0 = ld_pack<T, V>(xb + i * V), p1 = ld_pack<T, V>(xb + (i + stride) * V);
+  if constexpr (sizeof(T) == 8) {
+    for (; i < nv; i += stride) {
+      Pack<T, V> p0 = ld_pack<T, V>(xb + i * V);
 #pragma unroll
-    for (int k = 0; k < V; ++k) { double v = fabs((double)to_acc<T>(p0.v[k])); a += v; b += v * v; }
+      for (int k = 0; k < V; ++k) { double v = fabs((double)to_acc<T>(p0.v[k])); a += v; b += v * v; }
+    }
+  } else {
+    // Four packs in flight per thread; their 16 to 32 elements are summed in fp32 (a short chain, so the rounding
+    // stays near 1e-7 relative) and only the two partial sums go through the slow fp32 -> fp64 conversion.
+    constexpr int U = 4;
+    auto fold = [&](const Pack<T, V>& p, float& fa, float& fb) {
 #pragma unroll
-    for (int k = 0; k < V; ++k) { double v = fabs((double)to_acc<T>(p1.v[k])); a += v; b += v * v; }
-  }
-  for (; i < nv; i += stride) {
-    Pack<T, V> p0 = ld_pack<T, V>(xb + i * V);
+      for (int k = 0; k < V; ++k) { float v = fabsf((float)to_acc<T>(p.v[k])); fa += v; fb = fmaf(v, v, fb); }
+    };
+    for (; i + (U - 1) * stride < nv; i += U * stride) {
+      Pack<T, V> p[U];
 #pragma unroll
-    for (int k = 0; k < V; ++k) { double v = fabs((double)to_acc<T>(p0.v[k])); a += v; b += v * v; }
+      for (int u = 0; u < U; ++u) p[u] = ld_pack<T, V>(xb + (i + u * stride) * V);
+      float fa = 0.f, fb = 0.f;
+#pragma unroll
+      for (int u = 0; u < U; ++u) fold(p[u], fa, fb);
+      a += (double)fa; b += (double)fb;
+    }
+    for (; i < nv; i += stride) {
+      Pack<T, V> p0 = ld_pack<T, V>(xb + i * V);
+      float fa = 0.f, fb = 0.f;
+      fold(p0, fa, fb);
+      a += (double)fa; b += (double)fb;
+    }
   }
   for (int o = 16; o; o >>= 1) { a += __shfl_xor_sync(~0u, a, o); b += __shfl_xor_sync(~0u, b, o); }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -279,12 +356,20 @@ __device__ __forceinline__ void absstat_body(const T* __restrict__ x, size_t n, 
     s_last = atomicAdd(counter, 1u) == gridDim.x - 1;
   }
   __syncthreads();
-  if (s_last && threadIdx.x == 0) {
+  if (s_last) {                  // the last block sums the partials: a fixed tree, the same bits on every run
     __threadfence();
     double ta = 0.0, tb = 0.0;
-    for (unsigned i = 0; i < gridDim.x; ++i) { ta += partial[2 * i]; tb += partial[2 * i + 1]; }  // block order
-    out2[0] = ta; out2[1] = tb;
-    *counter = 0;   // ready for the next launch
+    for (unsigned i = threadIdx.x; i < gridDim.x; i += kStatThreads) { ta += partial[2 * i]; tb += partial[2 * i + 1]; }
+    for (int o = 16; o; o >>= 1) { ta += __shfl_xor_sync(~0u, ta, o); tb += __shfl_xor_sync(~0u, tb, o); }
+    __syncthreads();
+    if (lane == 0) { s1[warp] = ta; s2[warp] = tb; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      ta = 0.0; tb = 0.0;
+      for (int w = 0; w < kStatThreads / 32; ++w) { ta += s1[w]; tb += s2[w]; }
+      out2[0] = ta; out2[1] = tb;
+      *counter = 0;   // ready for the next launch
+    }
   }
 }
 

@@ -20,6 +20,7 @@ enum CollOp {
   OP_BARRIER,
   OP_AR_TWOSHOT_ANY,    // two-shot on tensors outside the heap: scatter-push, local reduce, gather-pull
   OP_BCAST_ANY,         // broadcast of a tensor outside the heap: root pushes into scratch, peers copy out
+  OP_BCAST_SCATTER_MC,  // member m reads chunk m from the root and stores it through the multicast mapping
   OP_COUNT
 };
 
