@@ -160,11 +160,55 @@ def test_fused_engine_single_gpu_matches_torch_sgd(fused_bn):
                     moms[i] = g.clone() if moms[i] is None else moms[i].mul_(0.9).add_(g)
                     masters[i].add_(moms[i], alpha=-0.05)
                     p.copy_(masters[i])
+        # bf16 activations: the two runs only differ by rounding (the loss gradient is rounded to bf16 from another
+        # intermediate), which a freshly initialised batch-norm shift of order 1e-3 amplifies in relative terms:
+        # compare all parameters together, and each tensor against a floor of its own scale
+        num = sum((p.float() - q.float()).square().sum().item() for p, q in zip(model.parameters(), ref.parameters()))
+        den = sum(q.float().square().sum().item() for q in ref.parameters())
+        assert (num / den) ** 0.5 < 5e-3, (num / den) ** 0.5
         worst = 0.0
         for p, q in zip(model.parameters(), ref.parameters()):
-            worst = max(worst, (p.float() - q.float()).abs().max().item() / (q.float().abs().max().item() + 1e-3))
-        assert worst < 0.05, worst           # bf16 activations: the two runs only differ by rounding
+            worst = max(worst, (p.float() - q.float()).abs().max().item() / (q.float().abs().max().item() + 0.05))
+        assert worst < 0.05, worst
         for p in model.parameters():
             assert torch.count_nonzero(p.grad) == 0      # gradients cleared by the kernel
+    finally:
+        mpi.stop()
+
+
+@pytest.mark.gpu
+def test_fused_sgd_accumulates_micro_batches():
+    """Two micro-batches under ``accumulate()`` + one outside give the step of the summed gradient."""
+    import copy
+    import torchmpi_b200 as mpi
+    from torchmpi_b200.parallel.fused_sgd import FusedSGD
+    mpi.start(with_cuda=True)
+    try:
+        dev = mpi.device
+        torch.manual_seed(3)
+        net = torch.nn.Sequential(torch.nn.Linear(64, 96), torch.nn.Tanh(), torch.nn.Linear(96, 10)).to(dev)
+        ref = copy.deepcopy(net)
+        opt = FusedSGD(net.parameters(), momentum=0.9, bucket_bytes=8 << 10)
+        sgd = torch.optim.SGD(ref.parameters(), lr=0.1, momentum=0.9)
+        for step in range(3):
+            xs = [torch.randn(16, 64, device=dev) for _ in range(3)]
+            opt.begin_step(0.1)
+            launched = opt.launches
+            with opt.accumulate():
+                for x in xs[:2]:
+                    net(x).square().mean().backward()
+            assert opt.launches == launched           # nothing reduced inside the context
+            net(xs[2]).square().mean().backward()
+            opt.finish_step()
+            sgd.zero_grad()
+            for x in xs:
+                ref(x).square().mean().backward()
+            sgd.step()
+        torch.cuda.synchronize()
+        opt.check()
+        for p, q in zip(net.parameters(), ref.parameters()):
+            assert torch.allclose(p, q, atol=2e-5, rtol=1e-4), (p - q).abs().max().item()
+            assert torch.count_nonzero(p.grad) == 0
+        opt.remove_hooks()
     finally:
         mpi.stop()

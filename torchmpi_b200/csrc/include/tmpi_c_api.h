@@ -284,6 +284,12 @@ size_t tmpi_conv_wgrad_workspace_bytes(int N, int H, int W, int Cin, int Cout, i
 int tmpi_conv_wgrad(const void* dy, const void* x, void* dw, int N, int H, int W, int Cin, int Cout, int R, int S,
                     int stride, int pad, void* workspace, size_t workspace_bytes, int accumulate, void* stream);
 int tmpi_conv_status(void);
+// causal self-attention forward, head size 64, bf16: q, k, v as [B * T, H * 64] matrices with one row pitch (the column
+// blocks of a fused QKV projection), out [B * T, ld_out], lse [B, H, T] fp32 (optional); T a multiple of 128
+int tmpi_attention_fwd(const void* q, const void* k, const void* v, int64_t ld_qkv, void* out, int64_t ld_out, float* lse,
+                       int B, int T, int H, float scale, void* stream);
+int tmpi_attention_ctas_per_sm(void);
+int tmpi_attention_status(void);
 // C[M, N] (+)= A^T B for A [K, M], B [K, N] with a long K and a small output (split over K; same kernel family)
 size_t tmpi_gemm_tn_splitk_workspace_bytes(int M, int N, int64_t K);
 int tmpi_gemm_bf16_tn_splitk(const void* A, const void* B, void* C, int M, int N, int64_t K, int64_t lda, int64_t ldb,

@@ -2,10 +2,11 @@
 
 Used by the hierarchical-training config: synchronous fused allreduce inside a group of GPUs, a
 GPU-resident parameter server across groups.  The reference has no sequence model
-(its largest network is a 6-layer Linear stack, test/async.lua:37-43).  Attention uses PyTorch's
-scaled-dot-product attention; the matrix products of the MLP and projections go through
-``ops.gemm.linear`` (the tcgen05 kernel) when ``tc_linear=True``, which also selects the one-pass
-layer norm of ``ops.layernorm`` and the pitched LM head of ``ops.gemm.wide_head``; the loss is ``ops.xent``.
+(its largest network is a 6-layer Linear stack, test/async.lua:37-43).  With ``tc_linear=True`` the matrix
+products of the MLP and projections go through ``ops.gemm.linear`` (the tcgen05 kernel), attention through
+``ops.attention`` (its own tcgen05 forward kernel on the packed QKV projection; PyTorch's scaled-dot-product
+attention otherwise, and for shapes that kernel does not take), layer norm through the one-pass ``ops.layernorm``
+and the LM head through the pitched ``ops.gemm.wide_head``; the loss is ``ops.xent``.
 """
 from __future__ import annotations
 
@@ -61,6 +62,7 @@ class Block(nn.Module):
     def __init__(self, c: GPT2Config):
         super().__init__()
         self.n_head = c.n_head
+        self.own_attention = c.tc_linear
         self.ln1 = _layer_norm(c)
         self.qkv = _Linear(c.n_embd, 3 * c.n_embd, c.tc_linear)
         self.proj = _Linear(c.n_embd, c.n_embd, c.tc_linear)
@@ -70,10 +72,14 @@ class Block(nn.Module):
 
     def forward(self, x):
         B, T, C = x.shape
-        q, k, v = self.qkv(self.ln1(x).to(x.dtype)).split(C, dim=2)
-        q, k, v = (t.view(B, T, self.n_head, C // self.n_head).transpose(1, 2) for t in (q, k, v))
-        a = F.scaled_dot_product_attention(q, k, v, is_causal=True)
-        x = x + self.proj(a.transpose(1, 2).reshape(B, T, C))
+        qkv = self.qkv(self.ln1(x).to(x.dtype))
+        if self.own_attention:
+            from ..ops import attention
+            a = attention.causal_attention(qkv, self.n_head)
+        else:
+            q, k, v = (t.view(B, T, self.n_head, C // self.n_head).transpose(1, 2) for t in qkv.split(C, dim=2))
+            a = F.scaled_dot_product_attention(q, k, v, is_causal=True).transpose(1, 2).reshape(B, T, C)
+        x = x + self.proj(a)
         return x + self.out(self.fc(self.ln2(x).to(x.dtype)))
 
 

@@ -14,11 +14,13 @@ backward, or per-layer async allreduces, then torchnet's per-tensor update
 (torchmpi/nn.lua:49-56,112-242; torchmpi/engine/sgdengine.lua:126-147) - folded
 into one launch per bucket with no NCCL call and no elementwise kernel.
 
-Limits: one backward pass per step (no gradient accumulation across passes);
-all parameters of the model must share one dtype per bucket.
+Several backward passes per step (gradient accumulation over micro-batches): run all but the last inside
+``with opt.accumulate():``; those passes only add to the gradient buckets, and the buckets are reduced and applied
+during the last pass, still overlapped with its backward.  All parameters of a bucket must share one dtype.
 """
 from __future__ import annotations
 
+import contextlib
 from typing import Iterable, List, Optional, Sequence
 
 import torch
@@ -46,6 +48,7 @@ class FusedSGD:
         self.lr = 0.0
         self.step_count = 0
         self.launches = 0
+        self._defer = False
         params = [p for p in params if p.requires_grad]
         self.buckets = FlatBuckets(params, bucket_bytes or config.get("bucket_bytes"), pad_to=128 * self.N,
                                    allocator=self.heap.allocator())
@@ -91,7 +94,19 @@ class FusedSGD:
         b.extra["launched"] = True
         self.launches += 1
 
+    @contextlib.contextmanager
+    def accumulate(self):
+        """Backward passes inside this context add their gradients to the buckets without launching the reduction
+        (micro-batches of one optimizer step); the next pass outside it reduces and applies the sum."""
+        self._defer = True
+        try:
+            yield self
+        finally:
+            self._defer = False
+
     def _on_bucket_ready(self, b: Bucket) -> None:
+        if self._defer:
+            return
         # gradients of this bucket are complete on the compute stream: hand it to the comm stream
         self.comm_stream.wait_stream(torch.cuda.current_stream())
         self._launch(b, self.comm_stream)

@@ -83,7 +83,14 @@ def cases(small: bool):
     out["xent_fwd_bwd"] = (lambda: xent._XentFn.apply(logits, labels), rows * cols * 2 * 2)  # x once (the row is kept in shared memory), dx once
 
     big = torch.randn((64 if small else 256) << 20, device=dev)
-    out["absmean_var"] = (lambda: stats.absmean_var(big), big.numel() * 4)
+    stat_scratch = torch.zeros(lib.tmpi_absmean_var_scratch_bytes(), dtype=torch.uint8, device=dev)
+    stat_out = torch.empty(2, dtype=torch.float64, device=dev)
+
+    def absstat():                  # the kernel alone (stats.absmean_var adds a device-to-host read of the two sums)
+        check(lib.tmpi_absmean_var(big.data_ptr(), dtype_code(big.dtype), big.numel(), stat_out.data_ptr(),
+                                   stat_scratch.data_ptr(), stream_ptr()))
+    out["absmean_var"] = (absstat, big.numel() * 4)
+    out["absmean_var_with_readback"] = (lambda: stats.absmean_var(big), big.numel() * 4)
 
     from torchmpi_b200 import config
     from torchmpi_b200.ops import gemm
@@ -161,6 +168,20 @@ def lazy_cases(small: bool) -> dict:
                       "3x3_14_256_256": (14, 256, 256, 3, 1, 1)}.items():
         for mode in ("fwd", "fwd_stats", "dgrad", "dgrad_add", "wgrad", "cudnn_fwd"):
             out[f"conv_{tag}_{mode}"] = conv_case(*geom, mode)
+
+    def attn_case(own):
+        def build():
+            from torchmpi_b200.ops import attention
+            Bq, T, H = (2 if small else 8), 1024, 16                      # GPT-2 medium: 16 heads of 64
+            qkv = torch.randn(Bq, T, 3 * H * 64, device=dev).to(torch.bfloat16)
+            flops = 4.0 * Bq * H * T * T * 64 / 2                          # causal: half of the score matrix
+            nbytes = qkv.numel() * 2 + Bq * T * H * 64 * 2
+            if own:
+                return (lambda: attention.attention_forward(qkv, H)), nbytes, flops
+            return (lambda: attention._reference(qkv, H)), nbytes, flops
+        return build
+    out["attention_fwd"] = attn_case(True)
+    out["attention_sdpa_fwd"] = attn_case(False)
 
     def ln_case(backward):
         def build():
