@@ -133,21 +133,21 @@ def test_oneshot_slots_stay_inside_their_lane(emu):
             assert not bool((v[lo:hi] == 0x5A).all())
 
 
-@pytest.mark.parametrize("algo", [1, 2])    # 1 = pull (auto small), 2 = chunked
+@pytest.mark.parametrize("algo", [1, 2, 5])    # 1 = pull (auto small), 2 = chunked, 5 = scatter + push in one pass
 def test_broadcast(emu, algo):
     from torchmpi_b200._lib import lib, check
     h, W = emu, emu.world
     lib.tmpi_cuda_heap_reset_allocator(0)
     for n in (16, 4099 * 16, 1 << 20):
-        off, ts = fill(h, n, torch.uint8 if False else torch.int8, 3)
-        root = W - 1
-        want = ts[root].clone()
-        g, keep = group(W)
-        check(lib.tmpi_cuda_broadcast_heap(off, n, 1, root, C.byref(g), algo, torch.cuda.current_stream().cuda_stream))
-        torch.cuda.synchronize()
-        status_ok(h)
-        for t in ts:
-            assert torch.equal(t, want)
+        for root in (W - 1, 0):
+            off, ts = fill(h, n, torch.uint8 if False else torch.int8, 3)
+            want = ts[root].clone()
+            g, keep = group(W)
+            check(lib.tmpi_cuda_broadcast_heap(off, n, 1, root, C.byref(g), algo, torch.cuda.current_stream().cuda_stream))
+            torch.cuda.synchronize()
+            status_ok(h)
+            for t in ts:
+                assert torch.equal(t, want)
 
 
 def test_reduce_allgather_reduce_scatter(emu):

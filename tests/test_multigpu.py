@@ -102,9 +102,10 @@ def _collectives(rank, world, backend):
     mpi.p2p.allreduce_tensor(sym)
     assert torch.all(sym == n * (n + 1) // 2)
     # every broadcast algorithm on a heap tensor whose length does not split evenly (pull, scatter + all-gather,
-    # multicast store, scatter + multicast stores; the multicast ones fall back to the pull without a mapping)
+    # multicast store, scatter + multicast stores, scatter + plain stores; the multicast ones fall back to the pull
+    # without a mapping)
     symb = heap.empty((1 << 20) + 8 * 13, torch.bfloat16)
-    for algo in (1, 2, 3, 4):
+    for algo in (1, 2, 3, 4, 5):
         mpi.config.set("broadcast_algo", algo)
         for root in (0, n - 1):
             symb.copy_((torch.arange(symb.numel(), device=dev) % 251 + rank * 7).to(torch.bfloat16))

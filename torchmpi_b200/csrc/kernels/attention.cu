@@ -24,6 +24,7 @@
 #include <stdint.h>
 #include <mutex>
 #include "sm100_ptx.cuh"
+#include "attn_util.cuh"
 #include "../include/tmpi_c_api.h"
 #include "../runtime/common.h"
 
@@ -34,31 +35,34 @@ int make_tmap_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t c
 }
 
 namespace attn {
+using namespace attn_util;
 
 constexpr int BQ = 128, BKV = 128, D = 64, THREADS = 320, UMMA_K = 16;
 constexpr int TILE_BYTES = 128 * D * 2;                       // a 128 x 64 bf16 tile: 16 KB
 constexpr int P_BYTES = BQ * BKV * 2;                         // 32 KB: two K-major chunks of 64 keys
 constexpr int SMEM_TILES = TILE_BYTES * 4 + P_BYTES;          // Q, K x 2, V, P
-constexpr int V_OFF = TILE_BYTES * 3, P_OFF = TILE_BYTES * 4;
-constexpr int SMEM_DYNAMIC = SMEM_TILES + 128;                // the barrier block follows the tiles
+constexpr int V_OFF = TILE_BYTES * 3;                          // P follows the one or two V buffers
+constexpr int SMEM_SHARED = 256;                              // the barrier block follows the tiles
 constexpr int TMEM_COLS = 256;                                // S: columns 0-127, O_j: columns 128-191
 constexpr unsigned long long kWaitBudgetNs = 2000000000ull;
 
 struct alignas(128) Shared {
-  uint64_t q_full, k_full[2], k_empty[2], v_full, v_empty, s_full, s_empty, p_full, o_full;
+  uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full, s_empty, p_full, o_full;
   uint64_t pair[4];            // the 64 threads that share 32 rows meet here (bounded, unlike a named barrier)
   uint32_t tmem_base;
   int error;
 };
-static_assert(sizeof(Shared) == 128, "barrier block");
+static_assert(sizeof(Shared) <= SMEM_SHARED, "barrier block");
 
 struct Params {
   int B, T, H, q_blocks;
+  int v_stages;                // 1 or 2 V buffers (2 prefetches V a block ahead and costs 16 KB of shared memory)
   float scale_log2;            // softmax scale times log2(e)
   __nv_bfloat16* out;          // [B * T, ld_out], head h at columns h * 64
   int ld_out;
   float* lse;                  // [B, H, T]: natural-log sum of exponentials of the scaled scores
   int* status;
+  unsigned long long* trace;   // optional: time stamps of the phases of CTA 0 (see tmpi_attention_set_trace)
 };
 
 __device__ __forceinline__ void fail(Shared* sh, const Params& p, int where) {
@@ -66,14 +70,13 @@ __device__ __forceinline__ void fail(Shared* sh, const Params& p, int where) {
   if (p.status) atomicCAS(p.status, 0, 3000 + where);
 }
 
+// Phase time stamps of one CTA for tuning: slot = (block * 16 + event), written by one thread per role.
+__device__ __forceinline__ void stamp(const Params& p, int j, int ev) {
+  if (p.trace && blockIdx.x == 0) p.trace[j * 16 + ev] = sm100::now_ns();
+}
+
 #define ATTN_WAIT(bar, parity, where) \
   do { if (!sm100::mbar_wait((bar), (parity), kWaitBudgetNs) || sh->error) { fail(sh, p, (where)); return; } } while (0)
-
-__device__ __forceinline__ float ex2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
 
 __device__ void producer(Shared* sh, unsigned char* tiles, const Params& p, const CUtensorMap* mq, const CUtensorMap* mk,
                          const CUtensorMap* mv, int b, int h, int qblk) {
@@ -90,23 +93,41 @@ __device__ void producer(Shared* sh, unsigned char* tiles, const Params& p, cons
       if (j + 1 >= 2) ATTN_WAIT(&sh->k_empty[(j + 1) & 1], (((j + 1) >> 1) - 1) & 1, 1);   // S of block j - 1 has read this stage
       load_k(j + 1);
     }
-    if (j >= 1) ATTN_WAIT(&sh->v_empty, (j - 1) & 1, 13);                  // P V of block j - 1 has read V
-    sm100::mbar_expect_tx(&sh->v_full, TILE_BYTES);
-    sm100::tma_load_2d(tiles + V_OFF, mv, h * D, row0 + j * BKV, &sh->v_full);
+    const int vs = p.v_stages == 2 ? (j & 1) : 0, vuse = p.v_stages == 2 ? (j >> 1) : j;
+    if (vuse >= 1) ATTN_WAIT(&sh->v_empty[vs], (vuse - 1) & 1, 13);        // the P V that read this buffer is done
+    sm100::mbar_expect_tx(&sh->v_full[vs], TILE_BYTES);
+    sm100::tma_load_2d(tiles + V_OFF + vs * TILE_BYTES, mv, h * D, row0 + j * BKV, &sh->v_full[vs]);
   }
 }
 
 __device__ void mma_issuer(Shared* sh, unsigned char* tiles, const Params& p, int qblk) {
   const uint32_t tmem_s = sh->tmem_base, tmem_o = sh->tmem_base + 128;
-  const uint32_t q_addr = sm100::smem_u32(tiles), p_addr = sm100::smem_u32(tiles + P_OFF);
+  const uint32_t q_addr = sm100::smem_u32(tiles), p_addr = sm100::smem_u32(tiles + V_OFF + p.v_stages * TILE_BYTES);
   constexpr uint32_t idesc_s = sm100::make_idesc_f16(BQ, BKV, true);            // Q and K both K-major
   constexpr uint32_t idesc_o = sm100::make_idesc_f16(BQ, D, true, true);        // P K-major, V MN-major (d contiguous)
-  auto issue_s = [&](int j) {
-    const uint32_t k_addr = sm100::smem_u32(tiles + TILE_BYTES * (1 + (j & 1)));
+  // descriptors of every operand slice, built once
+  uint64_t dq[D / UMMA_K], dk[2][D / UMMA_K], dp[BKV / UMMA_K], dv[2][BKV / UMMA_K];
+  const uint32_t v_addr = sm100::smem_u32(tiles + V_OFF);
 #pragma unroll
-    for (int k = 0; k < D / UMMA_K; ++k)
-      sm100::umma_f16(tmem_s, sm100::make_desc_sw128(q_addr + k * UMMA_K * 2), sm100::make_desc_sw128(k_addr + k * UMMA_K * 2),
-                      idesc_s, k > 0 ? 1u : 0u);
+  for (int k = 0; k < D / UMMA_K; ++k) {
+    dq[k] = sm100::make_desc_sw128(q_addr + k * UMMA_K * 2);
+    dk[0][k] = sm100::make_desc_sw128(sm100::smem_u32(tiles + TILE_BYTES) + k * UMMA_K * 2);
+    dk[1][k] = sm100::make_desc_sw128(sm100::smem_u32(tiles + 2 * TILE_BYTES) + k * UMMA_K * 2);
+  }
+#pragma unroll
+  for (int k = 0; k < BKV / UMMA_K; ++k) {
+    dp[k] = sm100::make_desc_sw128(p_addr + (k >> 2) * TILE_BYTES + (k & 3) * UMMA_K * 2);
+    dv[0][k] = sm100::make_desc_sw128_mn(v_addr + k * UMMA_K * 128, TILE_BYTES, 1024);
+    dv[1][k] = sm100::make_desc_sw128_mn(v_addr + TILE_BYTES + k * UMMA_K * 128, TILE_BYTES, 1024);
+  }
+  auto issue_s = [&](int j) {
+    if (j & 1) {
+#pragma unroll
+      for (int k = 0; k < D / UMMA_K; ++k) sm100::umma_f16(tmem_s, dq[k], dk[1][k], idesc_s, k > 0 ? 1u : 0u);
+    } else {
+#pragma unroll
+      for (int k = 0; k < D / UMMA_K; ++k) sm100::umma_f16(tmem_s, dq[k], dk[0][k], idesc_s, k > 0 ? 1u : 0u);
+    }
     sm100::umma_commit(&sh->s_full);
     sm100::umma_commit(&sh->k_empty[j & 1]);
   };
@@ -117,21 +138,80 @@ __device__ void mma_issuer(Shared* sh, unsigned char* tiles, const Params& p, in
   for (int j = 0; j <= qblk; ++j) {
     if (j < qblk) {                      // S of the next block, as soon as this block's S has been read
       ATTN_WAIT(&sh->s_empty, j & 1, 4);
+      stamp(p, j, 8);
       ATTN_WAIT(&sh->k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, 5);
       sm100::tc_fence_after();
       issue_s(j + 1);
+      stamp(p, j, 9);
     }
     ATTN_WAIT(&sh->p_full, j & 1, 6);
-    ATTN_WAIT(&sh->v_full, j & 1, 14);
+    stamp(p, j, 10);
+    const int vs = p.v_stages == 2 ? (j & 1) : 0, vuse = p.v_stages == 2 ? (j >> 1) : j;
+    ATTN_WAIT(&sh->v_full[vs], vuse & 1, 14);
+    stamp(p, j, 11);
     sm100::tc_fence_after();
-    const uint32_t v_addr = sm100::smem_u32(tiles + V_OFF);
+    if (vs) {
 #pragma unroll
-    for (int k = 0; k < BKV / UMMA_K; ++k)
-      sm100::umma_f16(tmem_o, sm100::make_desc_sw128(p_addr + (k >> 2) * TILE_BYTES + (k & 3) * UMMA_K * 2),
-                      sm100::make_desc_sw128_mn(v_addr + k * UMMA_K * 128, TILE_BYTES, 1024), idesc_o, k > 0 ? 1u : 0u);
+      for (int k = 0; k < BKV / UMMA_K; ++k) sm100::umma_f16(tmem_o, dp[k], dv[1][k], idesc_o, k > 0 ? 1u : 0u);
+    } else {
+#pragma unroll
+      for (int k = 0; k < BKV / UMMA_K; ++k) sm100::umma_f16(tmem_o, dp[k], dv[0][k], idesc_o, k > 0 ? 1u : 0u);
+    }
     sm100::umma_commit(&sh->o_full);
-    sm100::umma_commit(&sh->v_empty);
+    sm100::umma_commit(&sh->v_empty[vs]);
+    stamp(p, j, 12);
   }
+}
+
+// One thread's 64 scores of a block: P = exp2(S * c2 + nmc) as bf16 into the swizzled K-major tile; returns their sum.
+// DIAG: the block on the diagonal, where a key after the query gives 0 and whole chunks of 32 keys may be masked
+// for the warp (then there is nothing to load or exponentiate).
+template <bool DIAG>
+__device__ __forceinline__ float exp_pass(Shared* sh, uint32_t (&r)[32], uint32_t tmem_s, unsigned char* p_row, int row, int half,
+                                          int last_row, float c2, float nmc) {
+  const unsigned long long c2x2 = pack2(__float_as_uint(c2), __float_as_uint(c2));
+  const unsigned long long nmc2 = pack2(__float_as_uint(nmc), __float_as_uint(nmc));
+  unsigned long long rs2 = 0ull;                          // two partial sums (0.f, 0.f)
+#pragma unroll 1
+  for (int c = 0; c < 2; ++c) {
+    const int key0 = half * 64 + c * 32;
+    const bool masked = DIAG && key0 > last_row;           // warp-uniform
+    if (!masked) {
+      sm100::tmem_ld_32x32(tmem_s + c * 32, r);
+      sm100::tmem_ld_wait();
+    }
+    if (c == 1) {                                         // S is in registers: the next S may overwrite it
+      sm100::tc_fence_before();
+      sm100::mbar_arrive(&sh->s_empty);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {                          // eight keys = one 16-byte unit of the swizzled row
+      uint32_t w[4] = {0u, 0u, 0u, 0u};
+      if (!masked) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int i = u * 8 + 2 * q;
+          float a0, a1;
+          unpack2(fma2(pack2(r[i], r[i + 1]), c2x2, nmc2), a0, a1);
+          // a quarter of the exponentials on the FMA pipe, the rest on the special-function unit
+          float e0 = q == 3 ? ex2_fma(a0) : ex2(a0);
+          float e1 = q == 3 ? ex2_fma(a1) : ex2(a1);
+          if (DIAG) {
+            if (key0 + i > row) e0 = 0.f;
+            if (key0 + i + 1 > row) e1 = 0.f;
+          }
+          rs2 = add2(rs2, pack2(__float_as_uint(e0), __float_as_uint(e1)));
+          __nv_bfloat162 hh = __floats2bfloat162_rn(e0, e1);
+          w[q] = *reinterpret_cast<uint32_t*>(&hh);
+        }
+      }
+      const int unit = c * 4 + u;
+      *reinterpret_cast<uint4*>(p_row + ((unit ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+  float rs0, rs1;
+  unpack2(rs2, rs0, rs1);
+  return rs0 + rs1;
 }
 
 // Two threads per query row: the warps with the same (warp & 3) read the same 32 tensor-memory lanes; `half` picks
@@ -144,72 +224,72 @@ __device__ void softmax_rows(Shared* sh, unsigned char* tiles, const Params& p, 
   const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
   const uint32_t tmem_row = sh->tmem_base + lane_base, tmem_s = tmem_row + half * 64;
   const uint32_t tmem_o = sh->tmem_base + 128 + lane_base + half * 32;
-  unsigned char* p_row = tiles + P_OFF + half * TILE_BYTES + row * 128;      // chunk `half`: keys 64 half ...
-  float* xch = reinterpret_cast<float*>(tiles + P_OFF);     // the P tile, once the last MMA has read it
+  unsigned char* p_tile = tiles + V_OFF + p.v_stages * TILE_BYTES;
+  unsigned char* p_row = p_tile + half * TILE_BYTES + row * 128;      // chunk `half`: keys 64 half ...
+  float* xch = reinterpret_cast<float*>(p_tile);     // the P tile, once the last MMA has read it
   const float c2 = p.scale_log2;
   float m = -INFINITY, l = 0.f;
-  float acc[D / 2];
+  unsigned long long acc2[D / 4];                         // this thread's 32 output columns, two per register pair
 #pragma unroll
-  for (int i = 0; i < D / 2; ++i) acc[i] = 0.f;
+  for (int i = 0; i < D / 4; ++i) acc2[i] = 0ull;
   uint32_t r[32];
-  for (int j = 0; j <= qblk; ++j) {
+  const int last_row = quarter * 32 + 31;                 // a chunk of keys beyond it is masked for the whole warp
+  // the maximum of the row over block j (on the diagonal block a key after the query is masked)
+  auto row_max = [&](int j, float mx) {
     const bool diag = j == qblk;
-    ATTN_WAIT(&sh->s_full, j & 1, 7);
-    sm100::tc_fence_after();
-    // first pass over the whole row: its maximum (a masked entry is a key after the query)
-    float mx = m;
 #pragma unroll 1
     for (int c = 0; c < BKV / 32; ++c) {
+      if (diag && c * 32 > last_row) break;
       sm100::tmem_ld_32x32(tmem_row + c * 32, r);
       sm100::tmem_ld_wait();
+      if (!diag) {
 #pragma unroll
-      for (int i = 0; i < 32; ++i)
-        if (!diag || c * 32 + i <= row) mx = fmaxf(mx, __uint_as_float(r[i]));
+        for (int i = 0; i < 32; i += 2) mx = max3(mx, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (c * 32 + i <= row) mx = fmaxf(mx, __uint_as_float(r[i]));
+      }
     }
+    return mx;
+  };
+  const bool tracer = row == 0 && half == 0;
+  if (tracer) stamp(p, 0, 0);
+  ATTN_WAIT(&sh->s_full, 0, 7);
+  if (tracer) stamp(p, 0, 1);
+  sm100::tc_fence_after();
+  float mx = row_max(0, m);
+  for (int j = 0; j <= qblk; ++j) {
+    const bool diag = j == qblk;
+    if (tracer) stamp(p, j, 2);
     const float alpha = ex2((m - mx) * c2);             // 0 for the first block (m = -inf)
-    const float mc = mx * c2;
-    float rs = 0.f;
+    const float nmc = -mx * c2;
     // second pass: P = exp2(S * c2 - max * c2) as bf16 into the swizzled K-major tile
-#pragma unroll 1
-    for (int c = 0; c < 2; ++c) {
-      sm100::tmem_ld_32x32(tmem_s + c * 32, r);
-      sm100::tmem_ld_wait();
-      if (c == 1) {                                       // S is in registers: the next S may overwrite it
-        sm100::tc_fence_before();
-        sm100::mbar_arrive(&sh->s_empty);
-      }
-      const int key0 = half * 64 + c * 32;
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {                        // eight keys = one 16-byte unit of the swizzled row
-        uint32_t w[4];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int i = u * 8 + 2 * q;
-          float e0 = ex2(fmaf(__uint_as_float(r[i]), c2, -mc));
-          float e1 = ex2(fmaf(__uint_as_float(r[i + 1]), c2, -mc));
-          if (diag) {
-            if (key0 + i > row) e0 = 0.f;
-            if (key0 + i + 1 > row) e1 = 0.f;
-          }
-          rs += e0 + e1;
-          __nv_bfloat162 hh = __floats2bfloat162_rn(e0, e1);
-          w[q] = *reinterpret_cast<uint32_t*>(&hh);
-        }
-        const int unit = c * 4 + u;
-        *reinterpret_cast<uint4*>(p_row + ((unit ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-      }
-    }
+    const float rs = diag ? exp_pass<true>(sh, r, tmem_s, p_row, row, half, last_row, c2, nmc)
+                          : exp_pass<false>(sh, r, tmem_s, p_row, row, half, last_row, c2, nmc);
     l = l * alpha + rs;
     m = mx;
-    sm100::fence_proxy_async();                           // the MMA reads P through the async proxy
+    if (tracer) stamp(p, j, 3);
+    sm100::fence_proxy_async_smem();                      // the MMA reads P through the async proxy
     sm100::mbar_arrive(&sh->p_full);
+    if (tracer) stamp(p, j, 4);
+    // while the tensor core multiplies P by V: the maximum of the next block's scores, which are already there
+    if (j < qblk) {
+      ATTN_WAIT(&sh->s_full, (j + 1) & 1, 7);
+      if (tracer) stamp(p, j + 1, 1);
+      sm100::tc_fence_after();
+      mx = row_max(j + 1, m);
+    }
     // running output: this thread's 32 columns
     ATTN_WAIT(&sh->o_full, j & 1, 8);
+    if (tracer) stamp(p, j, 5);
     sm100::tc_fence_after();
     sm100::tmem_ld_32x32(tmem_o, r);
     sm100::tmem_ld_wait();
+    const unsigned long long al2 = pack2(__float_as_uint(alpha), __float_as_uint(alpha));
 #pragma unroll
-    for (int i = 0; i < 32; ++i) acc[i] = fmaf(acc[i], alpha, __uint_as_float(r[i]));
+    for (int i = 0; i < 16; ++i) acc2[i] = fma2(acc2[i], al2, pack2(r[2 * i], r[2 * i + 1]));
+    if (tracer) stamp(p, j, 6);
     sm100::tc_fence_before();
   }
   // the row sum is the sum of the two halves' partial sums (the last o_full says that the MMAs are done with P)
@@ -225,7 +305,9 @@ __device__ void softmax_rows(Shared* sh, unsigned char* tiles, const Params& p, 
     uint32_t w[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      __nv_bfloat162 hh = __floats2bfloat162_rn(acc[u * 8 + 2 * i] * inv, acc[u * 8 + 2 * i + 1] * inv);
+      float a0, a1;
+      unpack2(acc2[u * 4 + i], a0, a1);
+      __nv_bfloat162 hh = __floats2bfloat162_rn(a0 * inv, a1 * inv);
       w[i] = *reinterpret_cast<uint32_t*>(&hh);
     }
     *reinterpret_cast<uint4*>(o + u * 8) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -238,7 +320,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                      const __grid_constant__ CUtensorMap map_v, const Params p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];   // no static shared memory: the tiles start aligned
   unsigned char* tiles = smem_raw;
-  Shared* sh = (Shared*)(smem_raw + SMEM_TILES);
+  Shared* sh = (Shared*)(smem_raw + SMEM_TILES + (p.v_stages - 1) * TILE_BYTES);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // the longest rows of blocks (near the end of the sequence) start first
   const int bh = blockIdx.x % (p.B * p.H);
@@ -250,8 +332,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     sm100::tma_prefetch_desc(&map_v);
     sm100::mbar_init(&sh->q_full, 1);
     for (int s = 0; s < 2; ++s) { sm100::mbar_init(&sh->k_full[s], 1); sm100::mbar_init(&sh->k_empty[s], 1); }
-    sm100::mbar_init(&sh->v_full, 1);
-    sm100::mbar_init(&sh->v_empty, 1);
+    for (int s = 0; s < 2; ++s) { sm100::mbar_init(&sh->v_full[s], 1); sm100::mbar_init(&sh->v_empty[s], 1); }
     sm100::mbar_init(&sh->s_full, 1);
     sm100::mbar_init(&sh->s_empty, 256);
     sm100::mbar_init(&sh->p_full, 256);
@@ -295,6 +376,10 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 
 }  // namespace attn
 
+static unsigned long long* g_attn_trace = nullptr;
+static int g_attn_v_stages = 1;
+static int attn_smem_bytes() { return attn::SMEM_TILES + (g_attn_v_stages - 1) * attn::TILE_BYTES + attn::SMEM_SHARED; }
+
 static int* attn_status_word(int** host_out = nullptr) {
   static int* dev_ptr = nullptr;
   static int* host_ptr = nullptr;
@@ -325,7 +410,7 @@ int tmpi_attention_fwd(const void* q, const void* k, const void* v, int64_t ld_q
   if ((st = make_tmap_bf16(&mq, q, rows, cols, (uint64_t)ld_qkv, 128))) return st;
   if ((st = make_tmap_bf16(&mk, k, rows, cols, (uint64_t)ld_qkv, 128))) return st;
   if ((st = make_tmap_bf16(&mv, v, rows, cols, (uint64_t)ld_qkv, 128))) return st;
-  cudaError_t ae = cudaFuncSetAttribute(attn::attention_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, attn::SMEM_DYNAMIC);
+  cudaError_t ae = cudaFuncSetAttribute(attn::attention_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, attn_smem_bytes());
   if (ae == cudaSuccess)          // two CTAs per SM need the largest shared-memory carve-out
     ae = cudaFuncSetAttribute(attn::attention_fwd_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
   if (ae != cudaSuccess) return fail(TMPI_ERR_CUDA, "attention: shared memory attribute: %s", cudaGetErrorString(ae));
@@ -334,8 +419,10 @@ int tmpi_attention_fwd(const void* q, const void* k, const void* v, int64_t ld_q
   p.scale_log2 = scale * 1.4426950408889634f;
   p.out = (__nv_bfloat16*)out; p.ld_out = (int)ld_out; p.lse = lse;
   p.status = attn_status_word();
+  p.trace = g_attn_trace;
   const int grid = B * H * p.q_blocks;
-  attn::attention_fwd_kernel<<<grid, attn::THREADS, attn::SMEM_DYNAMIC, (cudaStream_t)stream>>>(mq, mk, mv, p);
+  p.v_stages = g_attn_v_stages;
+  attn::attention_fwd_kernel<<<grid, attn::THREADS, attn_smem_bytes(), (cudaStream_t)stream>>>(mq, mk, mv, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? TMPI_OK : fail(TMPI_ERR_CUDA, "attention launch: %s", cudaGetErrorString(e));
 }
@@ -343,11 +430,20 @@ int tmpi_attention_fwd(const void* q, const void* k, const void* v, int64_t ld_q
 // Resident CTAs of the attention kernel per SM (2 when shared memory and registers allow the intended overlap).
 int tmpi_attention_ctas_per_sm(void) {
   int n = 0;
-  cudaFuncSetAttribute(attn::attention_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, attn::SMEM_DYNAMIC);
+  cudaFuncSetAttribute(attn::attention_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, attn_smem_bytes());
   cudaFuncSetAttribute(attn::attention_fwd_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, attn::attention_fwd_kernel, attn::THREADS, attn::SMEM_DYNAMIC) != cudaSuccess) return -1;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, attn::attention_fwd_kernel, attn::THREADS, attn_smem_bytes()) != cudaSuccess) return -1;
   return n;
 }
+
+// Tuning aid: with a device buffer of (T / 128) * 16 64-bit words, CTA 0 of every later launch (the last query block
+// of the first batch and head) records the time of each phase of each key block (ns): 0 waits for S, 1 has S, 2 row
+// maximum known, 3 P written, 4 P announced, 5 has O_j, 6 output updated; MMA thread: 8 S was read, 9 next S issued,
+// 10 has P, 11 has V, 12 P V issued.  nullptr switches it off.
+// Tuning aid: one or two V buffers per CTA (see Params::v_stages).
+void tmpi_attention_set_v_stages(int n) { g_attn_v_stages = n == 2 ? 2 : 1; }
+
+void tmpi_attention_set_trace(void* device_buffer) { g_attn_trace = (unsigned long long*)device_buffer; }
 
 // Non-zero after an attention CTA gave up on a bounded wait (3000 + the point where it happened); clears it.
 int tmpi_attention_status(void) {

@@ -21,6 +21,7 @@ __device__ __forceinline__ void run_body(const CollArgs& a, int* s_abort) {
   else if constexpr (OP == OP_BCAST_MC) body_bcast_mc<T, V>(a, s_abort);
   else if constexpr (OP == OP_BCAST_ANY) body_bcast_any<T, V>(a, s_abort);
   else if constexpr (OP == OP_BCAST_SCATTER_MC) body_bcast_scatter_mc<T, V>(a, s_abort);
+  else if constexpr (OP == OP_BCAST_SCATTER_PUSH) body_bcast_scatter_push<T, V>(a, s_abort);
   else if constexpr (OP == OP_REDUCE) body_reduce<T, V>(a, s_abort);
   else if constexpr (OP == OP_ALLGATHER) body_allgather<T, V>(a, s_abort);
   else if constexpr (OP == OP_REDUCE_SCATTER) body_reduce_scatter<T, V>(a, s_abort);
@@ -127,6 +128,7 @@ cudaError_t launch_collective(int op, int dtype, const CollArgs* args, int nrank
     case OP_BCAST_CHUNKED: return launch_bytes<OP_BCAST_CHUNKED>(args, nranks, vec, grid, threads, s);
     case OP_BCAST_MC: return launch_typed<OP_BCAST_MC, uint8_t, 16>(args, nranks, grid, threads, s);
     case OP_BCAST_SCATTER_MC: return launch_typed<OP_BCAST_SCATTER_MC, uint8_t, 16>(args, nranks, grid, threads, s);
+    case OP_BCAST_SCATTER_PUSH: return launch_bytes<OP_BCAST_SCATTER_PUSH>(args, nranks, vec, grid, threads, s);
     case OP_ALLGATHER: return launch_bytes<OP_ALLGATHER>(args, nranks, vec, grid, threads, s);
     case OP_BCAST_ANY: return launch_bytes<OP_BCAST_ANY>(args, nranks, vec, grid, threads, s);
     case OP_BARRIER: return launch_typed<OP_BARRIER, uint8_t, 1>(args, nranks, grid, threads, s);

@@ -449,6 +449,53 @@ __device__ void body_bcast_scatter_mc(const CollArgs& a, int* s_abort) {
   }
 }
 
+// Scatter and all-gather in one pass over plain peer pointers: the message is cut into one chunk per non-root
+// member; a member reads its chunk out of the root's buffer and stores every pack it gets into its own buffer and
+// into the other non-root members'.  The root sends each byte once and no link carries more than the message
+// (a multicast store also returns to its sender and to the root, which costs the receivers a quarter of their
+// ingress on four GPUs).  Works on any heap backend: no multicast mapping is needed.
+template <typename T, int V>
+__device__ void body_bcast_scatter_push(const CollArgs& a, int* s_abort) {
+  const Peers& P = a.P;
+  const int N = P.n;
+  const size_t nv = a.n / V;
+  if (!peer_barrier(P, 1, 47, s_abort)) return;
+  if (P.me != a.root) {
+    const int my = P.me < a.root ? P.me : P.me - 1;      // my index among the N - 1 non-root members
+    const size_t per = ceil_div(nv, (size_t)(N - 1));
+    size_t lo = per * my, hi = lo + per;
+    if (lo > nv) lo = nv;
+    if (hi > nv) hi = nv;
+    const T* src = at<T>(P.base[a.root], a.out_off);
+    T* mine = at<T>(P.base[P.me], a.out_off);
+    T* dst[kMaxPeers];                                    // the other non-root members, my neighbour first
+    int nd = 0;
+    for (int j = 1; j < N; ++j) {
+      const int m = (P.me + j) % N;
+      if (m != a.root) dst[nd++] = at<T>(P.base[m], a.out_off);
+    }
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    constexpr int U = 4;
+    size_t i = lo + (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (; i + (U - 1) * stride < hi; i += U * stride) {
+      Pack<T, V> x[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) x[u] = ld_pack_peer<T, V>(src + (i + u * stride) * V);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        st_pack<T, V>(mine + (i + u * stride) * V, x[u]);
+        for (int d = 0; d < nd; ++d) st_pack_peer<T, V>(dst[d] + (i + u * stride) * V, x[u]);
+      }
+    }
+    for (; i < hi; i += stride) {
+      Pack<T, V> x = ld_pack_peer<T, V>(src + i * V);
+      st_pack<T, V>(mine + i * V, x);
+      for (int d = 0; d < nd; ++d) st_pack_peer<T, V>(dst[d] + i * V, x);
+    }
+  }
+  peer_barrier(P, 2, 46, s_abort);
+}
+
 // Broadcast of a tensor that lives outside the heap: the root pushes its buffer into every peer's
 // scratch (one multicast store through the switch when the heap has a multicast mapping, else one
 // store per peer), and after the barrier every other rank copies its scratch into its own tensor.

@@ -21,6 +21,7 @@ enum CollOp {
   OP_AR_TWOSHOT_ANY,    // two-shot on tensors outside the heap: scatter-push, local reduce, gather-pull
   OP_BCAST_ANY,         // broadcast of a tensor outside the heap: root pushes into scratch, peers copy out
   OP_BCAST_SCATTER_MC,  // member m reads chunk m from the root and stores it through the multicast mapping
+  OP_BCAST_SCATTER_PUSH,  // each non-root member reads its chunk from the root and stores it into the other non-root members
   OP_COUNT
 };
 

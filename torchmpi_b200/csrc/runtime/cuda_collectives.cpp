@@ -179,10 +179,12 @@ static int broadcast_heap(size_t off, size_t n, int dtype, int root, const tmpi_
   // with two ranks a multicast store also sends the data back to the root: the pull is faster there
   bool mc_ok = h.mc_base && whole_heap(g) && vec && tunable("use_nvls");
   const bool mc_auto = mc_ok && g->nmembers > 2;
-  // 0 auto, 1 pull, 2 chunked, 3 multicast store from the root, 4 scatter by peer loads + multicast stores by everyone
+  // 0 auto, 1 pull, 2 chunked, 3 multicast store from the root, 4 scatter by peer loads + multicast stores by everyone,
+  // 5 scatter by peer loads + plain stores into the other members (any heap backend)
   if (algo == 0) algo = (int)tunable("broadcast_algo");
   if (algo == 3 && mc_ok) op = OP_BCAST_MC;
   else if (algo == 4 && mc_ok) op = OP_BCAST_SCATTER_MC;
+  else if (algo == 5 && g->nmembers > 2) op = OP_BCAST_SCATTER_PUSH;
   else if (algo == 2) op = OP_BCAST_CHUNKED;
   else if (algo == 0) {
     if (mc_auto && bytes >= (size_t)tunable("bcast_scatter_min_bytes")) op = OP_BCAST_SCATTER_MC;
@@ -191,7 +193,7 @@ static int broadcast_heap(size_t off, size_t n, int dtype, int root, const tmpi_
   }
   return run_op(op, TMPI_U8, g, vec, items, s, [&](int, CollArgs* a) {
     a->out_off = off; a->n = bytes; a->root = root;
-  }, op == OP_BCAST_MC ? "bcast_max_ctas" : op == OP_BCAST_SCATTER_MC ? "bcast_scatter_max_ctas" : "comm_max_ctas");
+  }, op == OP_BCAST_MC ? "bcast_max_ctas" : (op == OP_BCAST_SCATTER_MC || op == OP_BCAST_SCATTER_PUSH) ? "bcast_scatter_max_ctas" : "comm_max_ctas");
 }
 
 static int broadcast_any(void* buf, size_t n, int dtype, int root, const tmpi_group_t* g, cudaStream_t s) {

@@ -5,8 +5,8 @@
 the same buffer) and writes the heads side by side, so there is no transpose before or after it.  It also returns
 the row-wise log-sum-exp that a backward pass needs.
 
-Forward is this package's kernel.  The backward pass is a library kernel fed with this forward's output and
-log-sum-exp: cuDNN's attention backward (``aten._scaled_dot_product_cudnn_attention_backward``, 112 us for
+Forward and backward are this package's kernels (csrc/kernels/attention.cu, attention_bwd.cu).  ``_BACKWARDS`` can
+put a library backward first instead, fed with this forward's output and log-sum-exp: cuDNN's attention backward (``aten._scaled_dot_product_cudnn_attention_backward``, 112 us for
 8 x 16 x 1024 x 64 on a B200), else PyTorch's flash-attention backward (246 us); if neither operator accepts the
 call, the backward recomputes the attention with ``F.scaled_dot_product_attention`` under autograd.
 ``last_backward`` says which one ran.  Shapes the kernel does
@@ -25,7 +25,7 @@ from .._lib import lib, check, has_symbol, stream_ptr, TorchMPIError
 launch_count = 0
 last_backward = ""
 HEAD = 64
-_BACKWARDS = ("cudnn", "flash")          # library backward kernels, in order of preference
+_BACKWARDS = ("own", "cudnn", "flash")   # backward kernels in order of preference: this package's, then the libraries'
 
 
 def supported(qkv: torch.Tensor, n_head: int) -> bool:
@@ -37,7 +37,7 @@ def supported(qkv: torch.Tensor, n_head: int) -> bool:
 
 def check_status() -> None:
     """Raises if an attention CTA gave up on one of its bounded waits since the last call."""
-    st = lib.tmpi_attention_status()
+    st = lib.tmpi_attention_status() or (lib.tmpi_attention_bwd_status() if has_symbol("tmpi_attention_bwd") else 0)
     if st:
         raise TorchMPIError(f"attention kernel: a bounded wait ran out (code {st})")
 
@@ -54,6 +54,25 @@ def attention_forward(qkv: torch.Tensor, n_head: int, need_lse: bool = True):
                                  lse.data_ptr() if need_lse else None, B, T, n_head, 1.0 / math.sqrt(HEAD), stream_ptr()))
     launch_count += 1
     return out, lse
+
+
+def attention_backward(qkv: torch.Tensor, out: torch.Tensor, lse: torch.Tensor, dout: torch.Tensor, n_head: int) -> torch.Tensor:
+    """Gradient of the packed projection ``[B, T, 3 C]`` on this package's backward kernel: dK and dV are written
+    into their column blocks by the kernel, dQ is accumulated in fp32 and rounded into its block afterwards."""
+    global launch_count
+    B, T, C3 = qkv.shape
+    C = C3 // 3
+    dout = dout.contiguous()
+    dqkv = torch.empty_like(qkv)
+    dq_acc = torch.zeros((B * T, C), dtype=torch.float32, device=qkv.device)
+    delta = torch.empty((B, n_head, T), dtype=torch.float32, device=qkv.device)
+    base, gbase, es = qkv.data_ptr(), dqkv.data_ptr(), qkv.element_size()
+    check(lib.tmpi_attention_bwd(base, base + C * es, base + 2 * C * es, C3, out.data_ptr(), C, dout.data_ptr(), C,
+                                 lse.data_ptr(), delta.data_ptr(), dq_acc.data_ptr(), gbase + C * es, gbase + 2 * C * es, C3,
+                                 B, T, n_head, 1.0 / math.sqrt(HEAD), stream_ptr()))
+    launch_count += 1
+    dqkv[:, :, :C].copy_(dq_acc.view(B, T, C))
+    return dqkv
 
 
 def _reference(qkv: torch.Tensor, n_head: int) -> torch.Tensor:
@@ -85,6 +104,9 @@ class _AttnFn(torch.autograd.Function):
         go, o = heads(dout.contiguous()), heads(out)
         grads = None
         for name in _BACKWARDS:
+            if name == "own":              # this package's kernel: an error of it is raised, not routed around
+                last_backward = name
+                return attention_backward(qkv, out, lse, dout, H), None
             try:
                 if name == "cudnn":
                     grads = torch.ops.aten._scaled_dot_product_cudnn_attention_backward(
