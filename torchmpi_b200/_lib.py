@@ -207,8 +207,9 @@ _CUDA_PROTOS = {
     "tmpi_conv_wgrad": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _sz, _i, _vp]),
     "tmpi_conv_status": (_i, []),
     "tmpi_attention_fwd": (_i, [_vp, _vp, _vp, _i64, _vp, _i64, _vp, _i, _i, _i, _f, _vp]),
-    "tmpi_attention_bwd": (_i, [_vp, _vp, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _f, _vp]),
+    "tmpi_attention_bwd": (_i, [_vp, _vp, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _f, _vp]),
     "tmpi_attention_bwd_status": (_i, []),
+    "tmpi_attention_bwd_set_trace": (None, [_vp]),
     "tmpi_attention_ctas_per_sm": (_i, []),
     "tmpi_attention_set_trace": (None, [_vp]),
     "tmpi_attention_set_v_stages": (None, [_i]),

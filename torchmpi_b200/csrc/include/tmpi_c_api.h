@@ -288,12 +288,13 @@ int tmpi_conv_status(void);
 // blocks of a fused QKV projection), out [B * T, ld_out], lse [B, H, T] fp32 (optional); T a multiple of 128
 int tmpi_attention_fwd(const void* q, const void* k, const void* v, int64_t ld_qkv, void* out, int64_t ld_out, float* lse,
                        int B, int T, int H, float scale, void* stream);
-// gradients: o and dout [B * T, H * 64] with their own pitches, lse from the forward, delta [B, H, T] scratch, dq_acc a zeroed
-// fp32 [B * T, H * 64] buffer that receives dQ, dk / dv bf16 [B * T, ld_dkv]
+// gradients: o and dout [B * T, H * 64] with their own pitches, lse from the forward, delta [B, H, T] scratch, dq_acc a
+// fp32 [B * T, H * 64] buffer (cleared by the call) that receives dQ, dq (optional: dq_acc rounded) / dk / dv bf16 [B * T, ld_dkv]
 int tmpi_attention_bwd(const void* q, const void* k, const void* v, int64_t ld_qkv, const void* o, int64_t ld_o,
-                       const void* dout, int64_t ld_do, const float* lse, float* delta, float* dq_acc, void* dk, void* dv,
-                       int64_t ld_dkv, int B, int T, int H, float scale, void* stream);
+                       const void* dout, int64_t ld_do, const float* lse, float* delta, float* dq_acc, void* dq, void* dk,
+                       void* dv, int64_t ld_dkv, int B, int T, int H, float scale, void* stream);
 int tmpi_attention_bwd_status(void);
+void tmpi_attention_bwd_set_trace(void* device_buffer);   // tuning aid, as for the forward
 int tmpi_attention_ctas_per_sm(void);
 void tmpi_attention_set_v_stages(int n);              // tuning aid: 1 or 2 V buffers per CTA
 void tmpi_attention_set_trace(void* device_buffer);   // tuning aid: phase time stamps of one CTA

@@ -8,11 +8,12 @@
 //   dV += P^T dO_i            dK += dS^T Q_i                        (128 keys x 64, accumulated over i, read once)
 //   dQ_ij = dS K_j                                                  (128 queries x 64, added to a fp32 dQ buffer)
 //
-// with P = exp(scale S - lse) and dS = scale P (dP - delta) computed by eight warps (two threads per query row, 64
+// with P = exp(scale S - lse) and dS = scale P (dP - delta) computed by sixteen warps (four threads per query row, 32
 // keys each) and written as bf16 into two shared-memory tiles laid out [query][key] with the 128-byte swizzle: the
 // tensor core reads them K-major for dS K_j and MN-major (transposed) for P^T dO_i and dS^T Q_i, so nothing is
 // transposed by hand.  Q_i and dO_i arrive by TMA through a two-stage ring, K_j and V_j once.  S and dP of the next
-// pair are issued as soon as the softmax warps have read the current ones.
+// pair are issued as soon as the softmax warps have read the current ones, and P and dS are double-buffered, so the
+// softmax of pair n + 1 runs while the tensor core works on the three products of pair n.
 //
 // dQ receives contributions from every key block: each CTA adds its 128 x 64 tile to a fp32 buffer with vector
 // reductions (red.global.add.v4.f32), so the low bits of dQ depend on the order in which CTAs arrive; dK and dV are
@@ -36,16 +37,16 @@ int make_tmap_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t c
 namespace attnb {
 using namespace attn_util;
 
-constexpr int BLK = 128, D = 64, THREADS = 320, UMMA_K = 16;
+constexpr int BLK = 128, D = 64, SOFTMAX_WARPS = 16, THREADS = 64 + SOFTMAX_WARPS * 32, UMMA_K = 16;
 constexpr int TILE = BLK * D * 2;                             // a 128 x 64 bf16 tile: 16 KB
-constexpr int K_OFF = 0, V_OFF = TILE, Q_OFF = 2 * TILE, DO_OFF = 4 * TILE, P_OFF = 6 * TILE, DS_OFF = 8 * TILE;
-constexpr int SMEM_TILES = 10 * TILE;                         // K, V, Q x 2, dO x 2, P (32 KB), dS (32 KB)
+constexpr int K_OFF = 0, V_OFF = TILE, Q_OFF = 2 * TILE, DO_OFF = 4 * TILE, P_OFF = 6 * TILE, DS_OFF = 10 * TILE;
+constexpr int SMEM_TILES = 14 * TILE;                         // K, V, Q x 2, dO x 2, P x 2 (32 KB each), dS x 2: 224 KB
 constexpr int SMEM_SHARED = 256;
 constexpr int TMEM_COLS = 512;                                // S 0, dP 128, dV 256, dK 320, dQ 384
 constexpr unsigned long long kWaitBudgetNs = 2000000000ull;
 
 struct alignas(128) Shared {
-  uint64_t kv_full, qd_full[2], qd_empty[2], sdp_full, sdp_empty, pds_full, dq_full, dq_empty, all_done;
+  uint64_t kv_full, qd_full[2], qd_empty[2], sdp_full, sdp_empty, pds_full[2], dq_full, dq_empty, all_done;
   uint32_t tmem_base;
   int error;
 };
@@ -56,16 +57,22 @@ struct Params {
   float scale, scale_log2;
   const float* lse;            // [B, H, T], natural log
   const float* delta;          // [B, H, T]
-  float* dq_acc;               // [B * T, H * 64] fp32, zeroed by the caller
+  float* dq_acc;               // [B * T, H * 64] fp32, cleared by the delta kernel
   __nv_bfloat16* dk;           // [B * T, ld_dkv], head h at columns h * 64
   __nv_bfloat16* dv;
   int ld_dkv;
   int* status;
+  unsigned long long* trace;   // optional: time stamps of the phases of CTA 0 (see tmpi_attention_bwd_set_trace)
 };
 
 __device__ __forceinline__ void fail(Shared* sh, const Params& p, int where) {
   atomicExch(&sh->error, where);
   if (p.status) atomicCAS(p.status, 0, 3100 + where);
+}
+
+// Phase time stamps of one CTA for tuning: slot = (pair * 16 + event), written by one thread per role.
+__device__ __forceinline__ void stamp(const Params& p, int n, int ev) {
+  if (p.trace && blockIdx.x == 0) p.trace[n * 16 + ev] = sm100::now_ns();
 }
 
 #define ATTNB_WAIT(bar, parity, where) \
@@ -90,150 +97,193 @@ __device__ void producer(Shared* sh, unsigned char* tiles, const Params& p, cons
 __device__ void mma_issuer(Shared* sh, unsigned char* tiles, const Params& p, int jblk) {
   const uint32_t t_s = sh->tmem_base, t_dp = t_s + 128, t_dv = t_s + 256, t_dk = t_s + 320, t_dq = t_s + 384;
   const uint32_t k_addr = sm100::smem_u32(tiles + K_OFF), v_addr = sm100::smem_u32(tiles + V_OFF);
-  const uint32_t p_addr = sm100::smem_u32(tiles + P_OFF), ds_addr = sm100::smem_u32(tiles + DS_OFF);
   constexpr uint32_t idesc_s = sm100::make_idesc_f16(BLK, BLK, true);                 // both operands K-major
   constexpr uint32_t idesc_t = sm100::make_idesc_f16(BLK, D, true, true, true);       // A and B MN-major (transposed reads)
   constexpr uint32_t idesc_q = sm100::make_idesc_f16(BLK, D, true, true, false);      // A K-major, B MN-major
   const int pairs = p.blocks - jblk;
+  // Descriptors: one per operand tile, built once; a slice further into the tile only adds to the address field
+  // (bytes / 16 in the low 14 bits; shared memory is far smaller than the field, so nothing carries out of it).
+  auto at = [](uint64_t desc, uint32_t bytes) { return desc + (uint64_t)(bytes >> 4); };
+  const uint64_t k_kmaj = sm100::make_desc_sw128(k_addr), v_kmaj = sm100::make_desc_sw128(v_addr);
+  const uint64_t k_mn = sm100::make_desc_sw128_mn(k_addr, TILE, 1024);
+  uint64_t q_kmaj[2], do_kmaj[2], q_mn[2], do_mn[2], p_mn[2], ds_mn[2], ds_kmaj[2];
+#pragma unroll
+  for (int s = 0; s < 2; ++s) {
+    const uint32_t q_addr = sm100::smem_u32(tiles + Q_OFF + s * TILE), do_addr = sm100::smem_u32(tiles + DO_OFF + s * TILE);
+    const uint32_t p_addr = sm100::smem_u32(tiles + P_OFF + s * 2 * TILE), ds_addr = sm100::smem_u32(tiles + DS_OFF + s * 2 * TILE);
+    q_kmaj[s] = sm100::make_desc_sw128(q_addr);
+    do_kmaj[s] = sm100::make_desc_sw128(do_addr);
+    q_mn[s] = sm100::make_desc_sw128_mn(q_addr, TILE, 1024);
+    do_mn[s] = sm100::make_desc_sw128_mn(do_addr, TILE, 1024);
+    p_mn[s] = sm100::make_desc_sw128_mn(p_addr, TILE, 1024);
+    ds_mn[s] = sm100::make_desc_sw128_mn(ds_addr, TILE, 1024);
+    ds_kmaj[s] = sm100::make_desc_sw128(ds_addr);
+  }
   auto issue_sdp = [&](int n) {
-    const uint32_t q_addr = sm100::smem_u32(tiles + Q_OFF + (n & 1) * TILE), do_addr = sm100::smem_u32(tiles + DO_OFF + (n & 1) * TILE);
+    const uint64_t dq = (n & 1) ? q_kmaj[1] : q_kmaj[0], dd = (n & 1) ? do_kmaj[1] : do_kmaj[0];
 #pragma unroll
     for (int k = 0; k < D / UMMA_K; ++k)
-      sm100::umma_f16(t_s, sm100::make_desc_sw128(q_addr + k * UMMA_K * 2), sm100::make_desc_sw128(k_addr + k * UMMA_K * 2),
-                      idesc_s, k > 0 ? 1u : 0u);
+      sm100::umma_f16(t_s, at(dq, k * UMMA_K * 2), at(k_kmaj, k * UMMA_K * 2), idesc_s, k > 0 ? 1u : 0u);
 #pragma unroll
     for (int k = 0; k < D / UMMA_K; ++k)
-      sm100::umma_f16(t_dp, sm100::make_desc_sw128(do_addr + k * UMMA_K * 2), sm100::make_desc_sw128(v_addr + k * UMMA_K * 2),
-                      idesc_s, k > 0 ? 1u : 0u);
+      sm100::umma_f16(t_dp, at(dd, k * UMMA_K * 2), at(v_kmaj, k * UMMA_K * 2), idesc_s, k > 0 ? 1u : 0u);
     sm100::umma_commit(&sh->sdp_full);
+  };
+  auto issue_products = [&](int n) {
+    const int s = n & 1;
+    const uint64_t a_p = s ? p_mn[1] : p_mn[0], a_ds = s ? ds_mn[1] : ds_mn[0], a_dsk = s ? ds_kmaj[1] : ds_kmaj[0];
+    const uint64_t b_do = s ? do_mn[1] : do_mn[0], b_q = s ? q_mn[1] : q_mn[0];
+    const uint32_t acc = n > 0 ? 1u : 0u;
+    // K dimension = the 128 queries of the block: 16 rows of 128 bytes per step in every [query][...] tile
+#pragma unroll
+    for (int k = 0; k < BLK / UMMA_K; ++k)      // dV += P^T dO
+      sm100::umma_f16(t_dv, at(a_p, k * UMMA_K * 128), at(b_do, k * UMMA_K * 128), idesc_t, k > 0 ? 1u : acc);
+#pragma unroll
+    for (int k = 0; k < BLK / UMMA_K; ++k)      // dK += dS^T Q
+      sm100::umma_f16(t_dk, at(a_ds, k * UMMA_K * 128), at(b_q, k * UMMA_K * 128), idesc_t, k > 0 ? 1u : acc);
+    // K dimension = the 128 keys: dS read K-major (two chunks of 64 keys), K_j read MN-major
+#pragma unroll
+    for (int k = 0; k < BLK / UMMA_K; ++k)      // dQ_ij = dS K_j
+      sm100::umma_f16(t_dq, at(a_dsk, (k >> 2) * TILE + (k & 3) * UMMA_K * 2), at(k_mn, k * UMMA_K * 128), idesc_q, k > 0 ? 1u : 0u);
+    sm100::umma_commit(&sh->dq_full);                // also: these P / dS buffers and this stage of Q / dO are free again
+    sm100::umma_commit(&sh->qd_empty[s]);
   };
   ATTNB_WAIT(&sh->kv_full, 0, 2);
   ATTNB_WAIT(&sh->qd_full[0], 0, 3);
   sm100::tc_fence_after();
   issue_sdp(0);
+  int next_sdp = 1;                                  // the next pair whose S and dP are to be issued
   for (int n = 0; n < pairs; ++n) {
-    if (n + 1 < pairs) {                 // S and dP of the next pair, as soon as this pair's have been read
-      ATTNB_WAIT(&sh->sdp_empty, n & 1, 4);
-      ATTNB_WAIT(&sh->qd_full[(n + 1) & 1], ((n + 1) >> 1) & 1, 5);
-      sm100::tc_fence_after();
-      issue_sdp(n + 1);
+    // Two things may become possible, in either order: S and dP of pair n + 1 (its Q and dO have landed and the
+    // softmax warps have read pair n's), and the three products of pair n (its P and dS are written and the previous
+    // dQ tile has been collected).  Whichever is ready goes first, so a late TMA load does not hold up the products.
+    const unsigned long long t0 = sm100::now_ns();
+    bool products_done = false;
+    unsigned spins = 0;
+    while (!products_done || (next_sdp == n + 1 && n + 1 < pairs)) {
+      if (next_sdp == n + 1 && n + 1 < pairs && sm100::mbar_try_wait(&sh->sdp_empty, n & 1) &&
+          sm100::mbar_try_wait(&sh->qd_full[(n + 1) & 1], ((n + 1) >> 1) & 1)) {
+        if (!products_done) stamp(p, n, 8);
+        sm100::tc_fence_after();
+        issue_sdp(n + 1);
+        ++next_sdp;
+        stamp(p, n, 9);
+      } else if (!products_done && sm100::mbar_try_wait(&sh->pds_full[n & 1], (n >> 1) & 1) &&
+                 (n == 0 || sm100::mbar_try_wait(&sh->dq_empty, (n - 1) & 1))) {
+        stamp(p, n, 10);
+        sm100::tc_fence_after();
+        issue_products(n);
+        products_done = true;
+        stamp(p, n, 12);
+      } else if ((++spins & 255u) == 0 && (sm100::now_ns() - t0 > kWaitBudgetNs || sh->error)) {
+        fail(sh, p, 6);
+        return;
+      }
     }
-    ATTNB_WAIT(&sh->pds_full, n & 1, 6);
-    if (n > 0) ATTNB_WAIT(&sh->dq_empty, (n - 1) & 1, 7);        // the previous dQ tile has been read
-    sm100::tc_fence_after();
-    const uint32_t q_addr = sm100::smem_u32(tiles + Q_OFF + (n & 1) * TILE), do_addr = sm100::smem_u32(tiles + DO_OFF + (n & 1) * TILE);
-    // K dimension = the 128 queries of the block: 16 rows of 128 bytes per step in every [query][...] tile
-#pragma unroll
-    for (int k = 0; k < BLK / UMMA_K; ++k) {
-      const uint64_t a_p = sm100::make_desc_sw128_mn(p_addr + k * UMMA_K * 128, TILE, 1024);     // P^T: keys x queries
-      const uint64_t b_do = sm100::make_desc_sw128_mn(do_addr + k * UMMA_K * 128, TILE, 1024);   // dO: queries x d
-      sm100::umma_f16(t_dv, a_p, b_do, idesc_t, (n > 0 || k > 0) ? 1u : 0u);
-    }
-#pragma unroll
-    for (int k = 0; k < BLK / UMMA_K; ++k) {
-      const uint64_t a_ds = sm100::make_desc_sw128_mn(ds_addr + k * UMMA_K * 128, TILE, 1024);   // dS^T
-      const uint64_t b_q = sm100::make_desc_sw128_mn(q_addr + k * UMMA_K * 128, TILE, 1024);     // Q: queries x d
-      sm100::umma_f16(t_dk, a_ds, b_q, idesc_t, (n > 0 || k > 0) ? 1u : 0u);
-    }
-    // K dimension = the 128 keys: dS read K-major (two chunks of 64 keys), K_j read MN-major
-#pragma unroll
-    for (int k = 0; k < BLK / UMMA_K; ++k) {
-      const uint64_t a_ds = sm100::make_desc_sw128(ds_addr + (k >> 2) * TILE + (k & 3) * UMMA_K * 2);
-      const uint64_t b_k = sm100::make_desc_sw128_mn(k_addr + k * UMMA_K * 128, TILE, 1024);
-      sm100::umma_f16(t_dq, a_ds, b_k, idesc_q, k > 0 ? 1u : 0u);
-    }
-    sm100::umma_commit(&sh->dq_full);                // also: P, dS and this stage of Q / dO are free again
-    sm100::umma_commit(&sh->qd_empty[n & 1]);
   }
   sm100::umma_commit(&sh->all_done);
 }
 
-// Two threads per query row (warps with the same warp & 3 share 32 tensor-memory lanes); `half` picks 64 of the 128
-// keys of the pair and 32 of the 64 columns of dQ (and, at the end, of dK / dV, where the rows are keys).
-__device__ void softmax_rows(Shared* sh, unsigned char* tiles, const Params& p, int b, int h, int jblk, int quarter, int half,
+// Four threads per query row (warps with the same warp & 3 share 32 tensor-memory lanes); `part` picks 32 of the 128
+// keys of the pair and 16 of the 64 columns of dQ (and, at the end, of dK / dV, where the rows are keys).
+__device__ void softmax_rows(Shared* sh, unsigned char* tiles, const Params& p, int b, int h, int jblk, int quarter, int part,
                              int lane) {
   const int row = quarter * 32 + lane;
   const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-  const uint32_t t_s = sh->tmem_base + lane_base + half * 64, t_dp = t_s + 128;
-  const uint32_t t_dv = sh->tmem_base + lane_base + 256 + half * 32, t_dk = t_dv + 64, t_dq = t_dv + 128;
-  unsigned char* p_row = tiles + P_OFF + half * TILE + row * 128;
-  unsigned char* ds_row = tiles + DS_OFF + half * TILE + row * 128;
+  const uint32_t t_s = sh->tmem_base + lane_base + part * 32, t_dp = t_s + 128;
+  const uint32_t t_dv = sh->tmem_base + lane_base + 256 + part * 16, t_dk = t_dv + 64, t_dq = t_dv + 128;
   const float c2 = p.scale_log2, scale = p.scale;
-  const int last_row = quarter * 32 + 31;
+  const int key0 = part * 32;
+  const int tile_off = (part >> 1) * TILE + row * 128;    // which 64-key chunk of the [query][key] tiles
+  const int unit0 = (part & 1) * 4;                       // first 16-byte unit of this thread's keys in the row
+  const bool masked_diag = key0 > quarter * 32 + 31;      // on the diagonal block: every key of the chunk is after the query
   uint32_t rs[32], rp[32];
-  int n = 0;
-  for (int i = jblk; i < p.blocks; ++i, ++n) {
-    const bool diag = i == jblk;
+  const int pairs = p.blocks - jblk;
+  const bool tracer = row == 0 && part == 0;
+  // P and dS of pair n (query block jblk + n) into the buffers n & 1
+  auto softmax_pair = [&](int n) -> bool {
+    const int i = jblk + n;
+    const bool diag = n == 0;
+    unsigned char* p_row = tiles + P_OFF + (n & 1) * 2 * TILE + tile_off;
+    unsigned char* ds_row = tiles + DS_OFF + (n & 1) * 2 * TILE + tile_off;
     const size_t stat = ((size_t)b * p.H + h) * p.T + (size_t)i * BLK + row;
     const float nl2 = -p.lse[stat] * 1.4426950408889634f, delta = p.delta[stat];
-    ATTNB_WAIT(&sh->sdp_full, n & 1, 8);
+    if (tracer) stamp(p, n, 0);
+    if (!sm100::mbar_wait(&sh->sdp_full, n & 1, kWaitBudgetNs) || sh->error) { fail(sh, p, 8); return false; }
+    if (tracer) stamp(p, n, 1);
     sm100::tc_fence_after();
-#pragma unroll 1
-    for (int c = 0; c < 2; ++c) {
-      const int key0 = half * 64 + c * 32;
-      const bool masked = diag && key0 > last_row;         // warp-uniform: every key of the chunk is after the query
+    const bool masked = diag && masked_diag;               // warp-uniform: nothing to load or exponentiate
+    if (!masked) {
+      sm100::tmem_ld_32x32(t_s, rs);
+      sm100::tmem_ld_32x32(t_dp, rp);
+      sm100::tmem_ld_wait();
+    }
+    sm100::tc_fence_before();                              // S and dP are in registers: the next pair may overwrite them
+    sm100::mbar_arrive(&sh->sdp_empty);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      uint32_t wp[4] = {0u, 0u, 0u, 0u}, wd[4] = {0u, 0u, 0u, 0u};
       if (!masked) {
-        sm100::tmem_ld_32x32(t_s + c * 32, rs);
-        sm100::tmem_ld_32x32(t_dp + c * 32, rp);
-        sm100::tmem_ld_wait();
-      }
-      if (c == 1) {                                       // S and dP are in registers: the next pair may overwrite them
-        sm100::tc_fence_before();
-        sm100::mbar_arrive(&sh->sdp_empty);
-      }
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        uint32_t wp[4] = {0u, 0u, 0u, 0u}, wd[4] = {0u, 0u, 0u, 0u};
-        if (!masked) {
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const int e = u * 8 + 2 * q;
-            float p0 = ex2(fmaf(__uint_as_float(rs[e]), c2, nl2)), p1 = ex2(fmaf(__uint_as_float(rs[e + 1]), c2, nl2));
-            if (diag) {
-              if (key0 + e > row) p0 = 0.f;
-              if (key0 + e + 1 > row) p1 = 0.f;
-            }
-            const float d0 = p0 * (__uint_as_float(rp[e]) - delta) * scale, d1 = p1 * (__uint_as_float(rp[e + 1]) - delta) * scale;
-            __nv_bfloat162 hp = __floats2bfloat162_rn(p0, p1), hd = __floats2bfloat162_rn(d0, d1);
-            wp[q] = *reinterpret_cast<uint32_t*>(&hp);
-            wd[q] = *reinterpret_cast<uint32_t*>(&hd);
+        for (int q = 0; q < 4; ++q) {
+          const int e = u * 8 + 2 * q;
+          float p0 = ex2(fmaf(__uint_as_float(rs[e]), c2, nl2)), p1 = ex2(fmaf(__uint_as_float(rs[e + 1]), c2, nl2));
+          if (diag) {
+            if (key0 + e > row) p0 = 0.f;
+            if (key0 + e + 1 > row) p1 = 0.f;
           }
+          const float d0 = p0 * (__uint_as_float(rp[e]) - delta) * scale, d1 = p1 * (__uint_as_float(rp[e + 1]) - delta) * scale;
+          __nv_bfloat162 hp = __floats2bfloat162_rn(p0, p1), hd = __floats2bfloat162_rn(d0, d1);
+          wp[q] = *reinterpret_cast<uint32_t*>(&hp);
+          wd[q] = *reinterpret_cast<uint32_t*>(&hd);
         }
-        const int off = ((c * 4 + u) ^ (row & 7)) << 4;
-        *reinterpret_cast<uint4*>(p_row + off) = make_uint4(wp[0], wp[1], wp[2], wp[3]);
-        *reinterpret_cast<uint4*>(ds_row + off) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
       }
+      const int off = ((unit0 + u) ^ (row & 7)) << 4;
+      *reinterpret_cast<uint4*>(p_row + off) = make_uint4(wp[0], wp[1], wp[2], wp[3]);
+      *reinterpret_cast<uint4*>(ds_row + off) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
     }
     sm100::fence_proxy_async_smem();                      // the MMAs read P and dS through the async proxy
-    sm100::mbar_arrive(&sh->pds_full);
-    // this pair's share of dQ: 32 columns of this thread's query row, added to the fp32 buffer
+    sm100::mbar_arrive(&sh->pds_full[n & 1]);
+    if (tracer) stamp(p, n, 2);
+    return true;
+  };
+  if (!softmax_pair(0)) return;
+  uint32_t rq[16];
+  for (int n = 0; n < pairs; ++n) {
+    // the next pair's P and dS while the tensor core multiplies this pair's (its buffers were freed by the MMAs of
+    // pair n - 1, whose dQ this thread has already collected)
+    if (n + 1 < pairs && !softmax_pair(n + 1)) return;
+    // this pair's share of dQ: 16 columns of this thread's query row, added to the fp32 buffer
+    if (tracer) stamp(p, n, 3);
     ATTNB_WAIT(&sh->dq_full, n & 1, 9);
+    if (tracer) stamp(p, n, 4);
     sm100::tc_fence_after();
-    sm100::tmem_ld_32x32(t_dq, rs);
+    sm100::tmem_ld_32x16(t_dq, rq);
     sm100::tmem_ld_wait();
     sm100::tc_fence_before();
     sm100::mbar_arrive(&sh->dq_empty);
-    float* dq = p.dq_acc + ((size_t)b * p.T + (size_t)i * BLK + row) * (p.H * D) + h * D + half * 32;
+    float* dq = p.dq_acc + ((size_t)b * p.T + (size_t)(jblk + n) * BLK + row) * (p.H * D) + h * D + part * 16;
 #pragma unroll
-    for (int u = 0; u < 8; ++u)
-      asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq + 4 * u), "f"(__uint_as_float(rs[4 * u])),
-                   "f"(__uint_as_float(rs[4 * u + 1])), "f"(__uint_as_float(rs[4 * u + 2])), "f"(__uint_as_float(rs[4 * u + 3]))
+    for (int u = 0; u < 4; ++u)
+      asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq + 4 * u), "f"(__uint_as_float(rq[4 * u])),
+                   "f"(__uint_as_float(rq[4 * u + 1])), "f"(__uint_as_float(rq[4 * u + 2])), "f"(__uint_as_float(rq[4 * u + 3]))
                    : "memory");
+    if (tracer) stamp(p, n, 5);
   }
   // dV and dK of this key block: the accumulator rows are keys now
   ATTNB_WAIT(&sh->all_done, 0, 10);
   sm100::tc_fence_after();
   const size_t grow = (size_t)b * p.T + (size_t)jblk * BLK + row;
   auto store = [&](uint32_t taddr, __nv_bfloat16* base) {
-    sm100::tmem_ld_32x32(taddr, rs);
+    sm100::tmem_ld_32x16(taddr, rq);
     sm100::tmem_ld_wait();
-    __nv_bfloat16* o = base + grow * p.ld_dkv + h * D + half * 32;
+    __nv_bfloat16* o = base + grow * p.ld_dkv + h * D + part * 16;
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < 2; ++u) {
       uint32_t w[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(rs[u * 8 + 2 * e]), __uint_as_float(rs[u * 8 + 2 * e + 1]));
+        __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(rq[u * 8 + 2 * e]), __uint_as_float(rq[u * 8 + 2 * e + 1]));
         w[e] = *reinterpret_cast<uint32_t*>(&hh);
       }
       *reinterpret_cast<uint4*>(o + u * 8) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -262,10 +312,10 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     sm100::mbar_init(&sh->kv_full, 1);
     for (int s = 0; s < 2; ++s) { sm100::mbar_init(&sh->qd_full[s], 1); sm100::mbar_init(&sh->qd_empty[s], 1); }
     sm100::mbar_init(&sh->sdp_full, 1);
-    sm100::mbar_init(&sh->sdp_empty, 256);
-    sm100::mbar_init(&sh->pds_full, 256);
+    sm100::mbar_init(&sh->sdp_empty, SOFTMAX_WARPS * 32);
+    for (int s = 0; s < 2; ++s) sm100::mbar_init(&sh->pds_full[s], SOFTMAX_WARPS * 32);
     sm100::mbar_init(&sh->dq_full, 1);
-    sm100::mbar_init(&sh->dq_empty, 256);
+    sm100::mbar_init(&sh->dq_empty, SOFTMAX_WARPS * 32);
     sm100::mbar_init(&sh->all_done, 1);
     sh->error = 0;
     sm100::fence_barrier_init();
@@ -302,10 +352,11 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   }
 }
 
-// delta[b, h, t] = sum_d dO[b, t, h, d] * O[b, t, h, d]: one thread per (row, head), 128-byte reads.
+// delta[b, h, t] = sum_d dO[b, t, h, d] * O[b, t, h, d]: one thread per (row, head), 128-byte reads; the same thread
+// clears its 64 entries of the fp32 dQ buffer, so the caller need not.
 __global__ void __launch_bounds__(256)
 attention_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout, int64_t ld_o, int64_t ld_do,
-                       float* __restrict__ delta, int B, int T, int H) {
+                       float* __restrict__ delta, float* __restrict__ dq_acc, int B, int T, int H) {
   const long long total = (long long)B * T * H;
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
     const int h = (int)(idx % H);
@@ -325,10 +376,33 @@ attention_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16*
     }
     const int b = (int)(r / T), t = (int)(r - (long long)b * T);
     delta[((size_t)b * H + h) * T + t] = acc;
+    float4* z = reinterpret_cast<float4*>(dq_acc + (size_t)r * (H * D) + h * D);
+#pragma unroll
+    for (int u = 0; u < D / 4; ++u) z[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+}
+
+// dq[r, c] = bf16(dq_acc[r, c]): the fp32 sums of the reductions rounded into the Q block of the packed gradient.
+__global__ void __launch_bounds__(256)
+attention_dq_round_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, int64_t ld_dq, long long rows, int cols) {
+  const int groups = cols / 8;
+  const long long total = rows * groups;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+    const long long r = idx / groups;
+    const int c = (int)(idx - r * groups) * 8;
+    const float4 a = *reinterpret_cast<const float4*>(acc + r * cols + c), b = *reinterpret_cast<const float4*>(acc + r * cols + c + 4);
+    __nv_bfloat162 h0 = __floats2bfloat162_rn(a.x, a.y), h1 = __floats2bfloat162_rn(a.z, a.w);
+    __nv_bfloat162 h2 = __floats2bfloat162_rn(b.x, b.y), h3 = __floats2bfloat162_rn(b.z, b.w);
+    uint4 u;
+    u.x = *reinterpret_cast<uint32_t*>(&h0); u.y = *reinterpret_cast<uint32_t*>(&h1);
+    u.z = *reinterpret_cast<uint32_t*>(&h2); u.w = *reinterpret_cast<uint32_t*>(&h3);
+    *reinterpret_cast<uint4*>(dq + r * ld_dq + c) = u;
   }
 }
 
 }  // namespace attnb
+
+static unsigned long long* g_attnb_trace = nullptr;
 
 static int* attnb_status_word(int** host_out = nullptr) {
   static int* dev_ptr = nullptr;
@@ -347,12 +421,13 @@ static int* attnb_status_word(int** host_out = nullptr) {
 extern "C" {
 
 // Gradients of tmpi_attention_fwd.  q, k, v as there (common row pitch ld_qkv); o and dout are [B * T, H * 64] with
-// their own pitches; lse [B, H, T] from the forward; delta [B, H, T] is scratch (written here); dq_acc is a zeroed
-// fp32 [B * T, H * 64] buffer that receives dQ; dk and dv are bf16 [B * T, ld_dkv] (for instance the K and V column
-// blocks of the gradient of a packed QKV projection).
+// their own pitches; lse [B, H, T] from the forward; delta [B, H, T] is scratch (written here); dq_acc is a fp32
+// [B * T, H * 64] buffer (cleared here) that receives dQ; dq (optional), dk and dv are bf16 [B * T, ld_dkv] (for instance
+// the column blocks of the gradient of a packed QKV projection): dk and dv are written by the main kernel, dq by a last
+// pass that rounds dq_acc.
 int tmpi_attention_bwd(const void* q, const void* k, const void* v, int64_t ld_qkv, const void* o, int64_t ld_o,
-                       const void* dout, int64_t ld_do, const float* lse, float* delta, float* dq_acc, void* dk, void* dv,
-                       int64_t ld_dkv, int B, int T, int H, float scale, void* stream) {
+                       const void* dout, int64_t ld_do, const float* lse, float* delta, float* dq_acc, void* dq, void* dk,
+                       void* dv, int64_t ld_dkv, int B, int T, int H, float scale, void* stream) {
   if (B < 1 || H < 1 || T < 128 || T % 128) return fail(TMPI_ERR_UNSUPPORTED, "attention backward: T=%d must be a positive multiple of 128", T);
   if (ld_dkv % 8 || ((uintptr_t)dk & 15) || ((uintptr_t)dv & 15) || ((uintptr_t)dq_acc & 15) || ld_o % 8 || ld_do % 8 ||
       ((uintptr_t)o & 15) || ((uintptr_t)dout & 15))
@@ -361,7 +436,7 @@ int tmpi_attention_bwd(const void* q, const void* k, const void* v, int64_t ld_q
   cudaStream_t s = (cudaStream_t)stream;
   const long long rows_heads = (long long)B * T * H;
   const int dgrid = (int)std::min<long long>((rows_heads + 255) / 256, 148 * 8);
-  attnb::attention_delta_kernel<<<dgrid, 256, 0, s>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, ld_o, ld_do, delta, B, T, H);
+  attnb::attention_delta_kernel<<<dgrid, 256, 0, s>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, ld_o, ld_do, delta, dq_acc, B, T, H);
   CUtensorMap mq, mk, mv, mdo;
   int st;
   const uint64_t rows = (uint64_t)B * T, cols = (uint64_t)H * attnb::D;
@@ -378,10 +453,23 @@ int tmpi_attention_bwd(const void* q, const void* k, const void* v, int64_t ld_q
   p.lse = lse; p.delta = delta; p.dq_acc = dq_acc;
   p.dk = (__nv_bfloat16*)dk; p.dv = (__nv_bfloat16*)dv; p.ld_dkv = (int)ld_dkv;
   p.status = attnb_status_word();
+  p.trace = g_attnb_trace;
   attnb::attention_bwd_kernel<<<B * H * p.blocks, attnb::THREADS, smem, s>>>(mq, mk, mv, mdo, p);
+  if (dq) {
+    if ((uintptr_t)dq & 15) return fail(TMPI_ERR_INVALID, "attention backward: dq must be 16-byte aligned");
+    const long long groups = (long long)rows * (cols / 8);
+    const int cgrid = (int)std::min<long long>((groups + 255) / 256, 148 * 8);
+    attnb::attention_dq_round_kernel<<<cgrid, 256, 0, s>>>(dq_acc, (__nv_bfloat16*)dq, ld_dkv, (long long)rows, (int)cols);
+  }
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? TMPI_OK : fail(TMPI_ERR_CUDA, "attention backward launch: %s", cudaGetErrorString(e));
 }
+
+// Tuning aid: with a device buffer of (T / 128) * 16 64-bit words, CTA 0 of every later launch (the first key block of
+// the first batch and head, which meets every query block) records the time of each phase of each pair (ns):
+// 0 waits for S and dP, 1 has them, 2 P and dS announced, 3 waits for dQ, 4 has it, 5 reductions issued; MMA thread:
+// 8 S and dP were read, 9 next S and dP issued, 10 has P and dS, 11 dQ tile free, 12 three products issued.
+void tmpi_attention_bwd_set_trace(void* device_buffer) { g_attnb_trace = (unsigned long long*)device_buffer; }
 
 // Non-zero after a CTA of the attention backward gave up on a bounded wait (3100 + the point where); clears it.
 int tmpi_attention_bwd_status(void) {

@@ -16,6 +16,7 @@ not take (head size other than 64, T not a multiple of 128, other dtypes, CPU) u
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 import torch.nn.functional as F
@@ -25,7 +26,12 @@ from .._lib import lib, check, has_symbol, stream_ptr, TorchMPIError
 launch_count = 0
 last_backward = ""
 HEAD = 64
-_BACKWARDS = ("own", "cudnn", "flash")   # backward kernels in order of preference: this package's, then the libraries'
+# backward kernels in order of preference: this package's, then the libraries'; TORCHMPI_ATTENTION_BACKWARD=cudnn
+# (or flash) puts a library first
+_BACKWARDS = ("own", "cudnn", "flash")
+_first = os.environ.get("TORCHMPI_ATTENTION_BACKWARD", "")
+if _first in _BACKWARDS:
+    _BACKWARDS = (_first,) + tuple(b for b in _BACKWARDS if b != _first)
 
 
 def supported(qkv: torch.Tensor, n_head: int) -> bool:
@@ -58,20 +64,19 @@ def attention_forward(qkv: torch.Tensor, n_head: int, need_lse: bool = True):
 
 def attention_backward(qkv: torch.Tensor, out: torch.Tensor, lse: torch.Tensor, dout: torch.Tensor, n_head: int) -> torch.Tensor:
     """Gradient of the packed projection ``[B, T, 3 C]`` on this package's backward kernel: dK and dV are written
-    into their column blocks by the kernel, dQ is accumulated in fp32 and rounded into its block afterwards."""
+    into their column blocks by the main kernel, dQ is accumulated in fp32 and rounded into its block by a last pass."""
     global launch_count
     B, T, C3 = qkv.shape
     C = C3 // 3
     dout = dout.contiguous()
     dqkv = torch.empty_like(qkv)
-    dq_acc = torch.zeros((B * T, C), dtype=torch.float32, device=qkv.device)
+    dq_acc = torch.empty((B * T, C), dtype=torch.float32, device=qkv.device)      # cleared by the kernel's first stage
     delta = torch.empty((B, n_head, T), dtype=torch.float32, device=qkv.device)
     base, gbase, es = qkv.data_ptr(), dqkv.data_ptr(), qkv.element_size()
     check(lib.tmpi_attention_bwd(base, base + C * es, base + 2 * C * es, C3, out.data_ptr(), C, dout.data_ptr(), C,
-                                 lse.data_ptr(), delta.data_ptr(), dq_acc.data_ptr(), gbase + C * es, gbase + 2 * C * es, C3,
-                                 B, T, n_head, 1.0 / math.sqrt(HEAD), stream_ptr()))
+                                 lse.data_ptr(), delta.data_ptr(), dq_acc.data_ptr(), gbase, gbase + C * es, gbase + 2 * C * es,
+                                 C3, B, T, n_head, 1.0 / math.sqrt(HEAD), stream_ptr()))
     launch_count += 1
-    dqkv[:, :, :C].copy_(dq_acc.view(B, T, C))
     return dqkv
 
 

@@ -186,6 +186,29 @@ def lazy_cases(small: bool) -> dict:
     out["attention_fwd"] = attn_case(True)
     out["attention_sdpa_fwd"] = attn_case(False)
 
+    def attn_bwd_case(route):
+        def build():
+            import math
+            from torchmpi_b200.ops import attention
+            Bq, T, H = (2 if small else 8), 1024, 16
+            C = H * 64
+            qkv = torch.randn(Bq, T, 3 * C, device=dev).to(torch.bfloat16)
+            o, lse = attention.attention_forward(qkv, H)
+            do = torch.randn_like(o)
+            flops = 10.0 * Bq * H * T * T * 64 / 2                         # five products per block pair, causal
+            nbytes = qkv.numel() * 2 * 2 + o.numel() * 2 * 2
+            if route == "own":
+                return (lambda: attention.attention_backward(qkv, o, lse, do, H)), nbytes, flops
+            heads = lambda t: t.view(Bq, T, H, 64).transpose(1, 2)
+            q, k, v = (heads(t) for t in qkv.split(C, dim=2))
+            zero = torch.zeros((), dtype=torch.int64, device=dev)
+            return (lambda: torch.ops.aten._scaled_dot_product_cudnn_attention_backward(
+                heads(do), q, k, v, heads(o), lse.unsqueeze(-1), zero, zero, None, None, None, T, T, 0.0, True,
+                scale=1.0 / math.sqrt(64))), nbytes, flops
+        return build
+    out["attention_bwd"] = attn_bwd_case("own")
+    out["attention_cudnn_bwd"] = attn_bwd_case("cudnn")
+
     def ln_case(backward):
         def build():
             rows, C = (131072 if not small else 65536), 1024        # > L2 both ways
