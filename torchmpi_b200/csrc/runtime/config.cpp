@@ -46,8 +46,8 @@ Tunable g_tunables[] = {
   {"comm_max_ctas", {64}},                 // CTAs of a stand-alone collective kernel
   {"broadcast_algo", {0}},                 // heap broadcasts: 0 by size, 1 pull from the root, 2 scatter + all-gather, 3 multicast store
   {"bcast_max_ctas", {128}},               // CTAs of the multicast-store broadcast (only the root moves data)
-  {"bcast_scatter_max_ctas", {64}},        // CTAs per rank of the scatter + multicast-store broadcast (every member moves 1/N)
-  {"bcast_scatter_min_bytes", {8 << 20}},  // from this size the broadcast scatters by peer loads and gathers by multicast stores
+  {"bcast_scatter_max_ctas", {64}},        // CTAs per rank of the single-pass scatter + all-gather broadcasts
+  {"bcast_scatter_min_bytes", {8 << 20}},  // from this size the broadcast is the single-pass scatter + push
   {"nvls_max_ctas", {32}},                 // CTAs of the multimem kernels: 32 measured best at 8 GPUs (832 GB/s bus at 1 GiB;
                                            // 64 MiB: 637 vs 588 with 64 CTAs); the switch reduction saturates, more CTAs only contend
   {"ps_max_ctas", {148}},                  // CTAs of a parameter-server push / pull kernel (one per SM: +30 % push bandwidth over 64)

@@ -187,7 +187,8 @@ static int broadcast_heap(size_t off, size_t n, int dtype, int root, const tmpi_
   else if (algo == 5 && g->nmembers > 2) op = OP_BCAST_SCATTER_PUSH;
   else if (algo == 2) op = OP_BCAST_CHUNKED;
   else if (algo == 0) {
-    if (mc_auto && bytes >= (size_t)tunable("bcast_scatter_min_bytes")) op = OP_BCAST_SCATTER_MC;
+    // large: scatter + push in one pass (measured ahead of the multicast variants and of NCCL on 4 GPUs from 16 MiB)
+    if (g->nmembers > 2 && vec && bytes >= (size_t)tunable("bcast_scatter_min_bytes")) op = OP_BCAST_SCATTER_PUSH;
     else if (mc_auto && bytes >= (size_t)tunable("nvls_min_bytes")) op = OP_BCAST_MC;
     else if (bytes > (size_t)tunable("broadcast_size_gpu_tree_based") && g->nmembers > 2) op = OP_BCAST_CHUNKED;
   }
