@@ -22,7 +22,7 @@ _scratch = {}
 
 
 def _scratch_for(dev: torch.device, C: int) -> torch.Tensor:
-    key = (dev.index, torch.cuda.current_stream().cuda_stream)
+    key = (dev.index, stream_ptr())
     need = lib.tmpi_bn_scratch_bytes(C)
     buf = _scratch.get(key)
     if buf is None or buf.numel() < need:

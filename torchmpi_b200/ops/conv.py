@@ -27,7 +27,7 @@ _ws = {}
 
 def _workspace(dev: torch.device, need: int) -> torch.Tensor:
     """Per (device, stream) workspace for the fp32 partial tiles of the weight gradient."""
-    key = (dev.index, torch.cuda.current_stream().cuda_stream)
+    key = (dev.index, stream_ptr())
     buf = _ws.get(key)
     if buf is None or buf.numel() < need:
         buf = _ws[key] = torch.empty(max(need, 64 << 20), dtype=torch.uint8, device=dev)

@@ -184,7 +184,7 @@ def bias_grad(dy2: torch.Tensor, z: Optional[torch.Tensor] = None):
             and (z is None or (z.is_contiguous() and z.dtype == dy2.dtype))):
         dz = torch.ops.aten.gelu_backward(dy2, z) if z is not None else dy2
         return dz, dz.sum(0)
-    sp = torch.cuda.current_stream().cuda_stream
+    sp = stream_ptr()
     key = (dy2.device.index, sp)
     need = _bg_need.get(C)
     if need is None:
