@@ -100,6 +100,38 @@ def _ps_scenarios(rank, world):
     return True
 
 
+def _ps_serialized(rank, world):
+    """Every rank overwrites the whole server with its own value, all at once and without barriers: with
+    ``serialized=True`` the server always holds one rank's complete message (lib/parameterserver.cpp:426-499 applies
+    one message at a time per shard), so after the last round every shard holds the same client's value, and the adds
+    that follow are all counted."""
+    import torchmpi_b200 as mpi
+    from torchmpi_b200 import parameterserver as ps
+    mpi.start(with_cuda=False)
+    n = world
+    server = ps.init(torch.zeros(40_000))
+    out = torch.empty(40_000)
+    for it in range(8):
+        h = ps.send(server, torch.full((40_000,), float(rank + 1 + 10 * it)), "copy", serialized=True)
+        assert h.done()                 # the update is in place when the call returns
+    mpi.barrier()
+    mpi.sync_handle(ps.receive(server, out))
+    winner = float(out[0])
+    assert torch.all(out == winner) and winner in [float(r + 1 + 70) for r in range(n)]
+    mpi.barrier()
+    ps.send(server, torch.ones(40_000), "add", serialized=True)
+    mpi.barrier()
+    mpi.sync_handle(ps.receive(server, out))
+    assert torch.all(out == winner + n)
+    ps.free_all()
+    mpi.stop()
+    return True
+
+
+def test_cpu_parameter_server_serialized_sends():
+    assert all(run_ranks(_ps_serialized, 4, timeout=300))
+
+
 def test_cpu_parameter_server_scenarios():
     assert all(run_ranks(_ps_scenarios, 4, timeout=300))
 

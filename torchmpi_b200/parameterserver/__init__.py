@@ -15,7 +15,12 @@ update is already in place at every owner, so ``sync_handle(send); barrier()``
 still means "visible to everybody" (lib/parameterserver.cpp:339-341).
 Concurrent ``add`` updates are exact (atomic adds on the GPU, a per-shard lock on
 the CPU); a ``copy``/``zero`` racing with other updates on the GPU is resolved
-per element, so separate them with a barrier as the reference's tests do.
+per element, so separate them with a barrier as the reference's tests do - or pass
+``serialized=True`` to ``send``: such sends to one server are applied one whole
+message at a time across all clients (a ticket lock in the rendezvous store; the
+call returns when the update is in place), which is the reference's guarantee that
+a shard never sees two rules interleaved (lib/parameterserver.cpp:426-499, one
+message at a time per shard) at the price of a blocking call.
 """
 from __future__ import annotations
 
@@ -30,6 +35,7 @@ from ..runtime import S
 
 RULES = {"zero": 0, "copy": 1, "add": 2}
 _live: List["ParameterServer"] = []
+_created = {}          # members -> servers created so far over exactly these members (the same on each of them)
 
 
 def shard_range(n: int, size: int, rank: int):
@@ -54,6 +60,10 @@ class ParameterServer:
             raise ValueError("parameter server needs at least one element per rank")
         self.on_gpu = bool(t.is_cuda and S.cuda_heap is not None and S.cuda_heap.covers(self.members))
         self.freed = False
+        # a name every member derives alike: creation is collective over the members, in the same order on each
+        key = tuple(self.members)
+        serial = _created[key] = _created.get(key, 0) + 1
+        self.uid = f"{min(key)}.{len(key)}.{hash(key) & 0xffffffff:x}.{serial}"
         self._arr = _lib.int_array(self.members)
         self._staging = None
         runtime.barrier()
@@ -72,16 +82,41 @@ class ParameterServer:
         _live.append(self)
 
     # ---- client operations
-    def send(self, t: torch.Tensor, rule: str = "add") -> Handle:
+    def send(self, t: torch.Tensor, rule: str = "add", serialized: bool = False) -> Handle:
         if rule not in RULES:
             raise ValueError(f"unknown update rule '{rule}' (expected one of {sorted(RULES)})")
         self._check(t)
+        if serialized:
+            return self._send_serialized(t, rule)
         if config.get("fault_drop_ps_requests"):      # host-side fault injection: the request never reports back
             return Handle(ids=[lib.tmpi_test_lost_handle()])
         if self.on_gpu:
             return S.cuda_heap.ps_push(self.impl, t, RULES[rule])
         host = self._to_host(t)
         return Handle(ids=[lib.tmpi_shm_ps_send(self.impl, host.data_ptr(), RULES[rule])], keep=(host,))
+
+    def _send_serialized(self, t: torch.Tensor, rule: str) -> Handle:
+        """One whole message at a time across all clients of this server: take a ticket, wait for the turn, apply the
+        update, wait until it is in place at every owner, pass the turn on.  Returns a completed handle."""
+        import time
+        from .. import watchdog
+        store = runtime._store()
+        base = f"tmpi/ps/{self.uid}"
+        ticket = store.add(base + "/ticket", 1)
+        budget_s = config.get("handle_wait_budget_ms") / 1e3
+        t0, pause = time.monotonic(), 1e-4
+        while store.add(base + "/serving", 0) != ticket - 1:
+            watchdog.check()
+            if time.monotonic() - t0 > budget_s:
+                watchdog.poison(f"parameter server {self.uid}: the turn of ticket {ticket} never came")
+                raise _lib.TimeoutError_(_lib.ERR_TIMEOUT, "serialized parameter-server send timed out waiting for its turn")
+            time.sleep(pause)
+            pause = min(pause * 2, 2e-3)
+        try:
+            self.send(t, rule).wait()
+        finally:
+            store.add(base + "/serving", 1)
+        return Handle()
 
     def receive(self, t: torch.Tensor) -> Handle:
         self._check(t)
@@ -129,8 +164,8 @@ def init(t: torch.Tensor) -> ParameterServer:
     return ParameterServer(t)
 
 
-def send(ps: ParameterServer, t: torch.Tensor, rule: str = "add") -> Handle:
-    return ps.send(t, rule)
+def send(ps: ParameterServer, t: torch.Tensor, rule: str = "add", serialized: bool = False) -> Handle:
+    return ps.send(t, rule, serialized)
 
 
 def receive(ps: ParameterServer, t: torch.Tensor) -> Handle:
