@@ -8,13 +8,15 @@
 //              one buffer (V of the next block is fetched while its scores are exponentiated)
 //   warp 1     MMA issuer:   S = Q K^T (128 x 128, fp32, tensor memory), then O_j = P V (128 x 64, tensor memory)
 //   warps 2-9  softmax:      two threads per query row (tcgen05.ld 32x32b gives a thread its own row, so there are no
-//                            shuffles; the two halves of a row exchange their maxima through shared memory): running
-//                            maximum, P = exp2(scaled S - max) written as bf16 into shared memory in the K-major
-//                            128-byte-swizzled layout that the second MMA reads, then the running output
-//                            acc = acc * alpha + O_j in registers
+//                            shuffles; both read the whole row for its maximum, each exponentiates 64 of the 128
+//                            scores): running maximum, P = exp2(scaled S - max) written as bf16 into shared memory
+//                            in the K-major 128-byte-swizzled layout that the second MMA reads, then the running
+//                            output acc = acc * alpha + O_j in registers (32 of the 64 columns per thread)
 //
 // S for block j + 1 is issued as soon as the softmax warps have read S of block j, so the tensor core works on it
-// while they exponentiate; two CTAs fit on an SM (256 tensor-memory columns and 96 KB of shared memory each), so
+// while they exponentiate, and the row maximum of block j + 1 is found while the tensor core multiplies P_j by V; a
+// quarter of the exponentials run as a cubic on the FMA pipe because the special-function unit (which also packs
+// fp32 pairs into bf16) is the busiest pipe of this kernel.  Two CTAs fit on an SM (256 tensor-memory columns and 96 KB of shared memory each), so
 // one CTA's softmax overlaps the other's MMAs.  Q, K and V are read where the fused QKV projection left them
 // ([B * T, 3 C], one tensor map per operand) and the output is written as [B * T, C]: no transposes around the
 // kernel.  Every wait is bounded; a CTA that gives up records where in the status word and frees its tensor memory.
