@@ -352,33 +352,38 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   }
 }
 
-// delta[b, h, t] = sum_d dO[b, t, h, d] * O[b, t, h, d]: one thread per (row, head), 128-byte reads; the same thread
-// clears its 64 entries of the fp32 dQ buffer, so the caller need not.
+// delta[b, h, t] = sum_d dO[b, t, h, d] * O[b, t, h, d]: eight threads per (row, head), one 16-byte load of O and of
+// dO each (a warp reads four whole 128-byte lines of each tensor per instruction), three shuffles; the same threads
+// clear their 64 entries of the fp32 dQ buffer, so the caller need not.
 __global__ void __launch_bounds__(256)
 attention_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout, int64_t ld_o, int64_t ld_do,
                        float* __restrict__ delta, float* __restrict__ dq_acc, int B, int T, int H) {
-  const long long total = (long long)B * T * H;
-  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+  const long long total = (long long)B * T * H;                  // (row, head) pairs; blockDim.x / 8 of them per block and step
+  const int sub = threadIdx.x & 7;
+  for (long long idx = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 3; idx < total;
+       idx += ((long long)gridDim.x * blockDim.x) >> 3) {
     const int h = (int)(idx % H);
     const long long r = idx / H;                                 // b * T + t
-    const uint4* po = reinterpret_cast<const uint4*>(o + r * ld_o + h * D);
-    const uint4* pd = reinterpret_cast<const uint4*>(dout + r * ld_do + h * D);
+    const uint4 a = __ldg(reinterpret_cast<const uint4*>(o + r * ld_o + h * D) + sub);
+    const uint4 g = __ldg(reinterpret_cast<const uint4*>(dout + r * ld_do + h * D) + sub);
+    const uint32_t wa[4] = {a.x, a.y, a.z, a.w}, wg[4] = {g.x, g.y, g.z, g.w};
     float acc = 0.f;
 #pragma unroll
-    for (int u = 0; u < D / 8; ++u) {
-      const uint4 a = __ldg(po + u), g = __ldg(pd + u);
-      const uint32_t wa[4] = {a.x, a.y, a.z, a.w}, wg[4] = {g.x, g.y, g.z, g.w};
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        acc = fmaf(__uint_as_float(wa[e] << 16), __uint_as_float(wg[e] << 16), acc);
-        acc = fmaf(__uint_as_float(wa[e] & 0xffff0000u), __uint_as_float(wg[e] & 0xffff0000u), acc);
-      }
+    for (int e = 0; e < 4; ++e) {
+      acc = fmaf(__uint_as_float(wa[e] << 16), __uint_as_float(wg[e] << 16), acc);
+      acc = fmaf(__uint_as_float(wa[e] & 0xffff0000u), __uint_as_float(wg[e] & 0xffff0000u), acc);
     }
-    const int b = (int)(r / T), t = (int)(r - (long long)b * T);
-    delta[((size_t)b * H + h) * T + t] = acc;
-    float4* z = reinterpret_cast<float4*>(dq_acc + (size_t)r * (H * D) + h * D);
-#pragma unroll
-    for (int u = 0; u < D / 4; ++u) z[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+    const unsigned group = 0xffu << (threadIdx.x & 24);          // the eight lanes of this (row, head)
+    acc += __shfl_xor_sync(group, acc, 1);
+    acc += __shfl_xor_sync(group, acc, 2);
+    acc += __shfl_xor_sync(group, acc, 4);
+    if (sub == 0) {
+      const int b = (int)(r / T), t = (int)(r - (long long)b * T);
+      delta[((size_t)b * H + h) * T + t] = acc;
+    }
+    float4* z = reinterpret_cast<float4*>(dq_acc + (size_t)r * (H * D) + h * D) + sub * 2;
+    z[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+    z[1] = make_float4(0.f, 0.f, 0.f, 0.f);
   }
 }
 
@@ -435,7 +440,7 @@ int tmpi_attention_bwd(const void* q, const void* k, const void* v, int64_t ld_q
   if ((int64_t)B * H * (T / 128) > 0x7fffffffLL) return fail(TMPI_ERR_INVALID, "attention backward: too many blocks");
   cudaStream_t s = (cudaStream_t)stream;
   const long long rows_heads = (long long)B * T * H;
-  const int dgrid = (int)std::min<long long>((rows_heads + 255) / 256, 148 * 8);
+  const int dgrid = (int)std::min<long long>((rows_heads * 8 + 255) / 256, 148 * 8);
   attnb::attention_delta_kernel<<<dgrid, 256, 0, s>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, ld_o, ld_do, delta, dq_acc, B, T, H);
   CUtensorMap mq, mk, mv, mdo;
   int st;
