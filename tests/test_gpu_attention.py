@@ -20,7 +20,7 @@ def _ref(qkv, H):
     return out.transpose(1, 2).reshape(B, T, C), lse
 
 
-@pytest.mark.parametrize("B,T,H", [(1, 128, 1), (2, 256, 3), (2, 1024, 4), (1, 512, 16)])
+@pytest.mark.parametrize("B,T,H", [(1, 128, 1), (2, 256, 3), (2, 1024, 4), (1, 512, 16), (1, 2048, 2)])
 def test_attention_forward_matches_fp32(B, T, H):
     from torchmpi_b200.ops import attention
     from torchmpi_b200._lib import lib
@@ -119,7 +119,7 @@ def test_attention_phase_trace_is_ordered():
     assert int(buf.abs().sum()) == 0
 
 
-@pytest.mark.parametrize("B,T,H", [(1, 128, 1), (2, 384, 2), (1, 1024, 3)])
+@pytest.mark.parametrize("B,T,H", [(1, 128, 1), (2, 384, 2), (1, 1024, 3), (1, 2048, 2)])
 def test_attention_backward_matches_fp32(B, T, H):
     """dQ, dK, dV of the tcgen05 backward kernel against fp32 autograd of softmax(Q K^T / sqrt(d)) V."""
     from torchmpi_b200.ops import attention
