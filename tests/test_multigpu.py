@@ -161,6 +161,65 @@ def test_gpu_collectives(backend, world):
     print(backend, world, res[0])
 
 
+def _hierarchical(rank, world):
+    """Hierarchical allreduce on GPUs (groups pushed as a second communicator level, lib/collectives_cuda.cpp:501-581):
+    synchronous, asynchronous (a live handle at once, the whole intra -> inter -> broadcast chain behind it,
+    lib/collectives_cuda.cpp:771-803) and from the asynchronous backward registration, each equal to the flat result."""
+    import time
+    import torchmpi_b200 as mpi
+    from torchmpi_b200 import nn as mpinn
+    gsize = 2 if world >= 4 else 1
+
+    def custom():
+        return mpi.push_communicator(str(mpi.rank() // gsize))
+
+    mpi.start(with_cuda=True, custom_communicator_init=custom, with_cartesian_communicator=True)
+    dev = mpi.device
+    mpi.set_collective_span(0, 1)                  # outer = everyone, inner = the groups
+    want = world * (world - 1) / 2
+    for n in (1000, 1 << 20):
+        t = torch.full((n,), float(rank), device=dev)
+        mpi.allreduce_tensor(t)
+        assert torch.all(t == want), (n, t[:3])
+        mpi.config.set_flat_collectives()
+        f = torch.full((n,), float(rank), device=dev)
+        mpi.allreduce_tensor(f)
+        assert torch.equal(f, t)
+        mpi.config.set_hierarchical_collectives()
+        a = torch.full((n,), float(rank), device=dev)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        h = mpi.async_.allreduce_tensor(a)
+        launch_us = (time.perf_counter() - t0) * 1e6
+        assert h is not None and launch_us < 20000, launch_us       # returns at once: the chain runs behind the handle
+        mpi.sync_handle(h)
+        torch.cuda.synchronize()
+        assert torch.equal(a, t)
+    # gradients through the asynchronous backward registration on the hierarchical span
+    torch.manual_seed(7)
+    net = torch.nn.Sequential(torch.nn.Linear(64, 128), torch.nn.ReLU(), torch.nn.Linear(128, 10)).to(dev)
+    mpinn.synchronize_parameters(net)
+    x = torch.randn(32, 64, generator=torch.Generator().manual_seed(100 + rank)).to(dev)
+    mpinn.async_.register_async_mpi_backward(net, scale=1.0 / world)
+    net(x).square().mean().backward()
+    mpinn.async_.synchronize_gradients(net)
+    torch.cuda.synchronize()
+    got = [p.grad.clone() for p in net.parameters()]
+    mpinn.async_.unregister_async_mpi_backward(net)
+    net.zero_grad()
+    net(x).square().mean().backward()
+    mpi.config.set_flat_collectives()
+    mpinn.synchronize_gradients(net, scale=1.0 / world)
+    for g, p in zip(got, net.parameters()):
+        assert torch.allclose(g, p.grad, atol=1e-6, rtol=1e-5)
+    mpi.stop()
+    return True
+
+
+def test_hierarchical_allreduce_on_gpus():
+    assert all(run_ranks(_hierarchical, world_sizes()[-1], timeout=600))
+
+
 def _engine(rank, world):
     import torchmpi_b200 as mpi
     from torchmpi_b200 import config
