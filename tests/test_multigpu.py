@@ -217,7 +217,9 @@ def _hierarchical(rank, world):
 
 
 def test_hierarchical_allreduce_on_gpus():
-    assert all(run_ranks(_hierarchical, world_sizes()[-1], timeout=600))
+    # two ranks, groups of one: the whole chain (intra, inter, broadcast) with the smallest GPU count; groups of two
+    # run among CPU ranks (tests/test_cpu_collectives.py) and in the 2 x 4 GPT-2 benchmark
+    assert all(run_ranks(_hierarchical, 2, timeout=600))
 
 
 def _engine(rank, world):
